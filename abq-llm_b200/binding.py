@@ -1,0 +1,172 @@
+"""ctypes binding of include/abq_b200.h.  Device buffers are torch CUDA tensors (or raw pointers).
+
+There is no fallback: if the shared library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+ROUTE_AUTO, ROUTE_B1_MMA, ROUTE_I8_MMA, ROUTE_I8_UMMA = 0, 1, 2, 3
+OUT_INT32, OUT_FP16 = 0, 1
+SCALE_NONE, SCALE_TENSOR_COMPAT, SCALE_CHANNEL, SCALE_GROUP = 0, 1, 2, 3
+FLAG_PDL = 1
+
+_PKG = Path(__file__).resolve().parent
+
+
+class AbqError(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        super().__init__(f"{what}: abq_status {status} ({_status_string(status)})")
+
+
+class GemmParams(ctypes.Structure):
+    """Mirror of ``abq_gemm_params`` (field order is part of the ABI)."""
+    _fields_ = [
+        ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+        ("X", ctypes.c_void_p), ("W", ctypes.c_void_p), ("C", ctypes.c_void_p), ("D", ctypes.c_void_p),
+        ("bias", ctypes.c_int),
+        ("x_bits", ctypes.c_int), ("w_bits", ctypes.c_int),
+        ("x_signed", ctypes.c_int), ("w_signed", ctypes.c_int),
+        ("out_dtype", ctypes.c_int), ("scale_mode", ctypes.c_int), ("group_size", ctypes.c_int),
+        ("w_scale", ctypes.c_void_p), ("w_zero", ctypes.c_void_p), ("x_scale", ctypes.c_void_p),
+        ("route", ctypes.c_int), ("flags", ctypes.c_int),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("status_word", ctypes.c_void_p),
+    ]
+
+
+class GemmState(ctypes.Structure):
+    """Mirror of ``abq_gemm_state``."""
+    _fields_ = [
+        ("p", GemmParams),
+        ("init_success", ctypes.c_int), ("route", ctypes.c_int),
+        ("grid", ctypes.c_int * 3), ("block", ctypes.c_int * 3), ("cluster", ctypes.c_int),
+        ("shared_mem_size", ctypes.c_size_t),
+        ("tile", ctypes.c_int * 4),
+        ("tmap", (ctypes.c_ulonglong * 16) * 3),
+    ]
+
+
+_lib = None
+
+
+def lib_path() -> Path:
+    return _PKG / "lib" / "libabq_b200.so"
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not path.exists():
+            raise FileNotFoundError(f"{path} is missing: run `python abq-llm_b200/build.py` (no fallback exists)")
+        L = ctypes.CDLL(str(path))
+        L.abq_version.restype = ctypes.c_char_p
+        L.abq_status_string.restype = ctypes.c_char_p
+        L.abq_status_string.argtypes = [ctypes.c_int]
+        L.abq_last_cuda_error.restype = ctypes.c_int
+        L.abq_gemm_workspace_bytes.restype = ctypes.c_size_t
+        L.abq_gemm_workspace_bytes.argtypes = [ctypes.c_int] * 6
+        L.abq_gemm_init.argtypes = [ctypes.POINTER(GemmParams), ctypes.POINTER(GemmState)]
+        L.abq_gemm_exec.argtypes = [ctypes.POINTER(GemmState), ctypes.c_void_p]
+        L.abq_gemm.argtypes = [ctypes.POINTER(GemmParams), ctypes.c_void_p]
+        L.abq_pack_int32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        L.abq_pack_int4.argtypes = L.abq_pack_int32.argtypes
+        L.abq_quantize_pack_half.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                             ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        L.abq_unpack_int8.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_void_p]
+        _lib = L
+    return _lib
+
+
+def _status_string(s: int) -> str:
+    try:
+        return lib().abq_status_string(s).decode()
+    except Exception:  # library missing: still give a message
+        return "?"
+
+
+def version() -> str:
+    return lib().abq_version().decode()
+
+
+def _ptr(t) -> int | None:
+    """Device address of a torch tensor, an int, or None."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    assert t.is_cuda and t.is_contiguous(), "device buffers must be contiguous CUDA tensors"
+    return t.data_ptr()
+
+
+def _stream(stream) -> int | None:
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        extra = ""
+        if status == 4:
+            extra = f" [cudaError {lib().abq_last_cuda_error()}]"
+        raise AbqError(status, what + extra)
+
+
+def gemm_workspace_bytes(M: int, N: int, K: int, x_bits: int, w_bits: int, route: int = ROUTE_AUTO) -> int:
+    return int(lib().abq_gemm_workspace_bytes(M, N, K, x_bits, w_bits, route))
+
+
+def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dtype=OUT_INT32, scale_mode=SCALE_NONE,
+                group_size=0, C=None, w_scale=None, w_zero=None, x_scale=None, route=ROUTE_AUTO, flags=0, workspace=None,
+                status_word=None) -> GemmParams:
+    p = GemmParams()
+    p.M, p.N, p.K = M, N, K
+    p.X, p.W, p.C, p.D = _ptr(X), _ptr(W), _ptr(C), _ptr(D)
+    p.bias = 0
+    p.x_bits, p.w_bits, p.x_signed, p.w_signed = x_bits, w_bits, int(x_signed), int(w_signed)
+    p.out_dtype, p.scale_mode, p.group_size = out_dtype, scale_mode, group_size
+    p.w_scale, p.w_zero, p.x_scale = _ptr(w_scale), _ptr(w_zero), _ptr(x_scale)
+    p.route, p.flags = route, flags
+    p.workspace = _ptr(workspace)
+    p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    p.status_word = _ptr(status_word)
+    return p
+
+
+def gemm_init(params: GemmParams) -> GemmState:
+    st = GemmState()
+    _check(lib().abq_gemm_init(ctypes.byref(params), ctypes.byref(st)), "abq_gemm_init")
+    return st
+
+
+def gemm_exec(state: GemmState, stream=None) -> None:
+    _check(lib().abq_gemm_exec(ctypes.byref(state), _stream(stream)), "abq_gemm_exec")
+
+
+def gemm(params: GemmParams, stream=None) -> None:
+    _check(lib().abq_gemm(ctypes.byref(params), _stream(stream)), "abq_gemm")
+
+
+def pack_int32(values, planes, rows: int, K: int, bits: int, stream=None) -> None:
+    _check(lib().abq_pack_int32(_ptr(values), _ptr(planes), rows, K, bits, _stream(stream)), "abq_pack_int32")
+
+
+def pack_int4(nibbles, planes, rows: int, K: int, bits: int = 4, stream=None) -> None:
+    _check(lib().abq_pack_int4(_ptr(nibbles), _ptr(planes), rows, K, bits, _stream(stream)), "abq_pack_int4")
+
+
+def quantize_pack_half(x_half, scale, planes, rows: int, K: int, bits: int, mode: int = 0, stream=None) -> None:
+    _check(lib().abq_quantize_pack_half(_ptr(x_half), _ptr(scale), _ptr(planes), rows, K, bits, mode, _stream(stream)),
+           "abq_quantize_pack_half")
+
+
+def unpack_int8(planes, out_i8, rows: int, K: int, bits: int, signed: bool, stream=None) -> None:
+    _check(lib().abq_unpack_int8(_ptr(planes), _ptr(out_i8), rows, K, bits, int(signed), _stream(stream)), "abq_unpack_int8")

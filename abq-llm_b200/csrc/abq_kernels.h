@@ -1,0 +1,50 @@
+// Host-callable launchers of the kernels in this directory and the layout constants they share.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "../../include/abq_b200.h"
+
+namespace abq {
+
+// ---- pack.cu
+cudaError_t pack_int32(const int32_t *in, uint32_t *planes, int rows, int K, int bits, cudaStream_t stream);
+cudaError_t pack_int4(const void *in, uint32_t *planes, int rows, int K, int bits, cudaStream_t stream);
+cudaError_t quantize_pack_half(const __half *in, const float *scale, uint32_t *planes, int rows, int K, int bits, int mode,
+                               cudaStream_t stream);
+
+// ---- xprep.cu
+cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream);
+// Bytes of one decode-route activation record (one per 128 input features): MT token tiles of 8.
+__host__ __device__ constexpr int decode_record_bytes(int MT) { return 1024 * MT + 64; }
+cudaError_t xprep_decode(const uint32_t *xplanes, void *records, int M, int K, int bits, int x_signed, int MT, bool pdl,
+                         cudaStream_t stream);
+
+// ---- gemm_decode.cu (route ABQ_ROUTE_I8_MMA, M <= 16)
+constexpr int kDecodeBN = 64;        // weight rows per CTA (4 consumer warps x 16)
+constexpr int kDecodeChunkK = 1024;  // input features per pipeline stage (128 B per plane row)
+abq_status decode_plan(abq_gemm_state *st);
+cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream);
+size_t decode_workspace_bytes(int M, int K);
+
+// ---- gemm_b1.cu (route ABQ_ROUTE_B1_MMA)
+abq_status b1_plan(abq_gemm_state *st);
+cudaError_t b1_launch(const abq_gemm_state *st, cudaStream_t stream);
+
+// ---- gemm_umma.cu (route ABQ_ROUTE_I8_UMMA)
+abq_status umma_plan(abq_gemm_state *st);
+cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream);
+size_t umma_workspace_bytes(int M, int N, int K);
+
+// ---- api.cu helpers
+// Encodes a tiled TMA descriptor through the driver entry point (no link-time libcuda dependency).
+// dims/strides innermost first; strides in bytes for dimensions 1..rank-1.
+enum TmapSwizzle { TMAP_SWIZZLE_NONE = 0, TMAP_SWIZZLE_64B = 2, TMAP_SWIZZLE_128B = 3 };
+enum TmapDtype { TMAP_U8 = 0, TMAP_U32 = 1 };
+bool encode_tmap(void *out128, TmapDtype dtype, int rank, const void *base, const uint64_t *dims, const uint64_t *strides_bytes,
+                 const uint32_t *box, TmapSwizzle swizzle);
+void set_last_cuda_error(cudaError_t e);
+int env_int(const char *name, int fallback);
+
+} // namespace abq

@@ -1,0 +1,178 @@
+/*
+ * abq_b200.h -- C ABI of the B200 (sm_100a) arbitrary-bit quantized GEMM engine.
+ *
+ * The library computes D = X * W^T where X (M x K, p-bit codes) and W (N x K, q-bit codes) are
+ * stored as bit-planes of 32-bit words:
+ *
+ *     plane word  P[b][row][kw]   (b < bits, row < rows, kw < K/32)
+ *     bit (31 - j) of that word = bit b of the code of element (row, 32*kw + j)
+ *
+ * Unsigned code value = sum_b 2^b bit_b.  Signed: the top plane has weight -2^(bits-1).
+ * K must be a multiple of 128.  This is the storage format of the reference engine
+ * (engine/common/pack.cu:46-64, engine/mma_any/aq_bmma_kernel.h:121-127); weights arrive already
+ * packed, activations are packed (or quantised and packed) per call.
+ *
+ * All pointers are device pointers unless stated otherwise.  Nothing is allocated by the library;
+ * scratch memory is a caller-owned workspace.  All launches are asynchronous on the stream given.
+ * Every entry point returns an abq_status; 0 is success.  There is no CPU fallback: if no usable
+ * GPU kernel exists for a request the call fails with ABQ_ERR_UNSUPPORTED.
+ *
+ * Each declaration cites the reference interface it replaces (path inside the reference repo).
+ */
+#ifndef ABQ_B200_H
+#define ABQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define ABQ_API __attribute__((visibility("default")))
+#else
+#define ABQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A CUDA stream handle (cudaStream_t) passed as an opaque pointer so that C callers need no CUDA headers. */
+typedef void *abq_stream_t;
+
+typedef enum abq_status {
+    ABQ_OK = 0,
+    ABQ_ERR_INVALID_ARG = 1,   /* null pointer, bad shape (K % 128 != 0, bits outside 1..8, ...) */
+    ABQ_ERR_UNSUPPORTED = 2,   /* valid request with no kernel (e.g. bias != 0) */
+    ABQ_ERR_WORKSPACE = 3,     /* workspace missing or smaller than abq_gemm_workspace_bytes() */
+    ABQ_ERR_CUDA = 4,          /* a CUDA runtime/driver call failed; see abq_last_cuda_error() */
+    ABQ_ERR_NOT_INITIALIZED = 5, /* abq_gemm_exec on a state that abq_gemm_init did not complete */
+    ABQ_ERR_DEVICE_TIMEOUT = 6 /* reported through the device status word: a bounded wait expired */
+} abq_status;
+
+typedef enum abq_out_dtype {
+    ABQ_OUT_INT32 = 0, /* raw plane-accumulated int32, as the reference engine writes */
+    ABQ_OUT_FP16 = 1   /* fused dequantisation to IEEE half */
+} abq_out_dtype;
+
+typedef enum abq_scale_mode {
+    ABQ_SCALE_NONE = 0,          /* int32 output only */
+    ABQ_SCALE_TENSOR_COMPAT = 1, /* D = half(int acc) * C[0]: the FasterTransformer copy's epilogue */
+    ABQ_SCALE_CHANNEL = 2,       /* D = x_scale[m] * w_scale[n] * (acc - w_zero[n] * sum_k x[m][k]) */
+    ABQ_SCALE_GROUP = 3          /* same with one scale/zero per run of group_size input features */
+} abq_scale_mode;
+
+typedef enum abq_route {
+    ABQ_ROUTE_AUTO = 0,
+    ABQ_ROUTE_B1_MMA = 1,   /* legacy mma.sync b1 AND+POPC over stacked planes (route A) */
+    ABQ_ROUTE_I8_MMA = 2,   /* planes recombined in registers, mma.sync s8/u8, TMA-fed, split-K (decode) */
+    ABQ_ROUTE_I8_UMMA = 3   /* planes recombined to int8 tiles, tcgen05.mma kind::i8 in TMEM (route B) */
+} abq_route;
+
+enum {
+    ABQ_FLAG_PDL = 1 /* launch with programmatic dependent launch so that consecutive GEMMs overlap */
+};
+
+/*
+ * Problem description.  The first eight fields are the reference's launch arguments in the
+ * reference's order (engine/mma_any/aq_bmma_op.h:24-31 `AqBMMAOpState::Argument_t`:
+ * M, N, K, X, W, C, D, bias); the rest extends them.
+ */
+typedef struct abq_gemm_params {
+    int M, N, K;
+    const void *X;  /* uint32 planes [x_bits][M][K/32] */
+    const void *W;  /* uint32 planes [w_bits][N][K/32] */
+    const void *C;  /* ABQ_SCALE_TENSOR_COMPAT: one fp16 scale; otherwise unused (reference: `half *C`) */
+    void *D;        /* int32 [M][N] or fp16 [M][N], row-major */
+    int bias;       /* must be 0: the reference asserts !bias (aq_bmma_op.h:79) */
+
+    int x_bits, w_bits;     /* 1..8 each */
+    int x_signed, w_signed; /* the reference has one SIGNED flag for both (common/base.h QuantType) */
+    int out_dtype;          /* abq_out_dtype */
+    int scale_mode;         /* abq_scale_mode */
+    int group_size;         /* ABQ_SCALE_GROUP: multiple of 128 dividing K */
+    const void *w_scale;    /* fp16 [N] (CHANNEL) or [N][K/group_size] (GROUP) */
+    const uint8_t *w_zero;  /* optional zero points, same shape as w_scale, NULL = 0 */
+    const float *x_scale;   /* optional per-token fp32 scale [M], NULL = 1 */
+    int route;              /* abq_route */
+    int flags;              /* ABQ_FLAG_* */
+    void *workspace;        /* >= abq_gemm_workspace_bytes(), 256-byte aligned */
+    size_t workspace_bytes;
+    int *status_word;       /* optional device int, set non-zero by a kernel whose bounded wait expired */
+} abq_gemm_params;
+
+/*
+ * Launch plan produced by abq_gemm_init and consumed by abq_gemm_exec.  Plain data, copyable, no
+ * ownership.  Replaces `AqBMMAOpState` (engine/mma_any/aq_bmma_op.h:19-32).
+ */
+typedef struct abq_gemm_state {
+    abq_gemm_params p;
+    int init_success;  /* reference: `bool initSuccess` */
+    int route;         /* route chosen (abq_route, never AUTO) */
+    int grid[3];
+    int block[3];
+    int cluster;       /* split-K factor == cluster size along K (decode route) */
+    size_t shared_mem_size;
+    int tile[4];       /* route specific tile description */
+    unsigned long long tmap[3][16]; /* TMA tensor maps (128 B each), route specific */
+} abq_gemm_state;
+
+/* Bytes of caller-owned scratch a GEMM of this shape may need (route AUTO: the maximum over routes). */
+ABQ_API size_t abq_gemm_workspace_bytes(int M, int N, int K, int x_bits, int w_bits, int route);
+
+/*
+ * Plan a GEMM: validates, picks the route and tile, encodes TMA descriptors, sets kernel
+ * attributes.  Host work only, no launch.  Replaces `AqBMMAInitFn_t` / `AqBWMMAInitFn_t`
+ * (engine/mma_any/aq_bmma_op.h:141-151,163; aq_wmma_op.h) and the per-config
+ * `AqBMMA_..._InitFn` globals (engine/common/base.h:144-166): tile shape is chosen here, not by name.
+ */
+ABQ_API abq_status abq_gemm_init(const abq_gemm_params *params, abq_gemm_state *state);
+
+/*
+ * Launch a planned GEMM on `stream`.  Replaces `AqBMMAExecFn_t` (aq_bmma_op.h:153-164) and
+ * `launchWmmaAnyKernel` (engine/wmma_any/wmma_any.h:30-38).
+ */
+ABQ_API abq_status abq_gemm_exec(const abq_gemm_state *state, abq_stream_t stream);
+
+/* init + exec in one call (what the FasterTransformer wrapper does per linear layer,
+ * fastertransformer/src/fastertransformer/kernels/abqgemm/abq_gemm_wrapper.cu:125-137). */
+ABQ_API abq_status abq_gemm(const abq_gemm_params *params, abq_stream_t stream);
+
+/*
+ * Value tensor -> bit-planes.  `in` holds one int32 per code, row-major [rows][K]; only the low
+ * `bits` bits are used.  Replaces `launch_pack` (engine/common/pack.h:23-24, pack.cu:93-103) and
+ * `ABQGEMMWrapper::pack(const int*, ...)` (abq_gemm_wrapper.cu:71-77).
+ */
+ABQ_API abq_status abq_pack_int32(const int32_t *in, void *planes, int rows, int K, int bits, abq_stream_t stream);
+
+/*
+ * Nibble-packed 4-bit codes (8 per 32-bit word, first element in the most significant nibble)
+ * -> bit-planes.  Replaces `launch_pack4` (engine/common/pack.h:20-21, pack.cu:73-84).
+ */
+ABQ_API abq_status abq_pack_int4(const void *in, void *planes, int rows, int K, int bits, abq_stream_t stream);
+
+/*
+ * fp16 activations -> integer codes -> bit-planes in one pass.
+ *   mode 0 (compat): code = (int)(half(x) * half(scale[0])), truncating, unclamped: bit-exact twin
+ *                    of `pack_half` (abq_gemm_wrapper.cu:29-54, called from :62-69).
+ *   mode 1 (rtn):    code = clamp(rint(x / scale[row]), -2^(bits-1), 2^(bits-1)-1), per-token
+ *                    scale (the dynamic per-token quantiser of algorithm/quantize/quantizer.py:111-159).
+ * `scale` is a device pointer to 1 (mode 0) or `rows` (mode 1) floats.
+ */
+ABQ_API abq_status abq_quantize_pack_half(const void *in_half, const float *scale, void *planes, int rows, int K,
+                                  int bits, int mode, abq_stream_t stream);
+
+/* Bit-planes -> int8 codes, row-major [rows][K] (two's complement for signed; unsigned 8-bit codes are
+ * stored as uint8).  Used by route B; exported because weight planes can be expanded once and cached. */
+ABQ_API abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, int K, int bits, int is_signed,
+                           abq_stream_t stream);
+
+/* Text for a status code; cudaError_t of the last failing CUDA call in this thread (0 if none). */
+ABQ_API const char *abq_status_string(abq_status s);
+ABQ_API int abq_last_cuda_error(void);
+
+/* Library / build identification, e.g. "abq_b200 0.1 sm_100a". */
+ABQ_API const char *abq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ABQ_B200_H */
