@@ -25,6 +25,7 @@ namespace abq {
 constexpr int kConsumerWarps = kDecodeBN / 16;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 8;
+constexpr int kScaleStageWords = 2 * 2 * 16 * 8; // per consumer warp: two buffers of 16 rows x 8 groups, scales and zero points
 
 struct DecodeArgs {
     int M, N, K;
@@ -55,7 +56,8 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const __grid_con
     uint8_t *stage_base = smem;
     uint8_t *rec_base = stage_base + (size_t)a.stages * kStageBytes;
     int *red = reinterpret_cast<int *>(rec_base + a.rec_smem_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(red + kDecodeBN * 8 * MT);
+    float *scale_stage = reinterpret_cast<float *>(red + kDecodeBN * 8 * MT); // [warp][buffer][16 rows][8 groups] scale, then zero
+    uint64_t *bars = reinterpret_cast<uint64_t *>(scale_stage + kConsumerWarps * kScaleStageWords);
     uint64_t *full = bars, *empty = bars + kMaxStages, *xbar = bars + 2 * kMaxStages;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -121,21 +123,47 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const __grid_con
             }
             xs[mt][0] = xs[mt][1] = 0;
         }
+        // GROUP mode: the scales / zero points of a chunk (16 rows x 8 groups per warp) are fetched one chunk ahead
+        // into registers (lane = row * 2 + half, four groups each) and parked in a warp-private staging buffer, so
+        // that folding a group never waits on global memory.
+        float *sc_stage = scale_stage + warp * kScaleStageWords;
+        int *z_stage = reinterpret_cast<int *>(sc_stage + 2 * 16 * 8);
+        float pre_sc[4];
+        int pre_z[4];
+        auto prefetch_scales = [&](int c) {
+            const int n = n0 + warp * 16 + (lane >> 1);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int gl = c * 8 + (lane & 1) * 4 + j;
+                pre_sc[j] = 0.f;
+                pre_z[j] = 0;
+                if (grouped && gl < g_count && n < a.N) {
+                    const size_t idx = (size_t)n * a.scale_groups + (g_begin + gl) / a.groups_per_scale;
+                    pre_sc[j] = __half2float(ld_half(a.w_scale + idx));
+                    if (a.w_zero)
+                        pre_z[j] = a.w_zero[idx];
+                }
+            }
+        };
+        auto park_scales = [&](int c) {
+            float *sdst = sc_stage + (c & 1) * 128 + (lane >> 1) * 8 + (lane & 1) * 4;
+            int *zdst = z_stage + (c & 1) * 128 + (lane >> 1) * 8 + (lane & 1) * 4;
+            *reinterpret_cast<float4 *>(sdst) = make_float4(pre_sc[0], pre_sc[1], pre_sc[2], pre_sc[3]);
+            *reinterpret_cast<int4 *>(zdst) = make_int4(pre_z[0], pre_z[1], pre_z[2], pre_z[3]);
+            __syncwarp();
+        };
+        if (grouped)
+            prefetch_scales(0);
         bool ok = mbar_wait_bounded(xbar, 0, a.status, STATUS_TIMEOUT_TMA);
-        int pending_sg = -1; // scale group with unfolded accumulators (a slice may end inside a scale group)
+        int pending_gi = -1; // group (within the current chunk) whose scale group still has unfolded accumulators
 
-        // One scale group finished: fold the integer accumulators into fp32 (GROUP mode).
-        auto fold = [&](int sg) {
+        // One scale group finished: fold the integer accumulators into fp32 (GROUP mode).  `buf`/`gi` select the
+        // staged scale and zero point of the 128-group that closes it.
+        auto fold = [&](int buf, int gi) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const int n = n0 + row_a + 8 * h;
-                float sc = 0.f;
-                int z = zoff;
-                if (n < a.N) {
-                    sc = __half2float(ld_half(a.w_scale + (size_t)n * a.scale_groups + sg));
-                    if (a.w_zero)
-                        z += __ldg(a.w_zero + (size_t)n * a.scale_groups + sg);
-                }
+                const float sc = sc_stage[buf * 128 + (g + 8 * h) * 8 + gi];
+                const int z = zoff + z_stage[buf * 128 + (g + 8 * h) * 8 + gi];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -158,6 +186,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const __grid_con
                 break;
             const uint8_t *stage = stage_base + (size_t)s * kStageBytes;
             const int groups_here = min(8, g_count - c * 8);
+            if (grouped) {
+                park_scales(c);
+                if (c + 1 < n_chunks)
+                    prefetch_scales(c + 1);
+            }
             for (int gi = 0; gi < groups_here; ++gi) {
                 const int gl = c * 8 + gi; // group index inside the slice
                 uint32_t pa[Q], pb[Q];
@@ -188,20 +221,23 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const __grid_con
                     xs[mt][1] += sv.y;
                 }
                 if (grouped) {
-                    const int gg = g_begin + gl;
-                    pending_sg = gg / a.groups_per_scale;
-                    if ((gg + 1) % a.groups_per_scale == 0) {
-                        fold(pending_sg);
-                        pending_sg = -1;
+                    pending_gi = gi;
+                    if ((g_begin + gl + 1) % a.groups_per_scale == 0) {
+                        fold(c & 1, gi);
+                        pending_gi = -1;
                     }
                 }
+            }
+            // a scale group that continues into the next chunk (or slice) is folded here with the same scale: the
+            // fold is linear, and the staged values of this chunk are overwritten two chunks from now
+            if (grouped && pending_gi >= 0) {
+                fold(c & 1, pending_gi);
+                pending_gi = -1;
             }
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(&empty[s]);
         }
-        if (grouped && pending_sg >= 0)
-            fold(pending_sg);
         __syncwarp();
 
         // partial result of this slice -> reduce buffer, [token][row] so that the reducer reads rows contiguously
@@ -365,7 +401,8 @@ abq_status decode_plan(abq_gemm_state *st)
     if (stages < 1 || stages > kMaxStages)
         return ABQ_ERR_INVALID_ARG;
     const int rec_bytes = chunks_per_cta * 8 * decode_record_bytes(MT);
-    const size_t smem = 1024 + (size_t)stages * stage_bytes + rec_bytes + (size_t)kDecodeBN * 8 * MT * 4 + (2 * kMaxStages + 1) * 8;
+    const size_t smem = 1024 + (size_t)stages * stage_bytes + rec_bytes + (size_t)kDecodeBN * 8 * MT * 4 +
+                        (size_t)kConsumerWarps * kScaleStageWords * 4 + (2 * kMaxStages + 1) * 8;
     if (smem > 227 * 1024)
         return ABQ_ERR_UNSUPPORTED;
     if (p.workspace_bytes < decode_workspace_bytes(p.M, p.K) || !p.workspace)

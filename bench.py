@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the arbitrary-bit quantized GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload at every N (one replica per GPU, no data-path collective): the decode-shape sweep
+W2A8, W3A8, W4A8 x M in {1, 4, 16} over the LLaMA-7B linear shapes (N, K) in {(4096, 4096),
+(12288, 4096), (11008, 4096), (4096, 11008)}; weights unsigned uniform over their bit range with a
+per-128-group fp16 scale ~U(0.001, 0.02) and an integer zero point, activations int8 ~N(0, 30)
+clipped, fp16 dequantised output.  One step = one pass over the 36 GEMMs.  All data is synthetic and
+seeded; it stands in for real checkpoints, which are not needed to time a GEMM.
+
+Metric: algorithmic GB/s (weight planes + activation planes + scales + zero points + output, each
+counted once per GEMM) summed over the sweep -- the decode path is HBM-bound, so this is the number
+its roofline is stated in; effective TOPS (2*M*N*K / t) per WxAy is reported beside it.
+
+The line also carries `e2e` (same metric through the C ABI with host buffers: activation planes are
+copied from pinned host memory and the fp16 result is copied back inside the timed region),
+`roofline` (dominant kernel against the measured HBM peak) and `cpu_baseline` (the reference's CPU
+loop on a bounded sample, rank 0, N=1 only).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = [(4096, 4096), (12288, 4096), (11008, 4096), (4096, 11008)]
+WBITS = [2, 3, 4]
+MS = [1, 4, 16]
+XBITS = 8
+GROUP = 128
+WEIGHT_COPIES = 2  # every weight exists twice and the copies alternate, so a pass never finds its planes in L2
+METRIC = "quant_gemm_decode_sweep_algorithmic_GBps"
+
+
+def load_package():
+    pkg = ROOT / "abq-llm_b200"
+    spec = importlib.util.spec_from_file_location("abq_llm_b200", pkg / "__init__.py", submodule_search_locations=[str(pkg)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["abq_llm_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def algorithmic_bytes(M, N, K, p, q, group=GROUP):
+    """Bytes one GEMM must move: W planes, X planes, fp16 output, fp16 scales, u8 zero points."""
+    return q * N * K // 8 + p * M * K // 8 + 2 * M * N + 2 * N * (K // group) + N * (K // group)
+
+
+def measured_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_workload(abq, torch, seed):
+    """Seeded device-resident operands (packed by the library's own pack kernel) and one launch plan per GEMM."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    B = abq.binding
+
+    def pack(codes, bits):
+        rows, K = codes.shape
+        planes = torch.empty((bits, rows, K // 32), dtype=torch.int32, device="cuda")
+        abq.pack_int32(codes.contiguous(), planes, rows, K, bits)
+        return planes
+
+    weights = {}
+    for q in WBITS:
+        for (N, K) in SHAPES:
+            copies = []
+            for c in range(WEIGHT_COPIES):
+                codes = torch.randint(0, 1 << q, (N, K), dtype=torch.int32, device="cuda", generator=gen)
+                planes = pack(codes, q)
+                ws = (torch.rand((N, K // GROUP), device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16)
+                wz = torch.randint(0, 1 << q, (N, K // GROUP), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8)
+                copies.append((planes, ws, wz))
+            weights[(q, N, K)] = copies
+    acts = {}
+    for M in MS:
+        for K in sorted({k for _, k in SHAPES}):
+            x = torch.clamp(torch.round(torch.randn((M, K), device="cuda", generator=gen) * 30.0), -128, 127).to(torch.int32)
+            dev_x = pack(x, XBITS)
+            host = torch.empty(dev_x.shape, dtype=torch.int32).pin_memory()
+            host.copy_(dev_x)
+            acts[(M, K)] = (host, dev_x)
+    torch.cuda.synchronize()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gemms = []
+    for M in MS:
+        for q in WBITS:
+            for (N, K) in SHAPES:
+                ws_bytes = abq.gemm_workspace_bytes(M, N, K, XBITS, q)
+                for c in range(WEIGHT_COPIES):
+                    planes, wsc, wz = weights[(q, N, K)][c]
+                    out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+                    out_host = torch.empty((M, N), dtype=torch.float16).pin_memory()
+                    work = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+                    host_x, dev_x = acts[(M, K)]
+                    stage_x = torch.empty_like(dev_x)  # e2e: destination of the per-step host->device copy
+                    states = {}
+                    for name, xbuf in (("resident", dev_x), ("e2e", stage_x)):
+                        p = B.make_params(M, N, K, xbuf, planes, out, x_bits=XBITS, w_bits=q, x_signed=True, w_signed=False,
+                                          out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP, group_size=GROUP, w_scale=wsc, w_zero=wz,
+                                          flags=abq.FLAG_PDL if os.environ.get("ABQ_BENCH_PDL", "1") == "1" else 0, workspace=work,
+                                          status_word=status)
+                        states[name] = abq.gemm_init(p)
+                    gemms.append(dict(M=M, N=N, K=K, q=q, copy=c, states=states, out=out, out_host=out_host, host_x=host_x, stage_x=stage_x,
+                                      keep=(planes, wsc, wz, work, dev_x), bytes=algorithmic_bytes(M, N, K, XBITS, q), ops=2 * M * N * K))
+    return gemms, status
+
+
+def one_pass(abq, gemms, copy, mode):
+    """One pass over the 36 GEMMs (weight copy `copy`).  mode 'resident': operands already in HBM;
+    mode 'e2e': activation planes come from pinned host memory and the result goes back to the host."""
+    for g in gemms:
+        if g["copy"] != copy:
+            continue
+        if mode == "e2e":
+            g["stage_x"].copy_(g["host_x"], non_blocking=True)
+            abq.gemm_exec(g["states"]["e2e"])
+            g["out_host"].copy_(g["out"], non_blocking=True)
+        else:
+            abq.gemm_exec(g["states"]["resident"])
+
+
+def capture_passes(torch, abq, gemms, mode):
+    """One CUDA graph per weight copy holding a whole pass (72 kernels, plus the copies in e2e mode), so that the
+    timed region measures the device and not the Python launch loop.  Returns a callable step(i)."""
+    side = torch.cuda.Stream()
+    graphs = []
+    with torch.cuda.stream(side):
+        for c in range(WEIGHT_COPIES):
+            one_pass(abq, gemms, c, mode)  # first launches outside capture: kernel attributes get set here
+        side.synchronize()
+        for c in range(WEIGHT_COPIES):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                one_pass(abq, gemms, c, mode)
+            graphs.append(g)
+    torch.cuda.synchronize()
+    return lambda i: graphs[i % WEIGHT_COPIES].replay()
+
+
+def timed(torch, dist, fn, steps, warmup):
+    """W warm-up calls, then K timed calls between device events, barrier + synchronize on both sides; max over ranks."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, wall_ms
+
+
+def per_config_detail(torch, abq, gemms, reps=20):
+    """Device time of every (WxAy, M, shape) GEMM alone, alternating the weight copies: TOPS and GB/s per config."""
+    rows = []
+    by_key = {}
+    for g in gemms:
+        by_key.setdefault((g["q"], g["M"], g["N"], g["K"]), []).append(g)
+    for (q, M, N, K), gs in sorted(by_key.items()):
+        for i in range(4):
+            abq.gemm_exec(gs[i % len(gs)]["states"]["resident"])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            abq.gemm_exec(gs[i % len(gs)]["states"]["resident"])
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        rows.append({"wxay": f"W{q}A{XBITS}", "M": M, "N": N, "K": K, "us": round(us, 3), "GBps": round(gs[0]["bytes"] / us / 1e3, 1),
+                     "TOPS": round(gs[0]["ops"] / us / 1e6, 3)})
+    return rows
+
+
+def cpu_baseline_sample(kind_pref: str, budget_s: float = 12.0):
+    """The reference's CPU loop (`compute_ref`) on a bounded sample of the sweep: its W2A8, M=16, N=4096,
+    K=4096 GEMM, repeated until about `budget_s` seconds of host time are spent; all host cores."""
+    from oracle import oracle as O
+    O.build()
+    use_ref = O.ref_available() and kind_pref != "port"
+    M, N, K, q, p = 16, 4096, 4096, 2, XBITS
+    rng = np.random.default_rng(1)
+    cores = os.cpu_count() or 1
+    x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+    xp = O.pack(x, p)
+    rows = (N + cores - 1) // cores
+    slabs = [O.pack(rng.integers(0, 1 << q, size=(rows, K), dtype=np.int32), q) for _ in range(cores)]
+    whole = np.concatenate(slabs, axis=1)
+
+    def run():
+        def work(i):
+            O.ref_compute_ref(slabs[i], xp, True)
+
+        t0 = time.perf_counter()
+        if use_ref:  # the reference loop is single-threaded: one slab of weight rows per core
+            threads = [threading.Thread(target=work, args=(i,)) for i in range(cores)]
+            for th in threads:
+                th.start()
+            for th in threads:
+                th.join()
+        else:        # the C restatement splits the output range over pthreads itself
+            O.set_threads(cores)
+            O.compute_ref(whole, xp, True, True)
+        return time.perf_counter() - t0
+
+    first = run()
+    reps = int(max(1, min(64, budget_s / max(first, 1e-3))))
+    t = sum(run() for _ in range(reps))
+    n_rows = rows * cores
+    nbytes = algorithmic_bytes(M, n_rows, K, p, q) * reps
+    return {"value": nbytes / t / 1e9, "unit": "GB/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "sample": f"W2A8 M=16 N={n_rows} K=4096 (signed planes, as the reference's driver runs it), compute_ref x{reps} "
+                      f"in {t:.2f} s = {2 * M * n_rows * K * reps / t / 1e12:.6f} effective TOPS",
+            "seconds": t}
+
+
+def run_reference(args, rank, world):
+    """`--impl reference`: the reference's own CPU implementation of the path on the host cores."""
+    if rank != 0:
+        return
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    per = max(1.0, min(10.0, 60.0 / (steps + warm)))
+    vals = []
+    base = None
+    for i in range(warm + steps):
+        base = cpu_baseline_sample("reference", budget_s=per)
+        if i >= warm:
+            vals.append(base)
+    total_t = sum(v["seconds"] for v in vals)
+    value = statistics.mean(v["value"] for v in vals)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+            "ms_per_step": total_t / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
+            "data": "synthetic", "config": {"workload": "decode sweep W{2,3,4}A8 x M{1,4,16} x 4 LLaMA-7B shapes; each step a bounded "
+                                                        "sample of its first GEMM on the host cores"},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    line["cpu_baseline"]["value"] = value
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--detail", action="store_true", help="also time every GEMM of the sweep alone")
+    ap.add_argument("--only", default="", help="profiling aid: restrict the sweep to GEMMs 'q:M:N:K[,q:M:N:K...]' (0 = any)")
+    ap.add_argument("--no-graph", action="store_true", help="profiling aid: launch kernel by kernel instead of one CUDA graph per pass")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling aid: skip the host-side reference timing")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    args.warmup = max(3, args.warmup)
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    abq = load_package()
+    gemms, status = build_workload(abq, torch, seed=20241 + rank)
+    if args.only:
+        pats = [tuple(int(v) for v in item.split(":")) for item in args.only.split(",")]
+        gemms = [g for g in gemms if any(all(a == 0 or a == b for a, b in zip(pat, (g["q"], g["M"], g["N"], g["K"]))) for pat in pats)]
+    n_gemm = len(gemms) // WEIGHT_COPIES
+    bytes_per_step = sum(g["bytes"] for g in gemms if g["copy"] == 0)
+    ops_per_step = sum(g["ops"] for g in gemms if g["copy"] == 0)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    use_graph = not args.no_graph
+    step_res = capture_passes(torch, abq, gemms, "resident") if use_graph else (lambda i: one_pass(abq, gemms, i % WEIGHT_COPIES, "resident"))
+    step_e2e = capture_passes(torch, abq, gemms, "e2e") if use_graph else (lambda i: one_pass(abq, gemms, i % WEIGHT_COPIES, "e2e"))
+    ms, wall_ms = timed(torch, dist, step_res, args.steps, args.warmup)
+    clocks = sampler.stop()
+    ms_e2e, _ = timed(torch, dist, step_e2e, args.steps, args.warmup)
+    if int(status.item()) != 0:
+        raise SystemExit(f"device status word {int(status.item())}: a bounded wait expired, the numbers are void")
+
+    value = world * bytes_per_step * args.steps / (ms * 1e-3) / 1e9
+    e2e = world * bytes_per_step * args.steps / (ms_e2e * 1e-3) / 1e9
+    h2d = sum(g["host_x"].numel() * 4 for g in gemms if g["copy"] == 0)
+    d2h = sum(g["out"].numel() * 2 for g in gemms if g["copy"] == 0)
+    peak, peak_kind = measured_peaks()
+    per_gpu = bytes_per_step * args.steps / (ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": {"workload": "decode sweep (BASELINE configs[1]): W{2,3,4}A8 x M{1,4,16} x (N,K) in "
+                               "{(4096,4096),(12288,4096),(11008,4096),(4096,11008)}, g128 fp16 scale + u8 zero, fp16 out; "
+                               f"{n_gemm} GEMMs per step" + (f" (restricted by --only {args.only})" if args.only else ""),
+                   "l2": f"two alternating copies of every weight, {bytes_per_step / 1e6:.0f} MB of distinct operands between reuses (> 126 MB L2)",
+                   "replicas": world, "pdl": os.environ.get("ABQ_BENCH_PDL", "1") == "1", "cuda_graph_per_pass": use_graph},
+        "effective_TOPS": world * ops_per_step * args.steps / (ms * 1e-3) / 1e12,
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 2 * n_gemm * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "decode_kernel (36 launches per step, all shapes)", "achieved": per_gpu, "peak": peak,
+                     "unit": "GB/s", "frac": per_gpu / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
+                     "traffic": None},
+        "wall_ms_per_step": wall_ms / args.steps,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        base = cpu_baseline_sample("reference")
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if args.detail and rank == 0:
+        line["detail"] = per_config_detail(torch, abq, gemms)
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
