@@ -138,7 +138,7 @@ size_t abq_gemm_workspace_bytes(int M, int N, int K, int x_bits, int w_bits, int
     (void)w_bits;
     size_t need = 0;
     if ((route == ABQ_ROUTE_AUTO || route == ABQ_ROUTE_I8_MMA) && M <= 16)
-        need = decode_workspace_bytes(M, K);
+        need = decode_workspace_bytes(M, N, K);
     if (route == ABQ_ROUTE_I8_UMMA || (route == ABQ_ROUTE_AUTO && M > 16)) {
         size_t u = umma_workspace_bytes(M, N, K);
         need = u > need ? u : need;

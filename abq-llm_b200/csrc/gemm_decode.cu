@@ -1,15 +1,22 @@
 // Decode-shape GEMM (M <= 16), route ABQ_ROUTE_I8_MMA.
 //
-// HBM-bound: the weight bit-planes are streamed exactly once.  Per CTA a producer warp drives a ring
-// of TMA stages (one 3-D box = all q planes x 64 weight rows x 1024 input features, 128-byte rows,
-// 128B-swizzled); four consumer warps each own 16 weight rows.  A consumer thread takes one 32-bit word
-// per plane and row, recombines the q plane words into eight registers of unsigned byte codes
-// (planes_to_bytes) and feeds them as the A operand of mma.sync.m16n8k32 (u8 x s8/u8 -> s32); the B
-// operand (up to 8 tokens per MMA) comes from activation records prepared once per GEMM by
-// xprep_decode, whose byte order matches the expansion.  The input-feature range is split over the
-// CTAs of a thread-block cluster (split-K); partial sums are reduced through distributed shared
-// memory in rank order, so the result does not depend on scheduling.  Scale / zero-point
-// dequantisation is fused: per scale group the int32 accumulators are folded into fp32.
+// HBM-bound: every weight plane word is read exactly once, and the kernel is organised so that the
+// SM never waits for a CTA-wide event while planes are in flight.
+//
+//  * Work unit = 16 weight rows x one K-slice.  The grid is persistent (one or two CTAs per SM); CTA i
+//    owns a contiguous range of units, and each of its eight warps walks that range with stride 8.
+//  * Every warp feeds itself: lane 0 issues 3-D TMA boxes (all q planes x 16 rows x 512 input features,
+//    64-byte rows, 64B-swizzled) into a warp-private ring and refills a slot right after the warp has
+//    consumed it, across unit boundaries, so the stream never drains before the kernel ends.
+//  * A thread takes one 32-bit word per plane and row and recombines the q plane words into byte codes
+//    with a butterfly (expand.cuh); the bytes are the A operand of mma.sync.m16n8k32 (u8 x s8/u8 -> s32).
+//    Two accumulator sets carry different power-of-two scales, which saves the shifts that would
+//    otherwise normalise the bit fields.
+//  * The B operand (tokens) comes from activation records prepared once per GEMM (xprep.cu).
+//  * Scale / zero-point dequantisation is fused: per scale group the int32 accumulators are folded into
+//    fp32; scales and zero points are fetched one stage ahead and handed round by shuffles.
+//  * Split-K partials go to a workspace slot per slice; the warp that arrives last at a tile's counter
+//    adds the slots in slice order (deterministic) and writes the output.
 //
 // Covers what the reference does with plane-stacked 1-bit MMAs and an smem shift-accumulate epilogue
 // (engine/mma_any/aq_bmma_kernel.h:109-271, 485-580) and with its fp16 scalar-scale epilogue
@@ -19,20 +26,26 @@
 
 #include "abq_common.cuh"
 #include "abq_kernels.h"
+#include "expand.cuh"
 
 namespace abq {
 
-constexpr int kConsumerWarps = kDecodeBN / 16;
-constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxStages = 8;
-constexpr int kScaleStageWords = 2 * 2 * 16 * 8; // per consumer warp: two buffers of 16 rows x 8 groups, scales and zero points
+constexpr int kDecWarps = 8;
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr int kMaxRing = 6;
 
 struct DecodeArgs {
     int M, N, K;
-    int chunks_per_cta;  // pipeline chunks (1024 features each) per CTA; blockIdx.y selects the slice
-    int stages;
-    int rec_smem_bytes;  // shared memory reserved for the activation records of one slice
+    int tiles;            // ceil(N / 16)
+    int total_groups;     // K / 128
+    int stages_per_slice; // 512-feature stages per K-slice
+    int slices;           // split-K factor
+    int units;            // slices * tiles, unit = slice * tiles + tile
+    int ring;             // TMA stages per warp
+    int rec_region_bytes; // shared memory per activation-record region (one slice)
     const uint8_t *records;
+    int *counters;        // one per tile, zeroed by xprep_decode
+    int *partials;        // [slice][tile][token][16 rows] int32 or fp32 bit patterns
     void *D;
     const __half *w_scale;
     const uint8_t *w_zero;
@@ -45,132 +58,153 @@ struct DecodeArgs {
     int *status;
 };
 
-template <int Q, int MT, bool XU8>
-__global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const DecodeArgs a)
+template <int Q, int MT, bool XU8, bool GROUPED>
+__global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const DecodeArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    constexpr int kStageBytes = Q * kDecodeBN * 128;
+    constexpr int kStageBytes = Q * 1024; // [plane][16 rows][64 B]
     constexpr int kRec = decode_record_bytes(MT);
-    // carve-up: [stages][records][reduce buffer][barriers]
+    using X = Expand<Q>;
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *stage_base = smem;
-    uint8_t *rec_base = stage_base + (size_t)a.stages * kStageBytes;
-    int *red = reinterpret_cast<int *>(rec_base + a.rec_smem_bytes);
-    float *scale_stage = reinterpret_cast<float *>(red + kDecodeBN * 8 * MT); // [warp][buffer][16 rows][8 groups] scale, then zero
-    uint64_t *bars = reinterpret_cast<uint64_t *>(scale_stage + kConsumerWarps * kScaleStageWords);
-    uint64_t *full = bars, *empty = bars + kMaxStages, *xbar = bars + 2 * kMaxStages;
+    uint8_t *ring_base = smem;
+    uint8_t *rec_base = ring_base + (size_t)kDecWarps * a.ring * kStageBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(rec_base + 2 * (size_t)a.rec_region_bytes);
+    uint64_t *full = bars;                          // [warp][slot]
+    uint64_t *recbar = bars + kDecWarps * kMaxRing; // [2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kDecodeBN;
-    const int total_groups = a.K >> 7;
-    const int g_begin = blockIdx.y * a.chunks_per_cta * 8;                          // first 128-group of this slice
-    const int g_count = max(0, min(total_groups - g_begin, a.chunks_per_cta * 8));   // groups in this slice
-    const int n_chunks = (g_count + 7) >> 3;
+    const int g = lane >> 2, t = lane & 3;
+    const int u0 = (int)((long long)blockIdx.x * a.units / gridDim.x);
+    const int u1 = (int)((long long)(blockIdx.x + 1) * a.units / gridDim.x);
+    const int total_stages = (a.total_groups + 3) >> 2;
+    const int slice_a = u0 / a.tiles; // slice held in record region 0; region 1 holds slice_a + 1
+    auto slice_stages = [&](int s) { return max(0, min(total_stages - s * a.stages_per_slice, a.stages_per_slice)); };
+    auto slice_groups = [&](int s) { return max(0, min(a.total_groups - s * a.stages_per_slice * 4, a.stages_per_slice * 4)); };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < a.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kConsumerWarps);
-        }
-        mbar_init(xbar, 1);
+        for (int i = 0; i < kDecWarps * a.ring; ++i)
+            mbar_init(&full[(i / a.ring) * kMaxRing + i % a.ring], 1);
+        mbar_init(&recbar[0], 1);
+        mbar_init(&recbar[1], 1);
         fence_mbar_init();
     }
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == kConsumerWarps) {
-        // ---------------- producer warp: weights first (they never depend on an earlier kernel)
-        if (lane == 0) {
+    // ---- issue side (lane 0 of every warp): cursor over (unit, stage) in the order the warp consumes them
+    int iu = u0 + warp, ij = 0; // next stage to request
+    uint8_t *my_ring = ring_base + (size_t)warp * a.ring * kStageBytes;
+    uint64_t *my_full = full + warp * kMaxRing;
+    auto skip_empty = [&]() {
+        while (iu < u1 && slice_stages(iu / a.tiles) == 0)
+            iu += kDecWarps;
+    };
+    auto issue = [&](int slot) {
+        const int s = iu / a.tiles, r = iu - s * a.tiles;
+        mbar_arrive_expect_tx(&my_full[slot], kStageBytes);
+        tma_load_3d(my_ring + (size_t)slot * kStageBytes, &tmap_w, (s * a.stages_per_slice + ij) * 16, r * 16, 0, &my_full[slot]);
+        if (++ij == slice_stages(s)) {
+            ij = 0;
+            iu += kDecWarps;
+            skip_empty();
+        }
+    };
+    if (lane == 0) {
+        if (warp == 0)
             prefetch_tmap(&tmap_w);
-            int c = 0;
-            const int prologue = min(n_chunks, a.stages);
-            for (; c < prologue; ++c) {
-                mbar_arrive_expect_tx(&full[c], kStageBytes);
-                tma_load_3d(stage_base + (size_t)c * kStageBytes, &tmap_w, (g_begin + c * 8) * 4, n0, 0, &full[c]);
-            }
-            pdl_wait_prior_grid(); // activation records are written by the kernel launched just before
-            if (g_count > 0) {
-                mbar_arrive_expect_tx(xbar, (uint32_t)(g_count * kRec));
-                bulk_load(rec_base, a.records + (size_t)g_begin * kRec, (uint32_t)(g_count * kRec), xbar);
+        skip_empty();
+        for (int slot = 0; slot < a.ring && iu < u1; ++slot)
+            issue(slot); // weights never depend on an earlier kernel: request them before the dependency wait
+    }
+    if (threadIdx.x == 0) {
+        pdl_wait_prior_grid(); // records, counters and partial slots belong to the kernel launched just before
+        const int last_slice = (u1 - 1) / a.tiles;
+        for (int reg = 0; reg < 2; ++reg) {
+            const int s = slice_a + reg;
+            const int ng = (u1 > u0 && s <= last_slice) ? slice_groups(s) : 0;
+            if (ng > 0) {
+                mbar_arrive_expect_tx(&recbar[reg], (uint32_t)(ng * kRec));
+                bulk_load(rec_base + (size_t)reg * a.rec_region_bytes, a.records + (size_t)s * a.stages_per_slice * 4 * kRec,
+                          (uint32_t)(ng * kRec), &recbar[reg]);
             } else {
-                mbar_arrive(xbar);
-            }
-            for (; c < n_chunks; ++c) {
-                const int s = c % a.stages;
-                const uint32_t parity = ((c / a.stages) - 1) & 1;
-                if (!mbar_wait_bounded(&empty[s], parity, a.status, STATUS_TIMEOUT_PIPE))
-                    break;
-                mbar_arrive_expect_tx(&full[s], kStageBytes);
-                tma_load_3d(stage_base + (size_t)s * kStageBytes, &tmap_w, (g_begin + c * 8) * 4, n0, 0, &full[s]);
+                mbar_arrive(&recbar[reg]);
             }
         }
-        __syncwarp();
-    } else {
-        // ---------------- consumer warps
-        const int g = lane >> 2, t = lane & 3;
-        const int row_a = warp * 16 + g; // tile-local weight rows of this thread: row_a and row_a + 8
-        const bool grouped = a.scale_mode == ABQ_SCALE_GROUP;
-        const int zoff = a.w_signed ? (1 << (Q - 1)) : 0;
-        int acc[MT][4];
+    }
+    __syncwarp();
+
+    const uint32_t flip = a.w_signed ? 0xffffffffu : 0u;
+    const int zoff = a.w_signed ? (1 << (Q - 1)) : 0;
+    const uint32_t swz = (uint32_t)((g >> 1) & 3); // 64B swizzle: 16-byte chunk index ^= (row >> 1) & 3
+    int q_comp = 0;                                 // stages consumed so far by this warp (slot = q % ring)
+    bool ok = true;
+
+    for (int u = u0 + warp; u < u1; u += kDecWarps) {
+        const int s = u / a.tiles, r = u - s * a.tiles;
+        const int n0 = r * 16;
+        const int nst = slice_stages(s);
+        const int g_first = s * a.stages_per_slice * 4; // first 128-group of the slice
+        const uint8_t *recs = rec_base + (size_t)(s - slice_a) * a.rec_region_bytes;
+
+        int acc[X::kSets][MT][4];
         float facc[MT][4];
         int xs[MT][2];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                acc[mt][e] = 0;
+#pragma unroll
+                for (int k = 0; k < X::kSets; ++k)
+                    acc[k][mt][e] = 0;
                 facc[mt][e] = 0.f;
             }
             xs[mt][0] = xs[mt][1] = 0;
         }
-        // GROUP mode: the scales / zero points of a chunk (16 rows x 8 groups per warp) are fetched one chunk ahead
-        // into registers (lane = row * 2 + half, four groups each) and parked in a warp-private staging buffer, so
-        // that folding a group never waits on global memory.
-        float *sc_stage = scale_stage + warp * kScaleStageWords;
-        int *z_stage = reinterpret_cast<int *>(sc_stage + 2 * 16 * 8);
-        float pre_sc[4];
-        int pre_z[4];
-        auto prefetch_scales = [&](int c) {
-            const int n = n0 + warp * 16 + (lane >> 1);
+
+        // GROUP mode: lane l fetches (scale | zero << 16) of row l / 2 for the two groups (l & 1) * 2 + {0, 1} of a stage,
+        // one stage ahead; fold() gets the value it needs with a shuffle.
+        uint32_t pk_cur[2] = { 0, 0 }, pk_next[2] = { 0, 0 };
+        auto fetch_scales = [&](int j, uint32_t (&pk)[2]) {
+            const int n = n0 + (lane >> 1);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int gl = c * 8 + (lane & 1) * 4 + j;
-                pre_sc[j] = 0.f;
-                pre_z[j] = 0;
-                if (grouped && gl < g_count && n < a.N) {
-                    const size_t idx = (size_t)n * a.scale_groups + (g_begin + gl) / a.groups_per_scale;
-                    pre_sc[j] = __half2float(ld_half(a.w_scale + idx));
+            for (int k = 0; k < 2; ++k) {
+                const int gg = g_first + j * 4 + (lane & 1) * 2 + k;
+                pk[k] = 0;
+                if (gg < a.total_groups && n < a.N) {
+                    const size_t idx = (size_t)n * a.scale_groups + gg / a.groups_per_scale;
+                    uint32_t v = __half_as_ushort(ld_half(a.w_scale + idx));
                     if (a.w_zero)
-                        pre_z[j] = a.w_zero[idx];
+                        v |= (uint32_t)a.w_zero[idx] << 16;
+                    pk[k] = v;
                 }
             }
         };
-        auto park_scales = [&](int c) {
-            float *sdst = sc_stage + (c & 1) * 128 + (lane >> 1) * 8 + (lane & 1) * 4;
-            int *zdst = z_stage + (c & 1) * 128 + (lane >> 1) * 8 + (lane & 1) * 4;
-            *reinterpret_cast<float4 *>(sdst) = make_float4(pre_sc[0], pre_sc[1], pre_sc[2], pre_sc[3]);
-            *reinterpret_cast<int4 *>(zdst) = make_int4(pre_z[0], pre_z[1], pre_z[2], pre_z[3]);
-            __syncwarp();
-        };
-        if (grouped)
-            prefetch_scales(0);
-        bool ok = mbar_wait_bounded(xbar, 0, a.status, STATUS_TIMEOUT_TMA);
-        int pending_gi = -1; // group (within the current chunk) whose scale group still has unfolded accumulators
+        if (GROUPED && nst > 0)
+            fetch_scales(0, pk_next);
+        if (ok)
+            ok = mbar_wait_bounded(&recbar[s - slice_a], 0, a.status, STATUS_TIMEOUT_TMA);
+        bool pending = false; // GROUP mode: accumulators hold an unfinished scale group
+        int pending_gi = 0;
 
-        // One scale group finished: fold the integer accumulators into fp32 (GROUP mode).  `buf`/`gi` select the
-        // staged scale and zero point of the 128-group that closes it.
-        auto fold = [&](int buf, int gi) {
+        // fold the integer accumulators of a finished scale group into fp32; gi = group within the stage
+        auto fold = [&](int gi) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float sc = sc_stage[buf * 128 + (g + 8 * h) * 8 + gi];
-                const int z = zoff + z_stage[buf * 128 + (g + 8 * h) * 8 + gi];
+                const uint32_t pk = __shfl_sync(0xffffffffu, (gi & 1) ? pk_cur[1] : pk_cur[0], 2 * (g + 8 * h) + (gi >> 1));
+                const float sc = __half2float(__ushort_as_half((unsigned short)(pk & 0xffffu))) * (1.0f / (float)(1 << X::kShift));
+                const int zs = (zoff + (int)(pk >> 16)) << X::kShift;
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
-                        const int v = acc[mt][2 * h + j] - z * xs[mt][j];
+                        int v = acc[0][mt][2 * h + j];
+                        if (X::kSets == 2)
+                            v = (v << X::kShift) + acc[X::kSets - 1][mt][2 * h + j];
+                        v -= zs * xs[mt][j];
                         facc[mt][2 * h + j] = fmaf((float)v, sc, facc[mt][2 * h + j]);
-                        acc[mt][2 * h + j] = 0;
+#pragma unroll
+                        for (int k = 0; k < X::kSets; ++k)
+                            acc[k][mt][2 * h + j] = 0;
                     }
                 }
             }
@@ -179,172 +213,283 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const __grid_con
                 xs[mt][0] = xs[mt][1] = 0;
         };
 
-        for (int c = 0; c < n_chunks && ok; ++c) {
-            const int s = c % a.stages;
-            ok = mbar_wait_bounded(&full[s], (c / a.stages) & 1, a.status, STATUS_TIMEOUT_TMA);
+        for (int j = 0; j < nst && ok; ++j) {
+            if (GROUPED) {
+                pk_cur[0] = pk_next[0];
+                pk_cur[1] = pk_next[1];
+                if (j + 1 < nst)
+                    fetch_scales(j + 1, pk_next);
+            }
+            const int slot = q_comp % a.ring;
+            ok = mbar_wait_bounded(&my_full[slot], (q_comp / a.ring) & 1, a.status, STATUS_TIMEOUT_TMA);
             if (!ok)
                 break;
-            const uint8_t *stage = stage_base + (size_t)s * kStageBytes;
-            const int groups_here = min(8, g_count - c * 8);
-            if (grouped) {
-                park_scales(c);
-                if (c + 1 < n_chunks)
-                    prefetch_scales(c + 1);
-            }
-            for (int gi = 0; gi < groups_here; ++gi) {
-                const int gl = c * 8 + gi; // group index inside the slice
-                uint32_t pa[Q], pb[Q];
-                const uint32_t off = (uint32_t)(((gi ^ g) << 4) + (t << 2)); // 128B swizzle: chunk ^= row & 7
+            const uint8_t *stage = my_ring + (size_t)slot * kStageBytes;
+            const int groups_here = min(4, a.total_groups - (g_first + j * 4));
 #pragma unroll
-                for (int b = 0; b < Q; ++b) {
-                    const uint8_t *plane = stage + b * (kDecodeBN * 128);
-                    pa[b] = *reinterpret_cast<const uint32_t *>(plane + row_a * 128 + off);
-                    pb[b] = *reinterpret_cast<const uint32_t *>(plane + (row_a + 8) * 128 + off);
-                }
-                uint32_t ra[8], rb[8];
-                planes_to_bytes<Q>(pa, a.w_signed != 0, ra);
-                planes_to_bytes<Q>(pb, a.w_signed != 0, rb);
-                const uint8_t *rec = rec_base + (size_t)gl * kRec;
+            for (int gi = 0; gi < 4; ++gi) {
+                if (gi < groups_here) {
+                    const uint32_t off = (((uint32_t)gi ^ swz) << 4) + (t << 2);
+                    uint32_t pa[Q], pb[Q];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                    for (int b = 0; b < Q; ++b) {
+                        pa[b] = *reinterpret_cast<const uint32_t *>(stage + b * 1024 + g * 64 + off);
+                        pb[b] = *reinterpret_cast<const uint32_t *>(stage + b * 1024 + (g + 8) * 64 + off);
+                    }
+                    pa[Q - 1] ^= flip;
+                    pb[Q - 1] ^= flip;
+                    uint32_t ra[8], rb[8];
+                    X::run(pa, ra);
+                    X::run(pb, rb);
+                    const uint8_t *rec = recs + (size_t)(j * 4 + gi) * kRec;
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const uint2 bf = *reinterpret_cast<const uint2 *>(rec + ((i * MT + mt) * 32 + lane) * 8);
-                        mma_u8<XU8>(acc[mt], ra[2 * i], rb[2 * i], ra[2 * i + 1], rb[2 * i + 1], bf.x, bf.y);
-                    }
-                }
-                const int *sums = reinterpret_cast<const int *>(rec + 1024 * MT);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const int2 sv = *reinterpret_cast<const int2 *>(sums + 8 * mt + 2 * t);
-                    xs[mt][0] += sv.x;
-                    xs[mt][1] += sv.y;
-                }
-                if (grouped) {
-                    pending_gi = gi;
-                    if ((g_begin + gl + 1) % a.groups_per_scale == 0) {
-                        fold(c & 1, gi);
-                        pending_gi = -1;
+                        for (int ip = 0; ip < 2; ++ip) {
+                            const uint4 bf = *reinterpret_cast<const uint4 *>(rec + ((mt * 2 + ip) * 32 + lane) * 16);
+                            mma_u8<XU8>(acc[X::set_of_step(2 * ip)][mt], ra[4 * ip], rb[4 * ip], ra[4 * ip + 1], rb[4 * ip + 1], bf.x, bf.y);
+                            mma_u8<XU8>(acc[X::set_of_step(2 * ip + 1)][mt], ra[4 * ip + 2], rb[4 * ip + 2], ra[4 * ip + 3], rb[4 * ip + 3], bf.z,
+                                        bf.w);
+                        }
+                    }
+                    const int *sums = reinterpret_cast<const int *>(rec + 1024 * MT);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int2 sv = *reinterpret_cast<const int2 *>(sums + 8 * mt + 2 * t);
+                        xs[mt][0] += sv.x;
+                        xs[mt][1] += sv.y;
+                    }
+                    if (GROUPED) {
+                        pending = true;
+                        pending_gi = gi;
+                        if ((g_first + j * 4 + gi + 1) % a.groups_per_scale == 0) {
+                            fold(gi);
+                            pending = false;
+                        }
                     }
                 }
             }
-            // a scale group that continues into the next chunk (or slice) is folded here with the same scale: the
-            // fold is linear, and the staged values of this chunk are overwritten two chunks from now
-            if (grouped && pending_gi >= 0) {
-                fold(c & 1, pending_gi);
-                pending_gi = -1;
+            // a scale group that continues in the next stage is folded with the scale staged for this one (the fold is
+            // linear); after this point pk_cur is overwritten
+            if (GROUPED && pending) {
+                fold(pending_gi);
+                pending = false;
             }
             __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&empty[s]);
+            if (lane == 0 && iu < u1)
+                issue(slot); // the slot just consumed is free again
+            ++q_comp;
         }
         __syncwarp();
 
-        // partial result of this slice -> reduce buffer, [token][row] so that the reducer reads rows contiguously
+        // ---- unit result: fp32 (GROUP) or exact int32 for rows g, g + 8 and tokens 8 mt + 2 t + {0, 1}
+        int v[MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int row = row_a + 8 * (e >> 1);
-                const int tok = 8 * mt + 2 * t + (e & 1);
-                int v;
-                if (grouped) {
-                    v = __float_as_int(facc[mt][e]);
+                if (GROUPED) {
+                    v[mt][e] = __float_as_int(facc[mt][e]);
                 } else {
                     int z = zoff;
-                    const int n = n0 + row;
+                    const int n = n0 + g + 8 * (e >> 1);
                     if (a.scale_mode == ABQ_SCALE_CHANNEL && a.w_zero && n < a.N)
-                        z += __ldg(a.w_zero + n);
-                    v = acc[mt][e] - z * xs[mt][e & 1];
+                        z += a.w_zero[n];
+                    int x = acc[0][mt][e];
+                    if (X::kSets == 2)
+                        x += acc[X::kSets - 1][mt][e] >> X::kShift; // exact: every term of that set is a multiple of 2^kShift
+                    v[mt][e] = x - z * xs[mt][e & 1];
                 }
-                red[tok * kDecodeBN + row] = v;
+            }
+        }
+
+        bool finish = true;
+        if (a.slices > 1) {
+            int *slot = a.partials + ((size_t)s * a.tiles + r) * (size_t)a.M * 16;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int tok = 8 * mt + 2 * t + (e & 1);
+                    if (tok < a.M)
+                        slot[tok * 16 + g + 8 * (e >> 1)] = v[mt][e];
+                }
+            }
+            __threadfence();
+            __syncwarp();
+            int old = 0;
+            if (lane == 0)
+                old = atomicAdd(a.counters + r, 1);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            finish = old == a.slices - 1;
+            if (finish) {
+                __threadfence();
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int tok = 8 * mt + 2 * t + (e & 1);
+                        int isum = 0;
+                        float fsum = 0.f;
+                        if (tok < a.M) {
+                            for (int sl = 0; sl < a.slices; ++sl) { // fixed order: the result does not depend on who finishes
+                                const int pv = __ldcg(a.partials + ((size_t)sl * a.tiles + r) * (size_t)a.M * 16 + tok * 16 + g + 8 * (e >> 1));
+                                if (GROUPED)
+                                    fsum += __int_as_float(pv);
+                                else
+                                    isum += pv;
+                            }
+                        }
+                        v[mt][e] = GROUPED ? __float_as_int(fsum) : isum;
+                    }
+                }
+            }
+        }
+        if (finish) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int tok = 8 * mt + 2 * t + (e & 1);
+                    const int n = n0 + g + 8 * (e >> 1);
+                    if (tok < a.M && n < a.N) {
+                        const size_t o = (size_t)tok * a.N + n;
+                        if (a.out_dtype == ABQ_OUT_INT32) {
+                            reinterpret_cast<int *>(a.D)[o] = v[mt][e];
+                        } else {
+                            __half h;
+                            if (a.scale_mode == ABQ_SCALE_TENSOR_COMPAT) {
+                                h = __hmul(__int2half_rn(v[mt][e]), ld_half(a.C));
+                            } else {
+                                float f = GROUPED ? __int_as_float(v[mt][e]) : (float)v[mt][e] * __half2float(ld_half(a.w_scale + n));
+                                if (a.x_scale)
+                                    f *= a.x_scale[tok];
+                                h = __float2half_rn(f);
+                            }
+                            reinterpret_cast<__half *>(a.D)[o] = h;
+                        }
+                    }
+                }
             }
         }
     }
 
-    // ---------------- split-K reduction across the cluster, then the fused epilogue
-    const uint32_t nranks = cluster_nctarank();
-    const uint32_t rank = cluster_ctarank();
-    if (nranks > 1)
-        cluster_sync_all();
-    else
-        __syncthreads();
-
-    const int rows_per_rank = kDecodeBN / (int)nranks;
-    const int elems = rows_per_rank * 8 * MT;
-    const bool grouped = a.scale_mode == ABQ_SCALE_GROUP;
-    for (int e = threadIdx.x; e < elems; e += kDecodeThreads) {
-        const int row = (int)rank * rows_per_rank + e % rows_per_rank;
-        const int tok = e / rows_per_rank;
-        const uint32_t local = smem_u32(&red[tok * kDecodeBN + row]);
-        int isum = 0;
-        float fsum = 0.f;
-        for (uint32_t q = 0; q < nranks; ++q) {
-            int v;
-            if (nranks > 1) {
-                asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(map_to_cta(local, q)) : "memory");
-            } else {
-                v = red[tok * kDecodeBN + row];
-            }
-            if (grouped)
-                fsum += __int_as_float(v);
-            else
-                isum += v;
-        }
-        const int n = n0 + row;
-        if (n < a.N && tok < a.M) {
-            const size_t o = (size_t)tok * a.N + n;
-            if (a.out_dtype == ABQ_OUT_INT32) {
-                reinterpret_cast<int *>(a.D)[o] = isum;
-            } else {
-                __half h;
-                if (a.scale_mode == ABQ_SCALE_TENSOR_COMPAT) {
-                    h = __hmul(__int2half_rn(isum), ld_half(a.C));
-                } else {
-                    float v = grouped ? fsum : (float)isum * __half2float(ld_half(a.w_scale + n));
-                    if (a.x_scale)
-                        v *= __ldg(a.x_scale + tok);
-                    h = __float2half_rn(v);
-                }
-                reinterpret_cast<__half *>(a.D)[o] = h;
-            }
-        }
+    // A wait that expired may have left copies in flight: give them one more bounded chance to land before the
+    // shared memory they target is released.
+    if (!ok && lane == 0) {
+        for (int slot = 0; slot < a.ring; ++slot)
+            mbar_wait_bounded(&my_full[slot], 0, nullptr, 0);
     }
-    if (nranks > 1)
-        cluster_sync_all(); // nobody may exit while a peer still reads its reduce buffer
 }
 
 // ------------------------------------------------------------------------------------------- host side
 
-size_t decode_workspace_bytes(int M, int K)
+struct DecodeLayout {
+    int MT, tiles, total_groups, slices, stages_per_slice, units, ring, rec_region, ctas;
+    size_t smem, off_counters, off_partials, bytes;
+};
+
+static int device_sms()
+{
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+        return v;
+    return 148;
+}
+
+// Workspace: [activation records][tile counters][split-K partial slots for up to kDecodeMaxSlices slices]
+static void workspace_layout(int M, int N, int K, size_t *off_counters, size_t *off_partials, size_t *total)
 {
     const int MT = M <= 8 ? 1 : 2;
-    return (size_t)(K / 128) * decode_record_bytes(MT);
+    const size_t rec = (size_t)(K / 128) * decode_record_bytes(MT);
+    const int tiles = (N + 15) / 16;
+    *off_counters = (rec + 255) & ~(size_t)255;
+    *off_partials = (*off_counters + (size_t)tiles * 4 + 255) & ~(size_t)255;
+    *total = *off_partials + (size_t)kDecodeMaxSlices * tiles * M * 16 * 4;
+}
+
+size_t decode_workspace_bytes(int M, int N, int K)
+{
+    size_t a, b, total;
+    workspace_layout(M, N, K, &a, &b, &total);
+    return total;
+}
+
+static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
+{
+    const int Q = p.w_bits;
+    L->MT = p.M <= 8 ? 1 : 2;
+    L->tiles = (p.N + 15) / 16;
+    L->total_groups = p.K / 128;
+    const int total_stages = (L->total_groups + 3) / 4;
+    const int sms = device_sms();
+    const int stage_bytes = Q * 1024;
+    const int rec = decode_record_bytes(L->MT);
+    // Split K until every warp of two CTAs per SM has about one unit, but keep slices of at least two stages and
+    // keep the partial-slot traffic (slices * M * N * 8 bytes through L2) well below the weight bytes.
+    int slices = 1;
+    const long long weight_bytes = (long long)Q * p.N * p.K / 8;
+    while (slices < kDecodeMaxSlices && (long long)L->tiles * slices < 2LL * sms * kDecWarps && total_stages >= slices * 4 &&
+           (long long)(slices * 2) * p.M * p.N * 8 * 4 <= weight_bytes)
+        slices *= 2;
+    slices = env_int("ABQ_DECODE_SLICES", slices);
+    if (slices < 1 || slices > kDecodeMaxSlices)
+        return false;
+    L->slices = slices;
+    L->stages_per_slice = (total_stages + slices - 1) / slices;
+    L->units = slices * L->tiles;
+    L->rec_region = L->stages_per_slice * 4 * rec;
+    const size_t fixed = 1024 + 2 * (size_t)L->rec_region + (kDecWarps * kMaxRing + 2) * 8;
+    // two CTAs per SM when their rings fit in half of the shared memory, else one
+    int per_sm = env_int("ABQ_DECODE_CTAS_PER_SM", 2);
+    int ring = 0;
+    for (; per_sm >= 1; --per_sm) {
+        const size_t budget = (size_t)(per_sm == 2 ? 113 : 226) * 1024;
+        if (fixed >= budget)
+            continue;
+        ring = (int)((budget - fixed) / ((size_t)kDecWarps * stage_bytes));
+        if (ring >= 2)
+            break;
+    }
+    if (ring < 2)
+        return false;
+    ring = ring > kMaxRing ? kMaxRing : ring;
+    ring = env_int("ABQ_DECODE_RING", ring);
+    if (ring < 1 || ring > kMaxRing)
+        return false;
+    L->ring = ring;
+    L->smem = fixed + (size_t)kDecWarps * ring * stage_bytes;
+    if (L->smem > 227 * 1024)
+        return false;
+    int ctas = sms * per_sm;
+    if (ctas > L->units)
+        ctas = L->units;
+    if (ctas < slices)
+        ctas = slices; // a CTA's unit range may then span at most two slices (two record regions)
+    L->ctas = ctas;
+    workspace_layout(p.M, p.N, p.K, &L->off_counters, &L->off_partials, &L->bytes);
+    return true;
 }
 
 template <int Q, int MT, bool XU8>
 static cudaError_t launch_variant(const abq_gemm_state *st, const DecodeArgs &args, cudaStream_t stream)
 {
-    auto kern = decode_kernel<Q, MT, XU8>;
-    static thread_local size_t configured = 0; // per instantiation and thread: largest size already opted in
-    if (st->shared_mem_size > configured) {
+    const bool grouped = args.scale_mode == ABQ_SCALE_GROUP;
+    auto kern = grouped ? decode_kernel<Q, MT, XU8, true> : decode_kernel<Q, MT, XU8, false>;
+    static thread_local size_t configured[2] = { 0, 0 }; // per instantiation and thread: largest size already opted in
+    if (st->shared_mem_size > configured[grouped]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->shared_mem_size);
         if (e != cudaSuccess)
             return e;
-        configured = st->shared_mem_size;
+        configured[grouped] = st->shared_mem_size;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(st->grid[0], st->grid[1], 1);
-    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.gridDim = dim3(st->grid[0], 1, 1);
+    cfg.blockDim = dim3(kDecThreads);
     cfg.dynamicSmemBytes = st->shared_mem_size;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     int na = 0;
-    attr[na].id = cudaLaunchAttributeClusterDimension;
-    attr[na].val.clusterDim.x = 1;
-    attr[na].val.clusterDim.y = st->cluster;
-    attr[na].val.clusterDim.z = 1;
-    ++na;
     if (st->p.flags & ABQ_FLAG_PDL) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
@@ -372,60 +517,29 @@ abq_status decode_plan(abq_gemm_state *st)
         return ABQ_ERR_UNSUPPORTED;
     if (p.scale_mode == ABQ_SCALE_GROUP && (p.group_size % 128 != 0))
         return ABQ_ERR_UNSUPPORTED;
-    const int MT = p.M <= 8 ? 1 : 2;
-    const int Q = p.w_bits;
-    const int n_tiles = (p.N + kDecodeBN - 1) / kDecodeBN;
-    const int chunks_total = (p.K + kDecodeChunkK - 1) / kDecodeChunkK;
-    int sms = 148;
-    {
-        int dev = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess) {
-            int v = 0;
-            if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
-                sms = v;
-        }
-    }
-    // split-K factor: enough CTAs for two per SM, as long as every slice keeps at least one chunk
-    int split = 1;
-    while (split < 8 && n_tiles * split < 2 * sms && chunks_total >= split * 2)
-        split *= 2;
-    split = env_int("ABQ_DECODE_SPLITK", split);
-    if (split < 1 || split > 8 || (split & (split - 1)) || kDecodeBN % split)
-        return ABQ_ERR_INVALID_ARG;
-    const int chunks_per_cta = (chunks_total + split - 1) / split;
-    const int stage_bytes = Q * kDecodeBN * 128;
-    int stages = chunks_per_cta < 4 ? chunks_per_cta : 4;
-    while (stages > 1 && stages * stage_bytes > 96 * 1024)
-        --stages;
-    stages = env_int("ABQ_DECODE_STAGES", stages);
-    if (stages < 1 || stages > kMaxStages)
-        return ABQ_ERR_INVALID_ARG;
-    const int rec_bytes = chunks_per_cta * 8 * decode_record_bytes(MT);
-    const size_t smem = 1024 + (size_t)stages * stage_bytes + rec_bytes + (size_t)kDecodeBN * 8 * MT * 4 +
-                        (size_t)kConsumerWarps * kScaleStageWords * 4 + (2 * kMaxStages + 1) * 8;
-    if (smem > 227 * 1024)
+    DecodeLayout L;
+    if (!make_layout(p, &L))
         return ABQ_ERR_UNSUPPORTED;
-    if (p.workspace_bytes < decode_workspace_bytes(p.M, p.K) || !p.workspace)
+    if (!p.workspace || p.workspace_bytes < L.bytes)
         return ABQ_ERR_WORKSPACE;
 
     const uint64_t KW = (uint64_t)p.K / 32;
-    const uint64_t dims[3] = { KW, (uint64_t)p.N, (uint64_t)Q };
+    const uint64_t dims[3] = { KW, (uint64_t)p.N, (uint64_t)p.w_bits };
     const uint64_t strides[2] = { KW * 4, KW * 4 * (uint64_t)p.N };
-    const uint32_t box[3] = { 32, (uint32_t)kDecodeBN, (uint32_t)Q };
-    if (!encode_tmap(st->tmap[0], TMAP_U32, 3, p.W, dims, strides, box, TMAP_SWIZZLE_128B))
+    const uint32_t box[3] = { 16, 16, (uint32_t)p.w_bits };
+    if (!encode_tmap(st->tmap[0], TMAP_U32, 3, p.W, dims, strides, box, TMAP_SWIZZLE_64B))
         return ABQ_ERR_CUDA;
 
-    st->grid[0] = n_tiles;
-    st->grid[1] = split;
-    st->grid[2] = 1;
-    st->block[0] = kDecodeThreads;
+    st->grid[0] = L.ctas;
+    st->grid[1] = st->grid[2] = 1;
+    st->block[0] = kDecThreads;
     st->block[1] = st->block[2] = 1;
-    st->cluster = split;
-    st->shared_mem_size = smem;
-    st->tile[0] = chunks_per_cta;
-    st->tile[1] = stages;
-    st->tile[2] = rec_bytes;
-    st->tile[3] = MT;
+    st->cluster = L.slices;
+    st->shared_mem_size = L.smem;
+    st->tile[0] = L.stages_per_slice;
+    st->tile[1] = L.ring;
+    st->tile[2] = L.rec_region;
+    st->tile[3] = L.MT;
     return ABQ_OK;
 }
 
@@ -434,17 +548,28 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     const abq_gemm_params &p = st->p;
     const int MT = st->tile[3];
     const bool pdl = (p.flags & ABQ_FLAG_PDL) != 0;
-    cudaError_t e = xprep_decode(reinterpret_cast<const uint32_t *>(p.X), p.workspace, p.M, p.K, p.x_bits, p.x_signed, MT, pdl, stream);
+    size_t off_counters, off_partials, total;
+    workspace_layout(p.M, p.N, p.K, &off_counters, &off_partials, &total);
+    uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
+    const int tiles = (p.N + 15) / 16;
+    cudaError_t e = xprep_decode(reinterpret_cast<const uint32_t *>(p.X), ws, reinterpret_cast<int *>(ws + off_counters), tiles, p.M, p.K,
+                                 p.x_bits, p.x_signed, MT, pdl, stream);
     if (e != cudaSuccess)
         return e;
     DecodeArgs a;
     a.M = p.M;
     a.N = p.N;
     a.K = p.K;
-    a.chunks_per_cta = st->tile[0];
-    a.stages = st->tile[1];
-    a.rec_smem_bytes = st->tile[2];
-    a.records = reinterpret_cast<const uint8_t *>(p.workspace);
+    a.tiles = tiles;
+    a.total_groups = p.K / 128;
+    a.stages_per_slice = st->tile[0];
+    a.slices = st->cluster;
+    a.units = a.slices * tiles;
+    a.ring = st->tile[1];
+    a.rec_region_bytes = st->tile[2];
+    a.records = ws;
+    a.counters = reinterpret_cast<int *>(ws + off_counters);
+    a.partials = reinterpret_cast<int *>(ws + off_partials);
     a.D = p.D;
     a.w_scale = reinterpret_cast<const __half *>(p.w_scale);
     a.w_zero = p.w_zero;

@@ -72,15 +72,16 @@ cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bi
 }
 
 // Decode-route activation records.  For 128-group G (k in [128G, 128G+128)) the record is
-//   [ step i = 0..3 ][ token tile mt ][ lane = 4*g + t ][ 8 bytes ]      (B fragments, 256 B each)
-//   [ int32 code sums of the group for tokens 0..15 ]                    (64 B)
-// The 8 bytes of (i, mt, lane) are the registers b0, b1 of mma.sync.m16n8k32 for token 8*mt + g:
-// b0 byte y = x[token][128G + 32t + 31 - 8y - 2i], b1 byte y = x[token][128G + 32t + 30 - 8y - 2i];
-// the weight side expands its planes into the matching k order (see gemm_decode.cu).
+//   [ token tile mt ][ step pair ip = 0..1 ][ lane = 4*g + t ][ 16 bytes ]   (B fragments, 512 B per pair)
+//   [ int32 code sums of the group for tokens 0..15 ]                        (64 B)
+// The 16 bytes of (mt, ip, lane) are the registers (b0, b1) of MMA step 2 ip and (b0, b1) of step 2 ip + 1 of
+// mma.sync.m16n8k32 for token 8*mt + g, i.e. registers r[4 ip .. 4 ip + 3] where byte y of r[s] is
+// x[token][128 G + 32 t + 31 - 8 y - s]; the weight side expands its planes into the matching k order
+// (expand.cuh, gemm_decode.cu).
 // One thread per (padded token, 32-element run); tokens >= M give zero fragments and zero sums.
 template <int BITS>
 __global__ void __launch_bounds__(128) xprep_decode_kernel(const uint32_t *__restrict__ xplanes, uint8_t *__restrict__ records,
-                                                           int M, int KW, int MT, int x_signed)
+                                                           int *__restrict__ counters, int n_counters, int M, int KW, int MT, int x_signed)
 {
     // Let the GEMM that follows start early (it prefetches weights, then waits for this grid); the
     // records themselves may still be read by the previous GEMM in the stream, so wait before writing.
@@ -89,6 +90,8 @@ __global__ void __launch_bounds__(128) xprep_decode_kernel(const uint32_t *__res
     const int rec_bytes = decode_record_bytes(MT);
     const long idx = (long)blockIdx.x * 128 + threadIdx.x;
     const long total = (long)MT * 8 * KW;
+    for (long i = idx; i < n_counters; i += (long)gridDim.x * 128)
+        counters[i] = 0; // split-K arrival counters of the GEMM that follows
     const int m = (int)(idx / KW), kw = (int)(idx % KW);
     const bool active = idx < total;
     uint32_t r[8];
@@ -128,9 +131,9 @@ __global__ void __launch_bounds__(128) xprep_decode_kernel(const uint32_t *__res
     const int G = kw >> 2, t = kw & 3, mt = m >> 3, g = m & 7;
     uint8_t *rec = records + (long)G * rec_bytes;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint2 *dst = reinterpret_cast<uint2 *>(rec + ((i * MT + mt) * 32 + g * 4 + t) * 8);
-        *dst = make_uint2(r[2 * i], r[2 * i + 1]);
+    for (int ip = 0; ip < 2; ++ip) {
+        uint4 *dst = reinterpret_cast<uint4 *>(rec + ((mt * 2 + ip) * 32 + g * 4 + t) * 16);
+        *dst = make_uint4(r[4 * ip], r[4 * ip + 1], r[4 * ip + 2], r[4 * ip + 3]);
     }
     if (t == 0)
         reinterpret_cast<int *>(rec + 1024 * MT)[m] = sum;
@@ -138,8 +141,8 @@ __global__ void __launch_bounds__(128) xprep_decode_kernel(const uint32_t *__res
         reinterpret_cast<int *>(rec + 1024 * MT)[8 + m] = 0;
 }
 
-cudaError_t xprep_decode(const uint32_t *xplanes, void *records, int M, int K, int bits, int x_signed, int MT, bool pdl,
-                         cudaStream_t stream)
+cudaError_t xprep_decode(const uint32_t *xplanes, void *records, int *counters, int n_counters, int M, int K, int bits, int x_signed,
+                         int MT, bool pdl, cudaStream_t stream)
 {
     const int KW = K / 32;
     const long total = (long)MT * 8 * KW;
@@ -153,7 +156,7 @@ cudaError_t xprep_decode(const uint32_t *xplanes, void *records, int M, int K, i
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     uint8_t *rec = reinterpret_cast<uint8_t *>(records);
-#define CALL(B) cudaLaunchKernelEx(&cfg, xprep_decode_kernel<B>, xplanes, rec, M, KW, MT, x_signed)
+#define CALL(B) cudaLaunchKernelEx(&cfg, xprep_decode_kernel<B>, xplanes, rec, counters, n_counters, M, KW, MT, x_signed)
     switch (bits) {
     case 1: return CALL(1);
     case 2: return CALL(2);
