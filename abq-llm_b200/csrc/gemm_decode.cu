@@ -30,19 +30,17 @@
 
 namespace abq {
 
-constexpr int kDecWarps = 8;
-constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kMaxRing = 6;
+constexpr int kMaxWarps = 16;
 
 struct DecodeArgs {
     int M, N, K;
     int tiles;            // ceil(N / 16)
     int total_groups;     // K / 128
     int stages_per_slice; // 512-feature stages per K-slice
-    int slices;           // split-K factor
-    int units;            // slices * tiles, unit = slice * tiles + tile
+    int slices;           // split-K factor; the grid is slices * ctas_per_slice
+    int ctas_per_slice;
     int ring;             // TMA stages per warp
-    int rec_region_bytes; // shared memory per activation-record region (one slice)
     const uint8_t *records;
     int *counters;        // one per tile, zeroed by xprep_decode
     int *partials;        // [slice][tile][token][16 rows] int32 or fp32 bit patterns
@@ -58,8 +56,10 @@ struct DecodeArgs {
     int *status;
 };
 
-template <int Q, int MT, bool XU8, bool GROUPED>
-__global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const DecodeArgs a)
+// NW warps per CTA, one CTA per SM.  CTA b works on K-slice b / ctas_per_slice and on an even share of the
+// 16-row tiles; its warps take those tiles with stride NW.
+template <int Q, int MT, bool XU8, bool GROUPED, bool GPS1, int NW>
+__global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const DecodeArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int kStageBytes = Q * 1024; // [plane][16 rows][64 B]
@@ -67,68 +67,57 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_con
     using X = Expand<Q>;
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *ring_base = smem;
-    uint8_t *rec_base = ring_base + (size_t)kDecWarps * a.ring * kStageBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(rec_base + 2 * (size_t)a.rec_region_bytes);
-    uint64_t *full = bars;                          // [warp][slot]
-    uint64_t *recbar = bars + kDecWarps * kMaxRing; // [2]
+    uint8_t *rec_base = ring_base + (size_t)NW * a.ring * kStageBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(rec_base + (size_t)a.stages_per_slice * 4 * kRec);
+    uint64_t *full = bars;                   // [warp][slot]
+    uint64_t *recbar = bars + NW * kMaxRing; // activation records of this CTA's slice
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int u0 = (int)((long long)blockIdx.x * a.units / gridDim.x);
-    const int u1 = (int)((long long)(blockIdx.x + 1) * a.units / gridDim.x);
+    const int s = blockIdx.x / a.ctas_per_slice;      // K-slice of this CTA
+    const int cb = blockIdx.x - s * a.ctas_per_slice; // position among the CTAs of the slice
+    const int r_begin = (int)((long long)cb * a.tiles / a.ctas_per_slice);
+    const int r_end = (int)((long long)(cb + 1) * a.tiles / a.ctas_per_slice);
     const int total_stages = (a.total_groups + 3) >> 2;
-    const int slice_a = u0 / a.tiles; // slice held in record region 0; region 1 holds slice_a + 1
-    auto slice_stages = [&](int s) { return max(0, min(total_stages - s * a.stages_per_slice, a.stages_per_slice)); };
-    auto slice_groups = [&](int s) { return max(0, min(a.total_groups - s * a.stages_per_slice * 4, a.stages_per_slice * 4)); };
+    const int nst = max(0, min(total_stages - s * a.stages_per_slice, a.stages_per_slice)); // stages of this slice
+    const int g_first = s * a.stages_per_slice * 4;                                          // its first 128-group
+    const int n_groups = max(0, min(a.total_groups - g_first, a.stages_per_slice * 4));
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kDecWarps * a.ring; ++i)
-            mbar_init(&full[(i / a.ring) * kMaxRing + i % a.ring], 1);
-        mbar_init(&recbar[0], 1);
-        mbar_init(&recbar[1], 1);
+        for (int w = 0; w < NW; ++w)
+            for (int i = 0; i < a.ring; ++i)
+                mbar_init(&full[w * kMaxRing + i], 1);
+        mbar_init(recbar, 1);
         fence_mbar_init();
     }
     __syncthreads();
     pdl_launch_dependents();
 
-    // ---- issue side (lane 0 of every warp): cursor over (unit, stage) in the order the warp consumes them
-    int iu = u0 + warp, ij = 0; // next stage to request
+    // ---- request side (lane 0 of every warp): cursor over (tile, stage) in the order the warp consumes them
+    int ir = r_begin + warp, ij = 0;
     uint8_t *my_ring = ring_base + (size_t)warp * a.ring * kStageBytes;
     uint64_t *my_full = full + warp * kMaxRing;
-    auto skip_empty = [&]() {
-        while (iu < u1 && slice_stages(iu / a.tiles) == 0)
-            iu += kDecWarps;
-    };
     auto issue = [&](int slot) {
-        const int s = iu / a.tiles, r = iu - s * a.tiles;
         mbar_arrive_expect_tx(&my_full[slot], kStageBytes);
-        tma_load_3d(my_ring + (size_t)slot * kStageBytes, &tmap_w, (s * a.stages_per_slice + ij) * 16, r * 16, 0, &my_full[slot]);
-        if (++ij == slice_stages(s)) {
+        tma_load_3d(my_ring + (size_t)slot * kStageBytes, &tmap_w, (s * a.stages_per_slice + ij) * 16, ir * 16, 0, &my_full[slot]);
+        if (++ij == nst) {
             ij = 0;
-            iu += kDecWarps;
-            skip_empty();
+            ir += NW;
         }
     };
-    if (lane == 0) {
+    if (lane == 0 && nst > 0) {
         if (warp == 0)
             prefetch_tmap(&tmap_w);
-        skip_empty();
-        for (int slot = 0; slot < a.ring && iu < u1; ++slot)
+        for (int slot = 0; slot < a.ring && ir < r_end; ++slot)
             issue(slot); // weights never depend on an earlier kernel: request them before the dependency wait
     }
     if (threadIdx.x == 0) {
         pdl_wait_prior_grid(); // records, counters and partial slots belong to the kernel launched just before
-        const int last_slice = (u1 - 1) / a.tiles;
-        for (int reg = 0; reg < 2; ++reg) {
-            const int s = slice_a + reg;
-            const int ng = (u1 > u0 && s <= last_slice) ? slice_groups(s) : 0;
-            if (ng > 0) {
-                mbar_arrive_expect_tx(&recbar[reg], (uint32_t)(ng * kRec));
-                bulk_load(rec_base + (size_t)reg * a.rec_region_bytes, a.records + (size_t)s * a.stages_per_slice * 4 * kRec,
-                          (uint32_t)(ng * kRec), &recbar[reg]);
-            } else {
-                mbar_arrive(&recbar[reg]);
-            }
+        if (n_groups > 0) {
+            mbar_arrive_expect_tx(recbar, (uint32_t)(n_groups * kRec));
+            bulk_load(rec_base, a.records + (size_t)g_first * kRec, (uint32_t)(n_groups * kRec), recbar);
+        } else {
+            mbar_arrive(recbar);
         }
     }
     __syncwarp();
@@ -136,15 +125,14 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_con
     const uint32_t flip = a.w_signed ? 0xffffffffu : 0u;
     const int zoff = a.w_signed ? (1 << (Q - 1)) : 0;
     const uint32_t swz = (uint32_t)((g >> 1) & 3); // 64B swizzle: 16-byte chunk index ^= (row >> 1) & 3
-    int q_comp = 0;                                 // stages consumed so far by this warp (slot = q % ring)
-    bool ok = true;
+    int slot = 0;                                   // ring slot of the next stage this warp consumes
+    uint32_t phase = 0;                             // parity of that slot's current use
 
-    for (int u = u0 + warp; u < u1; u += kDecWarps) {
-        const int s = u / a.tiles, r = u - s * a.tiles;
+    bool ok = mbar_wait_bounded(recbar, 0, a.status, STATUS_TIMEOUT_TMA);
+    const uint8_t *recs = rec_base;
+
+    for (int r = r_begin + warp; r < r_end; r += NW) {
         const int n0 = r * 16;
-        const int nst = slice_stages(s);
-        const int g_first = s * a.stages_per_slice * 4; // first 128-group of the slice
-        const uint8_t *recs = rec_base + (size_t)(s - slice_a) * a.rec_region_bytes;
 
         int acc[X::kSets][MT][4];
         float facc[MT][4];
@@ -161,47 +149,54 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_con
             xs[mt][0] = xs[mt][1] = 0;
         }
 
-        // GROUP mode: lane l fetches (scale | zero << 16) of row l / 2 for the two groups (l & 1) * 2 + {0, 1} of a stage,
-        // one stage ahead; fold() gets the value it needs with a shuffle.
+        // GROUP mode: lane l fetches scale and zero point of row l / 2 for the two groups (l & 1) * 2 + {0, 1} of a stage,
+        // one stage ahead, packed as the fp32 bits of the scale (an fp16 value: its low 13 mantissa bits are zero) with
+        // the zero point in the low byte; fold() gets the value it needs with one shuffle.
         uint32_t pk_cur[2] = { 0, 0 }, pk_next[2] = { 0, 0 };
+        const bool row_ok = n0 + (lane >> 1) < a.N;
+        const size_t row_off = (size_t)(n0 + (lane >> 1)) * a.scale_groups;
         auto fetch_scales = [&](int j, uint32_t (&pk)[2]) {
-            const int n = n0 + (lane >> 1);
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
                 const int gg = g_first + j * 4 + (lane & 1) * 2 + k;
                 pk[k] = 0;
-                if (gg < a.total_groups && n < a.N) {
-                    const size_t idx = (size_t)n * a.scale_groups + gg / a.groups_per_scale;
-                    uint32_t v = __half_as_ushort(ld_half(a.w_scale + idx));
+                if (gg < a.total_groups && row_ok) {
+                    const size_t idx = row_off + (GPS1 ? gg : gg / a.groups_per_scale);
+                    uint32_t v = __float_as_uint(__half2float(ld_half(a.w_scale + idx)));
                     if (a.w_zero)
-                        v |= (uint32_t)a.w_zero[idx] << 16;
+                        v |= (uint32_t)a.w_zero[idx];
                     pk[k] = v;
                 }
             }
         };
         if (GROUPED && nst > 0)
             fetch_scales(0, pk_next);
-        if (ok)
-            ok = mbar_wait_bounded(&recbar[s - slice_a], 0, a.status, STATUS_TIMEOUT_TMA);
         bool pending = false; // GROUP mode: accumulators hold an unfinished scale group
         int pending_gi = 0;
+        int in_group = GPS1 ? 0 : g_first % a.groups_per_scale; // 128-groups already seen of the current scale group
 
-        // fold the integer accumulators of a finished scale group into fp32; gi = group within the stage
+        // fold the integer accumulators of a finished scale group into fp32; gi = group within the stage.
+        // v = acc0 + acc1 / 2^kShift - (zero + offset) * sum(x) is exact; with one scale group per 128 features its
+        // magnitude is below 2^22 for the narrow bit widths, where int -> float is done with the 1.5 * 2^23 trick
+        // (two ALU/FMA operations) instead of a conversion instruction.
+        constexpr long long kBound = 128LL * (XU8 ? 255 : 128) * (((1 << Q) - 1) + ((1 << Q) - 1) + (1 << (Q - 1)));
+        constexpr bool kMagic = GPS1 && kBound < (1LL << 22);
         auto fold = [&](int gi) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint32_t pk = __shfl_sync(0xffffffffu, (gi & 1) ? pk_cur[1] : pk_cur[0], 2 * (g + 8 * h) + (gi >> 1));
-                const float sc = __half2float(__ushort_as_half((unsigned short)(pk & 0xffffu))) * (1.0f / (float)(1 << X::kShift));
-                const int zs = (zoff + (int)(pk >> 16)) << X::kShift;
+                const float sc = __uint_as_float(pk & 0xffffff00u);
+                const int z = zoff + (int)(pk & 0xffu);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         int v = acc[0][mt][2 * h + j];
                         if (X::kSets == 2)
-                            v = (v << X::kShift) + acc[X::kSets - 1][mt][2 * h + j];
-                        v -= zs * xs[mt][j];
-                        facc[mt][2 * h + j] = fmaf((float)v, sc, facc[mt][2 * h + j]);
+                            v += acc[X::kSets - 1][mt][2 * h + j] >> X::kShift;
+                        v -= z * xs[mt][j];
+                        const float fv = kMagic ? __int_as_float(v + 0x4b400000) - 12582912.0f : (float)v;
+                        facc[mt][2 * h + j] = fmaf(fv, sc, facc[mt][2 * h + j]);
 #pragma unroll
                         for (int k = 0; k < X::kSets; ++k)
                             acc[k][mt][2 * h + j] = 0;
@@ -220,8 +215,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_con
                 if (j + 1 < nst)
                     fetch_scales(j + 1, pk_next);
             }
-            const int slot = q_comp % a.ring;
-            ok = mbar_wait_bounded(&my_full[slot], (q_comp / a.ring) & 1, a.status, STATUS_TIMEOUT_TMA);
+            ok = mbar_wait_bounded(&my_full[slot], phase, a.status, STATUS_TIMEOUT_TMA);
             if (!ok)
                 break;
             const uint8_t *stage = my_ring + (size_t)slot * kStageBytes;
@@ -260,25 +254,33 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_con
                         xs[mt][1] += sv.y;
                     }
                     if (GROUPED) {
-                        pending = true;
-                        pending_gi = gi;
-                        if ((g_first + j * 4 + gi + 1) % a.groups_per_scale == 0) {
+                        if (GPS1) {
                             fold(gi);
-                            pending = false;
+                        } else {
+                            pending = true;
+                            pending_gi = gi;
+                            if (++in_group == a.groups_per_scale) {
+                                in_group = 0;
+                                fold(gi);
+                                pending = false;
+                            }
                         }
                     }
                 }
             }
             // a scale group that continues in the next stage is folded with the scale staged for this one (the fold is
             // linear); after this point pk_cur is overwritten
-            if (GROUPED && pending) {
+            if (GROUPED && !GPS1 && pending) {
                 fold(pending_gi);
                 pending = false;
             }
             __syncwarp();
-            if (lane == 0 && iu < u1)
+            if (lane == 0 && ir < r_end)
                 issue(slot); // the slot just consumed is free again
-            ++q_comp;
+            if (++slot == a.ring) {
+                slot = 0;
+                phase ^= 1;
+            }
         }
         __syncwarp();
 
@@ -385,7 +387,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_kernel(const __grid_con
 // ------------------------------------------------------------------------------------------- host side
 
 struct DecodeLayout {
-    int MT, tiles, total_groups, slices, stages_per_slice, units, ring, rec_region, ctas;
+    int MT, NW, tiles, total_groups, slices, stages_per_slice, ctas_per_slice, ring;
     size_t smem, off_counters, off_partials, bytes;
 };
 
@@ -415,6 +417,9 @@ size_t decode_workspace_bytes(int M, int N, int K)
     return total;
 }
 
+// Tile shape of a launch: warps per CTA, split-K factor, ring depth.  One CTA per SM; the split is chosen so that
+// every warp of the machine gets about one 16-row tile of its slice (the kernel is latency-bound per warp, so
+// equal tile counts per warp matter more than long slices).
 static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
 {
     const int Q = p.w_bits;
@@ -425,58 +430,50 @@ static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
     const int sms = device_sms();
     const int stage_bytes = Q * 1024;
     const int rec = decode_record_bytes(L->MT);
-    // Split K until every warp of two CTAs per SM has about one unit, but keep slices of at least two stages and
-    // keep the partial-slot traffic (slices * M * N * 8 bytes through L2) well below the weight bytes.
-    int slices = 1;
-    const long long weight_bytes = (long long)Q * p.N * p.K / 8;
-    while (slices < kDecodeMaxSlices && (long long)L->tiles * slices < 2LL * sms * kDecWarps && total_stages >= slices * 4 &&
-           (long long)(slices * 2) * p.M * p.N * 8 * 4 <= weight_bytes)
-        slices *= 2;
-    slices = env_int("ABQ_DECODE_SLICES", slices);
-    if (slices < 1 || slices > kDecodeMaxSlices)
-        return false;
-    L->slices = slices;
-    L->stages_per_slice = (total_stages + slices - 1) / slices;
-    L->units = slices * L->tiles;
-    L->rec_region = L->stages_per_slice * 4 * rec;
-    const size_t fixed = 1024 + 2 * (size_t)L->rec_region + (kDecWarps * kMaxRing + 2) * 8;
-    // two CTAs per SM when their rings fit in half of the shared memory, else one
-    int per_sm = env_int("ABQ_DECODE_CTAS_PER_SM", 2);
-    int ring = 0;
-    for (; per_sm >= 1; --per_sm) {
-        const size_t budget = (size_t)(per_sm == 2 ? 113 : 226) * 1024;
+    const int want_nw = env_int("ABQ_DECODE_WARPS", 16);
+    for (int nw = want_nw; nw >= 8; nw -= 8) {
+        int slices = (nw * sms + L->tiles / 2) / L->tiles;
+        slices = slices < 1 ? 1 : slices;
+        slices = slices > kDecodeMaxSlices ? kDecodeMaxSlices : slices;
+        slices = slices > total_stages ? total_stages : slices;
+        slices = env_int("ABQ_DECODE_SLICES", slices);
+        if (slices < 1 || slices > kDecodeMaxSlices || slices > total_stages)
+            return false;
+        const int sps = (total_stages + slices - 1) / slices;
+        slices = (total_stages + sps - 1) / sps; // drop slices that would be empty
+        int cps = sms / slices;
+        cps = cps > L->tiles ? L->tiles : cps;
+        cps = cps < 1 ? 1 : cps;
+        const size_t fixed = 1024 + (size_t)sps * 4 * rec + ((size_t)nw * kMaxRing + 1) * 8;
+        const size_t budget = 226 * 1024;
         if (fixed >= budget)
             continue;
-        ring = (int)((budget - fixed) / ((size_t)kDecWarps * stage_bytes));
-        if (ring >= 2)
-            break;
+        int ring = (int)((budget - fixed) / ((size_t)nw * stage_bytes));
+        ring = ring > kMaxRing ? kMaxRing : ring;
+        ring = env_int("ABQ_DECODE_RING", ring);
+        if (ring < 2 && nw > 8)
+            continue;
+        if (ring < 1 || ring > kMaxRing)
+            return false;
+        L->NW = nw;
+        L->slices = slices;
+        L->stages_per_slice = sps;
+        L->ctas_per_slice = cps;
+        L->ring = ring;
+        L->smem = fixed + (size_t)nw * ring * stage_bytes;
+        workspace_layout(p.M, p.N, p.K, &L->off_counters, &L->off_partials, &L->bytes);
+        return L->smem <= 227 * 1024;
     }
-    if (ring < 2)
-        return false;
-    ring = ring > kMaxRing ? kMaxRing : ring;
-    ring = env_int("ABQ_DECODE_RING", ring);
-    if (ring < 1 || ring > kMaxRing)
-        return false;
-    L->ring = ring;
-    L->smem = fixed + (size_t)kDecWarps * ring * stage_bytes;
-    if (L->smem > 227 * 1024)
-        return false;
-    int ctas = sms * per_sm;
-    if (ctas > L->units)
-        ctas = L->units;
-    if (ctas < slices)
-        ctas = slices; // a CTA's unit range may then span at most two slices (two record regions)
-    L->ctas = ctas;
-    workspace_layout(p.M, p.N, p.K, &L->off_counters, &L->off_partials, &L->bytes);
-    return true;
+    return false;
 }
 
-template <int Q, int MT, bool XU8>
+template <int Q, int MT, bool XU8, int NW>
 static cudaError_t launch_variant(const abq_gemm_state *st, const DecodeArgs &args, cudaStream_t stream)
 {
-    const bool grouped = args.scale_mode == ABQ_SCALE_GROUP;
-    auto kern = grouped ? decode_kernel<Q, MT, XU8, true> : decode_kernel<Q, MT, XU8, false>;
-    static thread_local size_t configured[2] = { 0, 0 }; // per instantiation and thread: largest size already opted in
+    const int grouped = args.scale_mode != ABQ_SCALE_GROUP ? 0 : (args.groups_per_scale == 1 ? 1 : 2);
+    auto kern = grouped == 0 ? decode_kernel<Q, MT, XU8, false, true, NW>
+                             : (grouped == 1 ? decode_kernel<Q, MT, XU8, true, true, NW> : decode_kernel<Q, MT, XU8, true, false, NW>);
+    static thread_local size_t configured[3] = { 0, 0, 0 }; // per instantiation and thread: largest size already opted in
     if (st->shared_mem_size > configured[grouped]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->shared_mem_size);
         if (e != cudaSuccess)
@@ -485,7 +482,7 @@ static cudaError_t launch_variant(const abq_gemm_state *st, const DecodeArgs &ar
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(st->grid[0], 1, 1);
-    cfg.blockDim = dim3(kDecThreads);
+    cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = st->shared_mem_size;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -503,11 +500,16 @@ static cudaError_t launch_variant(const abq_gemm_state *st, const DecodeArgs &ar
 }
 
 template <int Q>
-static cudaError_t launch_q(const abq_gemm_state *st, const DecodeArgs &args, int MT, bool xu8, cudaStream_t stream)
+static cudaError_t launch_q(const abq_gemm_state *st, const DecodeArgs &args, int MT, bool xu8, int nw, cudaStream_t stream)
 {
+    if (nw == 16) {
+        if (MT == 1)
+            return xu8 ? launch_variant<Q, 1, true, 16>(st, args, stream) : launch_variant<Q, 1, false, 16>(st, args, stream);
+        return xu8 ? launch_variant<Q, 2, true, 16>(st, args, stream) : launch_variant<Q, 2, false, 16>(st, args, stream);
+    }
     if (MT == 1)
-        return xu8 ? launch_variant<Q, 1, true>(st, args, stream) : launch_variant<Q, 1, false>(st, args, stream);
-    return xu8 ? launch_variant<Q, 2, true>(st, args, stream) : launch_variant<Q, 2, false>(st, args, stream);
+        return xu8 ? launch_variant<Q, 1, true, 8>(st, args, stream) : launch_variant<Q, 1, false, 8>(st, args, stream);
+    return xu8 ? launch_variant<Q, 2, true, 8>(st, args, stream) : launch_variant<Q, 2, false, 8>(st, args, stream);
 }
 
 abq_status decode_plan(abq_gemm_state *st)
@@ -530,15 +532,15 @@ abq_status decode_plan(abq_gemm_state *st)
     if (!encode_tmap(st->tmap[0], TMAP_U32, 3, p.W, dims, strides, box, TMAP_SWIZZLE_64B))
         return ABQ_ERR_CUDA;
 
-    st->grid[0] = L.ctas;
+    st->grid[0] = L.slices * L.ctas_per_slice;
     st->grid[1] = st->grid[2] = 1;
-    st->block[0] = kDecThreads;
+    st->block[0] = L.NW * 32;
     st->block[1] = st->block[2] = 1;
     st->cluster = L.slices;
     st->shared_mem_size = L.smem;
     st->tile[0] = L.stages_per_slice;
     st->tile[1] = L.ring;
-    st->tile[2] = L.rec_region;
+    st->tile[2] = L.ctas_per_slice;
     st->tile[3] = L.MT;
     return ABQ_OK;
 }
@@ -552,8 +554,10 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     workspace_layout(p.M, p.N, p.K, &off_counters, &off_partials, &total);
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
     const int tiles = (p.N + 15) / 16;
-    cudaError_t e = xprep_decode(reinterpret_cast<const uint32_t *>(p.X), ws, reinterpret_cast<int *>(ws + off_counters), tiles, p.M, p.K,
-                                 p.x_bits, p.x_signed, MT, pdl, stream);
+    cudaError_t e = cudaSuccess;
+    if (!env_int("ABQ_EXPERIMENT_SKIP_XPREP", 0))
+        e = xprep_decode(reinterpret_cast<const uint32_t *>(p.X), ws, reinterpret_cast<int *>(ws + off_counters), tiles, p.M, p.K,
+                         p.x_bits, p.x_signed, MT, pdl, stream);
     if (e != cudaSuccess)
         return e;
     DecodeArgs a;
@@ -564,9 +568,8 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.total_groups = p.K / 128;
     a.stages_per_slice = st->tile[0];
     a.slices = st->cluster;
-    a.units = a.slices * tiles;
+    a.ctas_per_slice = st->tile[2];
     a.ring = st->tile[1];
-    a.rec_region_bytes = st->tile[2];
     a.records = ws;
     a.counters = reinterpret_cast<int *>(ws + off_counters);
     a.partials = reinterpret_cast<int *>(ws + off_partials);
@@ -583,14 +586,14 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.status = p.status_word;
     const bool xu8 = !p.x_signed && p.x_bits == 8;
     switch (p.w_bits) {
-    case 1: return launch_q<1>(st, a, MT, xu8, stream);
-    case 2: return launch_q<2>(st, a, MT, xu8, stream);
-    case 3: return launch_q<3>(st, a, MT, xu8, stream);
-    case 4: return launch_q<4>(st, a, MT, xu8, stream);
-    case 5: return launch_q<5>(st, a, MT, xu8, stream);
-    case 6: return launch_q<6>(st, a, MT, xu8, stream);
-    case 7: return launch_q<7>(st, a, MT, xu8, stream);
-    case 8: return launch_q<8>(st, a, MT, xu8, stream);
+    case 1: return launch_q<1>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 2: return launch_q<2>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 3: return launch_q<3>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 4: return launch_q<4>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 5: return launch_q<5>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 6: return launch_q<6>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 7: return launch_q<7>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 8: return launch_q<8>(st, a, MT, xu8, st->block[0] / 32, stream);
     default: return cudaErrorInvalidValue;
     }
 }
