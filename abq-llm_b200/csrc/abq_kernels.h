@@ -18,8 +18,6 @@ cudaError_t quantize_pack_half(const __half *in, const float *scale, uint32_t *p
 cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream);
 // Bytes of one decode-route activation record (one per 128 input features): MT token tiles of 8.
 __host__ __device__ constexpr int decode_record_bytes(int MT) { return 1024 * MT + 64; }
-cudaError_t xprep_decode(const uint32_t *xplanes, void *records, int *counters, int n_counters, int M, int K, int bits, int x_signed,
-                         int MT, bool pdl, cudaStream_t stream);
 
 // ---- gemm_decode.cu (route ABQ_ROUTE_I8_MMA, M <= 16)
 constexpr int kDecodeMaxSlices = 8;  // largest split-K factor (the workspace reserves that many partial slots)

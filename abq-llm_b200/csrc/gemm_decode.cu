@@ -1,26 +1,31 @@
-// Decode-shape GEMM (M <= 16), route ABQ_ROUTE_I8_MMA.
+// Decode-shape GEMM (M <= 16), route ABQ_ROUTE_I8_MMA: one kernel per GEMM.
 //
-// HBM-bound: every weight plane word is read exactly once, and the kernel is organised so that the
-// SM never waits for a CTA-wide event while planes are in flight.
+// HBM-bound and, at LLaMA sizes, only a few microseconds long, so the kernel is built around two things:
+// every weight plane word is read exactly once, and nothing on the path from "activations are ready" to "output
+// is written" goes through global memory more often than it must.
 //
-//  * Work unit = 16 weight rows x one K-slice.  The grid is persistent (one or two CTAs per SM); CTA i
-//    owns a contiguous range of units, and each of its eight warps walks that range with stride 8.
-//  * Every warp feeds itself: lane 0 issues 3-D TMA boxes (all q planes x 16 rows x 512 input features,
-//    64-byte rows, 64B-swizzled) into a warp-private ring and refills a slot right after the warp has
-//    consumed it, across unit boundaries, so the stream never drains before the kernel ends.
-//  * A thread takes one 32-bit word per plane and row and recombines the q plane words into byte codes
-//    with a butterfly (expand.cuh); the bytes are the A operand of mma.sync.m16n8k32 (u8 x s8/u8 -> s32).
-//    Two accumulator sets carry different power-of-two scales, which saves the shifts that would
-//    otherwise normalise the bit fields.
-//  * The B operand (tokens) comes from activation records prepared once per GEMM (xprep.cu).
-//  * Scale / zero-point dequantisation is fused: per scale group the int32 accumulators are folded into
-//    fp32; scales and zero points are fetched one stage ahead and handed round by shuffles.
-//  * Split-K partials go to a workspace slot per slice; the warp that arrives last at a tile's counter
-//    adds the slots in slice order (deterministic) and writes the output.
+//  * One CTA of 16 warps per SM.  CTA c owns an even share of the 16-row weight tiles.  `split` warps share a
+//    tile, each taking a contiguous range of 512-feature stages, so that all 16 warps have work even when a CTA
+//    has only one or two tiles; their partial sums meet in shared memory (mbarrier hand-shake, fixed order).
+//  * Every warp feeds itself: lane 0 issues 3-D TMA boxes (all q planes x 16 rows x 512 input features, 64-byte
+//    rows, 64B-swizzled) into a warp-private ring and refills a slot right after the warp has consumed it, across
+//    tile boundaries.  Weight requests go out before the dependency wait of a programmatic dependent launch:
+//    weights never depend on the previous kernel.
+//  * The activations arrive as bit-planes; after the dependency wait the CTA expands the planes of its K range
+//    once into "records" in shared memory: the B fragments of mma.sync.m16n8k32 in the order the warps read them,
+//    plus per-128-feature code sums (for zero points and offset-coded signed weights).
+//  * A thread takes one 32-bit word per plane and row and recombines the q plane words into byte codes with a
+//    butterfly (expand.cuh); the bytes are the A operand of the MMA (u8 x s8/u8 -> s32).  Two accumulator sets
+//    carry different power-of-two scales, which saves the shifts that would otherwise normalise the bit fields.
+//  * Scale / zero-point dequantisation is fused: per scale group the int32 accumulators are folded into fp32.
+//  * Only when the records of the whole K range do not fit in shared memory is K also split over CTAs; those
+//    partials go through a workspace slot per slice and the CTA arriving last at the tile's counter adds them in
+//    slice order.
 //
 // Covers what the reference does with plane-stacked 1-bit MMAs and an smem shift-accumulate epilogue
-// (engine/mma_any/aq_bmma_kernel.h:109-271, 485-580) and with its fp16 scalar-scale epilogue
-// (fastertransformer/.../abqgemm/mma_any/aq_bmma_kernel.h:474-524).
+// (engine/mma_any/aq_bmma_kernel.h:109-271, 485-580), with its fp16 scalar-scale epilogue
+// (fastertransformer/.../abqgemm/mma_any/aq_bmma_kernel.h:474-524), and with the activation side of the plane
+// stacking (aq_bmma_kernel.h:146-152).
 #include <cuda.h>
 #include <cstring>
 
@@ -35,15 +40,18 @@ constexpr int kMaxWarps = 16;
 
 struct DecodeArgs {
     int M, N, K;
-    int tiles;            // ceil(N / 16)
-    int total_groups;     // K / 128
-    int stages_per_slice; // 512-feature stages per K-slice
-    int slices;           // split-K factor; the grid is slices * ctas_per_slice
+    int tiles;             // ceil(N / 16)
+    int total_groups;      // K / 128
+    int slices;            // K split over CTAs (1 unless the records of all K do not fit in shared memory)
+    int stages_per_slice;  // 512-feature stages per slice
     int ctas_per_slice;
-    int ring;             // TMA stages per warp
-    const uint8_t *records;
-    int *counters;        // one per tile, zeroed by xprep_decode
-    int *partials;        // [slice][tile][token][16 rows] int32 or fp32 bit patterns
+    int split;             // warps sharing one tile
+    int stages_per_split;  // stages per warp of a tile
+    int ring;              // TMA stages per warp
+    const uint32_t *X;     // activation planes [x_bits][M][K/32]
+    int x_bits, x_signed;
+    int *counters;         // one per tile (slices > 1), zero before the launch, left zero after it
+    int *partials;         // [slice][tile][token][16 rows] int32 or fp32 bit patterns (slices > 1)
     void *D;
     const __half *w_scale;
     const uint8_t *w_zero;
@@ -56,8 +64,83 @@ struct DecodeArgs {
     int *status;
 };
 
-// NW warps per CTA, one CTA per SM.  CTA b works on K-slice b / ctas_per_slice and on an even share of the
-// 16-row tiles; its warps take those tiles with stride NW.
+// Bit-planes of 32 activation codes -> eight registers of true byte values (byte y of r[s] = code at bit 8y + s).
+template <int P>
+__device__ __forceinline__ void x_bytes(const uint32_t (&p)[P], bool is_signed, uint32_t (&r)[8])
+{
+    if constexpr (P >= 5 || P == 1) {
+        Expand<P>::run(p, r); // these widths come out of the butterfly as plain byte values
+    } else {
+        uint32_t n[4];
+        if constexpr (P == 2)
+            nibble_fields(p[0], p[1], 0u, 0u, false, n);
+        else if constexpr (P == 3)
+            nibble_fields(p[0], p[1], p[2], 0u, false, n);
+        else
+            nibble_fields(p[0], p[1], p[2], p[3], true, n);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            r[s] = n[s] & 0x0f0f0f0fu;
+            r[4 + s] = (n[s] >> 4) & 0x0f0f0f0fu;
+        }
+    }
+    if (is_signed && P < 8) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            r[s] = sign_extend_bytes(r[s], P);
+    }
+}
+
+// Expand the activation planes of groups [g_first, g_first + n_groups) into records in shared memory.  Record of a
+// 128-feature group: [token tile mt][step pair ip][lane = 4 g + t][16 bytes] B fragments, then 16 int32 code sums.
+// The 16 bytes of (mt, ip, lane) are registers r[4 ip .. 4 ip + 3] of token 8 mt + g and 32-feature run t.
+template <int P, int NW>
+__device__ __forceinline__ void build_records(const DecodeArgs &a, uint8_t *rec_base, int g_first, int n_groups, int MT, int rec_bytes)
+{
+    const int KW = a.K >> 5;
+    const int words = n_groups * 4;
+    const int items = MT * 8 * words;
+    const size_t plane = (size_t)a.M * KW;
+    for (int idx = threadIdx.x; idx < items; idx += NW * 32) {
+        const int m = idx / words, kwl = idx - m * words;
+        uint32_t r[8];
+        int sum = 0;
+        if (m < a.M) {
+            uint32_t p[P];
+            const uint32_t *src = a.X + (size_t)m * KW + g_first * 4 + kwl;
+#pragma unroll
+            for (int b = 0; b < P; ++b)
+                p[b] = __ldg(src + b * plane);
+            x_bytes<P>(p, a.x_signed != 0, r);
+            if (a.x_signed) {
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    sum = __dp4a((int)r[s], 0x01010101, sum);
+            } else {
+                unsigned usum = 0;
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    usum = __dp4a(r[s], 0x01010101u, usum);
+                sum = (int)usum;
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                r[s] = 0;
+        }
+        // the four 32-feature runs of a group sit in four consecutive lanes (words is a multiple of 4)
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int G = kwl >> 2, t = kwl & 3, mt = m >> 3, g = m & 7;
+        uint8_t *rec = rec_base + (size_t)G * rec_bytes;
+        uint4 *dst = reinterpret_cast<uint4 *>(rec + ((mt * 2) * 32 + g * 4 + t) * 16);
+        dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
+        dst[32] = make_uint4(r[4], r[5], r[6], r[7]);
+        if (t == 0)
+            reinterpret_cast<int *>(rec + 1024 * MT)[m] = sum;
+    }
+}
+
 template <int Q, int MT, bool XU8, bool GROUPED, bool GPS1, int NW>
 __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const DecodeArgs a)
 {
@@ -68,9 +151,11 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *ring_base = smem;
     uint8_t *rec_base = ring_base + (size_t)NW * a.ring * kStageBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(rec_base + (size_t)a.stages_per_slice * 4 * kRec);
-    uint64_t *full = bars;                   // [warp][slot]
-    uint64_t *recbar = bars + NW * kMaxRing; // activation records of this CTA's slice
+    int *red = reinterpret_cast<int *>(rec_base + (size_t)a.stages_per_slice * 4 * kRec); // [warp][4 MT][32 lanes]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red + NW * 4 * MT * 32);
+    uint64_t *full = bars;                      // [warp][slot]: TMA stage landed
+    uint64_t *red_ready = bars + NW * kMaxRing; // [tile slot]: partials of the other warps of the tile are written
+    uint64_t *red_free = red_ready + NW;        // [tile slot]: the reducing warp has read them
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -79,296 +164,348 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
     const int r_begin = (int)((long long)cb * a.tiles / a.ctas_per_slice);
     const int r_end = (int)((long long)(cb + 1) * a.tiles / a.ctas_per_slice);
     const int total_stages = (a.total_groups + 3) >> 2;
-    const int nst = max(0, min(total_stages - s * a.stages_per_slice, a.stages_per_slice)); // stages of this slice
-    const int g_first = s * a.stages_per_slice * 4;                                          // its first 128-group
-    const int n_groups = max(0, min(a.total_groups - g_first, a.stages_per_slice * 4));
+    const int slice_first = s * a.stages_per_slice;                                     // first stage of the slice
+    const int slice_nst = max(0, min(total_stages - slice_first, a.stages_per_slice)); // its stage count
+    const int g_slice = slice_first * 4;                                                // its first 128-group
+    const int n_groups = max(0, min(a.total_groups - g_slice, a.stages_per_slice * 4));
 
-    if (threadIdx.x == 0) {
-        for (int w = 0; w < NW; ++w)
-            for (int i = 0; i < a.ring; ++i)
-                mbar_init(&full[w * kMaxRing + i], 1);
-        mbar_init(recbar, 1);
+    // role of this warp: tile slot ts of the round, part sc of that tile's stages
+    const int tiles_per_round = NW / a.split;
+    const int ts = warp / a.split, sc = warp - ts * a.split;
+    const bool active = ts < tiles_per_round;
+    const int st_begin = min(slice_nst, sc * a.stages_per_split); // stages [st_begin, st_end) of the slice
+    const int st_end = min(slice_nst, st_begin + a.stages_per_split);
+    const int my_nst = active ? st_end - st_begin : 0;
+
+    if (lane == 0) { // every warp sets up its own barriers
+        for (int i = 0; i < a.ring; ++i)
+            mbar_init(&full[warp * kMaxRing + i], 1);
+        mbar_init(&red_ready[warp], a.split > 1 ? a.split - 1 : 1);
+        mbar_init(&red_free[warp], 1);
         fence_mbar_init();
     }
     __syncthreads();
     pdl_launch_dependents();
 
     // ---- request side (lane 0 of every warp): cursor over (tile, stage) in the order the warp consumes them
-    int ir = r_begin + warp, ij = 0;
+    int ir = r_begin + ts, ij = 0;
     uint8_t *my_ring = ring_base + (size_t)warp * a.ring * kStageBytes;
     uint64_t *my_full = full + warp * kMaxRing;
     auto issue = [&](int slot) {
         mbar_arrive_expect_tx(&my_full[slot], kStageBytes);
-        tma_load_3d(my_ring + (size_t)slot * kStageBytes, &tmap_w, (s * a.stages_per_slice + ij) * 16, ir * 16, 0, &my_full[slot]);
-        if (++ij == nst) {
+        tma_load_3d(my_ring + (size_t)slot * kStageBytes, &tmap_w, (slice_first + st_begin + ij) * 16, ir * 16, 0, &my_full[slot]);
+        if (++ij == my_nst) {
             ij = 0;
-            ir += NW;
+            ir += tiles_per_round;
         }
     };
-    if (lane == 0 && nst > 0) {
+    if (lane == 0 && my_nst > 0) {
         if (warp == 0)
             prefetch_tmap(&tmap_w);
         for (int slot = 0; slot < a.ring && ir < r_end; ++slot)
             issue(slot); // weights never depend on an earlier kernel: request them before the dependency wait
     }
-    if (threadIdx.x == 0) {
-        pdl_wait_prior_grid(); // records, counters and partial slots belong to the kernel launched just before
-        if (n_groups > 0) {
-            mbar_arrive_expect_tx(recbar, (uint32_t)(n_groups * kRec));
-            bulk_load(rec_base, a.records + (size_t)g_first * kRec, (uint32_t)(n_groups * kRec), recbar);
-        } else {
-            mbar_arrive(recbar);
-        }
+
+    // ---- activations: everything below may depend on the kernel launched just before
+    pdl_wait_prior_grid();
+    switch (a.x_bits) {
+    case 1: build_records<1, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
+    case 2: build_records<2, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
+    case 3: build_records<3, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
+    case 4: build_records<4, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
+    case 5: build_records<5, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
+    case 6: build_records<6, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
+    case 7: build_records<7, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
+    default: build_records<8, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
     }
-    __syncwarp();
+    __syncthreads();
 
     const uint32_t flip = a.w_signed ? 0xffffffffu : 0u;
     const int zoff = a.w_signed ? (1 << (Q - 1)) : 0;
     const uint32_t swz = (uint32_t)((g >> 1) & 3); // 64B swizzle: 16-byte chunk index ^= (row >> 1) & 3
     int slot = 0;                                   // ring slot of the next stage this warp consumes
     uint32_t phase = 0;                             // parity of that slot's current use
+    uint32_t round_parity = 0;
+    bool ok = true;
+    const int g_first = g_slice + st_begin * 4; // first 128-group of this warp's stage range
+    const uint8_t *recs = rec_base + (size_t)st_begin * 4 * kRec;
 
-    bool ok = mbar_wait_bounded(recbar, 0, a.status, STATUS_TIMEOUT_TMA);
-    const uint8_t *recs = rec_base;
+    if (active) {
+        for (int r = r_begin + ts; r < r_end; r += tiles_per_round, round_parity ^= 1) {
+            const int n0 = r * 16;
 
-    for (int r = r_begin + warp; r < r_end; r += NW) {
-        const int n0 = r * 16;
-
-        int acc[X::kSets][MT][4];
-        float facc[MT][4];
-        int xs[MT][2];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-#pragma unroll
-                for (int k = 0; k < X::kSets; ++k)
-                    acc[k][mt][e] = 0;
-                facc[mt][e] = 0.f;
-            }
-            xs[mt][0] = xs[mt][1] = 0;
-        }
-
-        // GROUP mode: lane l fetches scale and zero point of row l / 2 for the two groups (l & 1) * 2 + {0, 1} of a stage,
-        // one stage ahead, packed as the fp32 bits of the scale (an fp16 value: its low 13 mantissa bits are zero) with
-        // the zero point in the low byte; fold() gets the value it needs with one shuffle.
-        uint32_t pk_cur[2] = { 0, 0 }, pk_next[2] = { 0, 0 };
-        const bool row_ok = n0 + (lane >> 1) < a.N;
-        const size_t row_off = (size_t)(n0 + (lane >> 1)) * a.scale_groups;
-        auto fetch_scales = [&](int j, uint32_t (&pk)[2]) {
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const int gg = g_first + j * 4 + (lane & 1) * 2 + k;
-                pk[k] = 0;
-                if (gg < a.total_groups && row_ok) {
-                    const size_t idx = row_off + (GPS1 ? gg : gg / a.groups_per_scale);
-                    uint32_t v = __float_as_uint(__half2float(ld_half(a.w_scale + idx)));
-                    if (a.w_zero)
-                        v |= (uint32_t)a.w_zero[idx];
-                    pk[k] = v;
-                }
-            }
-        };
-        if (GROUPED && nst > 0)
-            fetch_scales(0, pk_next);
-        bool pending = false; // GROUP mode: accumulators hold an unfinished scale group
-        int pending_gi = 0;
-        int in_group = GPS1 ? 0 : g_first % a.groups_per_scale; // 128-groups already seen of the current scale group
-
-        // fold the integer accumulators of a finished scale group into fp32; gi = group within the stage.
-        // v = acc0 + acc1 / 2^kShift - (zero + offset) * sum(x) is exact; with one scale group per 128 features its
-        // magnitude is below 2^22 for the narrow bit widths, where int -> float is done with the 1.5 * 2^23 trick
-        // (two ALU/FMA operations) instead of a conversion instruction.
-        constexpr long long kBound = 128LL * (XU8 ? 255 : 128) * (((1 << Q) - 1) + ((1 << Q) - 1) + (1 << (Q - 1)));
-        constexpr bool kMagic = GPS1 && kBound < (1LL << 22);
-        auto fold = [&](int gi) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t pk = __shfl_sync(0xffffffffu, (gi & 1) ? pk_cur[1] : pk_cur[0], 2 * (g + 8 * h) + (gi >> 1));
-                const float sc = __uint_as_float(pk & 0xffffff00u);
-                const int z = zoff + (int)(pk & 0xffu);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        int v = acc[0][mt][2 * h + j];
-                        if (X::kSets == 2)
-                            v += acc[X::kSets - 1][mt][2 * h + j] >> X::kShift;
-                        v -= z * xs[mt][j];
-                        const float fv = kMagic ? __int_as_float(v + 0x4b400000) - 12582912.0f : (float)v;
-                        facc[mt][2 * h + j] = fmaf(fv, sc, facc[mt][2 * h + j]);
-#pragma unroll
-                        for (int k = 0; k < X::kSets; ++k)
-                            acc[k][mt][2 * h + j] = 0;
-                    }
-                }
-            }
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-                xs[mt][0] = xs[mt][1] = 0;
-        };
-
-        for (int j = 0; j < nst && ok; ++j) {
-            if (GROUPED) {
-                pk_cur[0] = pk_next[0];
-                pk_cur[1] = pk_next[1];
-                if (j + 1 < nst)
-                    fetch_scales(j + 1, pk_next);
-            }
-            ok = mbar_wait_bounded(&my_full[slot], phase, a.status, STATUS_TIMEOUT_TMA);
-            if (!ok)
-                break;
-            const uint8_t *stage = my_ring + (size_t)slot * kStageBytes;
-            const int groups_here = min(4, a.total_groups - (g_first + j * 4));
-#pragma unroll
-            for (int gi = 0; gi < 4; ++gi) {
-                if (gi < groups_here) {
-                    const uint32_t off = (((uint32_t)gi ^ swz) << 4) + (t << 2);
-                    uint32_t pa[Q], pb[Q];
-#pragma unroll
-                    for (int b = 0; b < Q; ++b) {
-                        pa[b] = *reinterpret_cast<const uint32_t *>(stage + b * 1024 + g * 64 + off);
-                        pb[b] = *reinterpret_cast<const uint32_t *>(stage + b * 1024 + (g + 8) * 64 + off);
-                    }
-                    pa[Q - 1] ^= flip;
-                    pb[Q - 1] ^= flip;
-                    uint32_t ra[8], rb[8];
-                    X::run(pa, ra);
-                    X::run(pb, rb);
-                    const uint8_t *rec = recs + (size_t)(j * 4 + gi) * kRec;
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-                        for (int ip = 0; ip < 2; ++ip) {
-                            const uint4 bf = *reinterpret_cast<const uint4 *>(rec + ((mt * 2 + ip) * 32 + lane) * 16);
-                            mma_u8<XU8>(acc[X::set_of_step(2 * ip)][mt], ra[4 * ip], rb[4 * ip], ra[4 * ip + 1], rb[4 * ip + 1], bf.x, bf.y);
-                            mma_u8<XU8>(acc[X::set_of_step(2 * ip + 1)][mt], ra[4 * ip + 2], rb[4 * ip + 2], ra[4 * ip + 3], rb[4 * ip + 3], bf.z,
-                                        bf.w);
-                        }
-                    }
-                    const int *sums = reinterpret_cast<const int *>(rec + 1024 * MT);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const int2 sv = *reinterpret_cast<const int2 *>(sums + 8 * mt + 2 * t);
-                        xs[mt][0] += sv.x;
-                        xs[mt][1] += sv.y;
-                    }
-                    if (GROUPED) {
-                        if (GPS1) {
-                            fold(gi);
-                        } else {
-                            pending = true;
-                            pending_gi = gi;
-                            if (++in_group == a.groups_per_scale) {
-                                in_group = 0;
-                                fold(gi);
-                                pending = false;
-                            }
-                        }
-                    }
-                }
-            }
-            // a scale group that continues in the next stage is folded with the scale staged for this one (the fold is
-            // linear); after this point pk_cur is overwritten
-            if (GROUPED && !GPS1 && pending) {
-                fold(pending_gi);
-                pending = false;
-            }
-            __syncwarp();
-            if (lane == 0 && ir < r_end)
-                issue(slot); // the slot just consumed is free again
-            if (++slot == a.ring) {
-                slot = 0;
-                phase ^= 1;
-            }
-        }
-        __syncwarp();
-
-        // ---- unit result: fp32 (GROUP) or exact int32 for rows g, g + 8 and tokens 8 mt + 2 t + {0, 1}
-        int v[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (GROUPED) {
-                    v[mt][e] = __float_as_int(facc[mt][e]);
-                } else {
-                    int z = zoff;
-                    const int n = n0 + g + 8 * (e >> 1);
-                    if (a.scale_mode == ABQ_SCALE_CHANNEL && a.w_zero && n < a.N)
-                        z += a.w_zero[n];
-                    int x = acc[0][mt][e];
-                    if (X::kSets == 2)
-                        x += acc[X::kSets - 1][mt][e] >> X::kShift; // exact: every term of that set is a multiple of 2^kShift
-                    v[mt][e] = x - z * xs[mt][e & 1];
-                }
-            }
-        }
-
-        bool finish = true;
-        if (a.slices > 1) {
-            int *slot = a.partials + ((size_t)s * a.tiles + r) * (size_t)a.M * 16;
+            int acc[X::kSets][MT][4];
+            float facc[MT][4];
+            int xs[MT][2];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int tok = 8 * mt + 2 * t + (e & 1);
-                    if (tok < a.M)
-                        slot[tok * 16 + g + 8 * (e >> 1)] = v[mt][e];
+#pragma unroll
+                    for (int k = 0; k < X::kSets; ++k)
+                        acc[k][mt][e] = 0;
+                    facc[mt][e] = 0.f;
+                }
+                xs[mt][0] = xs[mt][1] = 0;
+            }
+
+            // GROUP mode: lane l fetches scale and zero point of row l / 2 for the two groups (l & 1) * 2 + {0, 1} of a
+            // stage, one stage ahead, packed as the fp32 bits of the scale (an fp16 value: its low 13 mantissa bits are
+            // zero) with the zero point in the low byte; fold() gets the value it needs with one shuffle.
+            uint32_t pk_cur[2] = { 0, 0 }, pk_next[2] = { 0, 0 };
+            const bool row_ok = n0 + (lane >> 1) < a.N;
+            const size_t row_off = (size_t)(n0 + (lane >> 1)) * a.scale_groups;
+            auto fetch_scales = [&](int j, uint32_t (&pk)[2]) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int gg = g_first + j * 4 + (lane & 1) * 2 + k;
+                    pk[k] = 0;
+                    if (gg < a.total_groups && row_ok) {
+                        const size_t idx = row_off + (GPS1 ? gg : gg / a.groups_per_scale);
+                        uint32_t v = __float_as_uint(__half2float(ld_half(a.w_scale + idx)));
+                        if (a.w_zero)
+                            v |= (uint32_t)a.w_zero[idx];
+                        pk[k] = v;
+                    }
+                }
+            };
+            if (GROUPED && my_nst > 0)
+                fetch_scales(0, pk_next);
+            bool pending = false; // GROUP mode: accumulators hold an unfinished scale group
+            int pending_gi = 0;
+            int in_group = GPS1 ? 0 : g_first % a.groups_per_scale; // 128-groups already seen of the current scale group
+
+            // fold the integer accumulators of a finished scale group into fp32; gi = group within the stage.
+            // v = acc0 + acc1 / 2^kShift - (zero + offset) * sum(x) is exact; with one scale group per 128 features its
+            // magnitude is below 2^22 for the narrow bit widths, where int -> float is done with the 1.5 * 2^23 trick
+            // (two ALU/FMA operations) instead of a conversion instruction.
+            constexpr long long kBound = 128LL * (XU8 ? 255 : 128) * (((1 << Q) - 1) + ((1 << Q) - 1) + (1 << (Q - 1)));
+            constexpr bool kMagic = GPS1 && kBound < (1LL << 22);
+            auto fold = [&](int gi) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t pk = __shfl_sync(0xffffffffu, (gi & 1) ? pk_cur[1] : pk_cur[0], 2 * (g + 8 * h) + (gi >> 1));
+                    const float sc_w = __uint_as_float(pk & 0xffffff00u);
+                    const int z = zoff + (int)(pk & 0xffu);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            int v = acc[0][mt][2 * h + j];
+                            if (X::kSets == 2)
+                                v += acc[X::kSets - 1][mt][2 * h + j] >> X::kShift;
+                            v -= z * xs[mt][j];
+                            const float fv = kMagic ? __int_as_float(v + 0x4b400000) - 12582912.0f : (float)v;
+                            facc[mt][2 * h + j] = fmaf(fv, sc_w, facc[mt][2 * h + j]);
+#pragma unroll
+                            for (int k = 0; k < X::kSets; ++k)
+                                acc[k][mt][2 * h + j] = 0;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                    xs[mt][0] = xs[mt][1] = 0;
+            };
+
+            for (int j = 0; j < my_nst && ok; ++j) {
+                if (GROUPED) {
+                    pk_cur[0] = pk_next[0];
+                    pk_cur[1] = pk_next[1];
+                    if (j + 1 < my_nst)
+                        fetch_scales(j + 1, pk_next);
+                }
+                ok = mbar_wait_bounded(&my_full[slot], phase, a.status, STATUS_TIMEOUT_TMA);
+                if (!ok)
+                    break;
+                const uint8_t *stage = my_ring + (size_t)slot * kStageBytes;
+                const int groups_here = min(4, a.total_groups - (g_first + j * 4));
+#pragma unroll
+                for (int gi = 0; gi < 4; ++gi) {
+                    if (gi < groups_here) {
+                        const uint32_t off = (((uint32_t)gi ^ swz) << 4) + (t << 2);
+                        uint32_t pa[Q], pb[Q];
+#pragma unroll
+                        for (int b = 0; b < Q; ++b) {
+                            pa[b] = *reinterpret_cast<const uint32_t *>(stage + b * 1024 + g * 64 + off);
+                            pb[b] = *reinterpret_cast<const uint32_t *>(stage + b * 1024 + (g + 8) * 64 + off);
+                        }
+                        pa[Q - 1] ^= flip;
+                        pb[Q - 1] ^= flip;
+                        uint32_t ra[8], rb[8];
+                        X::run(pa, ra);
+                        X::run(pb, rb);
+                        const uint8_t *rec = recs + (size_t)(j * 4 + gi) * kRec;
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                            for (int ip = 0; ip < 2; ++ip) {
+                                const uint4 bf = *reinterpret_cast<const uint4 *>(rec + ((mt * 2 + ip) * 32 + lane) * 16);
+                                mma_u8<XU8>(acc[X::set_of_step(2 * ip)][mt], ra[4 * ip], rb[4 * ip], ra[4 * ip + 1], rb[4 * ip + 1], bf.x,
+                                            bf.y);
+                                mma_u8<XU8>(acc[X::set_of_step(2 * ip + 1)][mt], ra[4 * ip + 2], rb[4 * ip + 2], ra[4 * ip + 3],
+                                            rb[4 * ip + 3], bf.z, bf.w);
+                            }
+                        }
+                        const int *sums = reinterpret_cast<const int *>(rec + 1024 * MT);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const int2 sv = *reinterpret_cast<const int2 *>(sums + 8 * mt + 2 * t);
+                            xs[mt][0] += sv.x;
+                            xs[mt][1] += sv.y;
+                        }
+                        if (GROUPED) {
+                            if (GPS1) {
+                                fold(gi);
+                            } else {
+                                pending = true;
+                                pending_gi = gi;
+                                if (++in_group == a.groups_per_scale) {
+                                    in_group = 0;
+                                    fold(gi);
+                                    pending = false;
+                                }
+                            }
+                        }
+                    }
+                }
+                // a scale group that continues in the next stage is folded with the scale staged for this one (the fold
+                // is linear); after this point pk_cur is overwritten
+                if (GROUPED && !GPS1 && pending) {
+                    fold(pending_gi);
+                    pending = false;
+                }
+                __syncwarp();
+                if (lane == 0 && ir < r_end)
+                    issue(slot); // the slot just consumed is free again
+                if (++slot == a.ring) {
+                    slot = 0;
+                    phase ^= 1;
                 }
             }
-            __threadfence();
             __syncwarp();
-            int old = 0;
-            if (lane == 0)
-                old = atomicAdd(a.counters + r, 1);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            finish = old == a.slices - 1;
-            if (finish) {
-                __threadfence();
+
+            // ---- this warp's share of the tile: fp32 (GROUP) or exact int32, rows g, g + 8, tokens 8 mt + 2 t + {0, 1}
+            int v[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (GROUPED) {
+                        v[mt][e] = __float_as_int(facc[mt][e]);
+                    } else {
+                        int z = zoff;
+                        const int n = n0 + g + 8 * (e >> 1);
+                        if (a.scale_mode == ABQ_SCALE_CHANNEL && a.w_zero && n < a.N)
+                            z += a.w_zero[n];
+                        int x = acc[0][mt][e];
+                        if (X::kSets == 2)
+                            x += acc[X::kSets - 1][mt][e] >> X::kShift; // exact: every term of that set is a multiple of 2^kShift
+                        v[mt][e] = x - z * xs[mt][e & 1];
+                    }
+                }
+            }
+
+            // ---- the warps of a tile meet in shared memory; part 0 adds the others in part order
+            if (a.split > 1) {
+                if (sc != 0) {
+                    if (ok)
+                        ok = mbar_wait_bounded(&red_free[ts], round_parity ^ 1, a.status, STATUS_TIMEOUT_PIPE); // previous round read
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            red[(warp * 4 * MT + mt * 4 + e) * 32 + lane] = v[mt][e];
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&red_ready[ts]);
+                    continue;
+                }
+                if (ok)
+                    ok = mbar_wait_bounded(&red_ready[ts], round_parity, a.status, STATUS_TIMEOUT_PIPE);
+                for (int k = 1; k < a.split; ++k) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int pv = red[((warp + k) * 4 * MT + mt * 4 + e) * 32 + lane];
+                            v[mt][e] = GROUPED ? __float_as_int(__int_as_float(v[mt][e]) + __int_as_float(pv)) : v[mt][e] + pv;
+                        }
+                }
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&red_free[ts]);
+            }
+
+            // ---- K split over CTAs as well: workspace slot per slice, last arrival adds them in slice order
+            bool finish = true;
+            if (a.slices > 1) {
+                int *pslot = a.partials + ((size_t)s * a.tiles + r) * (size_t)a.M * 16;
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int tok = 8 * mt + 2 * t + (e & 1);
-                        int isum = 0;
-                        float fsum = 0.f;
-                        if (tok < a.M) {
-                            for (int sl = 0; sl < a.slices; ++sl) { // fixed order: the result does not depend on who finishes
-                                const int pv = __ldcg(a.partials + ((size_t)sl * a.tiles + r) * (size_t)a.M * 16 + tok * 16 + g + 8 * (e >> 1));
-                                if (GROUPED)
-                                    fsum += __int_as_float(pv);
-                                else
-                                    isum += pv;
+                        if (tok < a.M)
+                            pslot[tok * 16 + g + 8 * (e >> 1)] = v[mt][e];
+                    }
+                }
+                __threadfence();
+                __syncwarp();
+                int old = 0;
+                if (lane == 0)
+                    old = atomicAdd(a.counters + r, 1);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                finish = old == a.slices - 1;
+                if (finish) {
+                    __threadfence();
+                    if (lane == 0)
+                        a.counters[r] = 0; // leave the counter ready for the next launch
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int tok = 8 * mt + 2 * t + (e & 1);
+                            int isum = 0;
+                            float fsum = 0.f;
+                            if (tok < a.M) {
+                                for (int sl = 0; sl < a.slices; ++sl) { // fixed order: the result does not depend on who finishes
+                                    const int pv =
+                                        __ldcg(a.partials + ((size_t)sl * a.tiles + r) * (size_t)a.M * 16 + tok * 16 + g + 8 * (e >> 1));
+                                    if (GROUPED)
+                                        fsum += __int_as_float(pv);
+                                    else
+                                        isum += pv;
+                                }
                             }
+                            v[mt][e] = GROUPED ? __float_as_int(fsum) : isum;
                         }
-                        v[mt][e] = GROUPED ? __float_as_int(fsum) : isum;
                     }
                 }
             }
-        }
-        if (finish) {
+            if (finish) {
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
+                for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int tok = 8 * mt + 2 * t + (e & 1);
-                    const int n = n0 + g + 8 * (e >> 1);
-                    if (tok < a.M && n < a.N) {
-                        const size_t o = (size_t)tok * a.N + n;
-                        if (a.out_dtype == ABQ_OUT_INT32) {
-                            reinterpret_cast<int *>(a.D)[o] = v[mt][e];
-                        } else {
-                            __half h;
-                            if (a.scale_mode == ABQ_SCALE_TENSOR_COMPAT) {
-                                h = __hmul(__int2half_rn(v[mt][e]), ld_half(a.C));
+                    for (int e = 0; e < 4; ++e) {
+                        const int tok = 8 * mt + 2 * t + (e & 1);
+                        const int n = n0 + g + 8 * (e >> 1);
+                        if (tok < a.M && n < a.N) {
+                            const size_t o = (size_t)tok * a.N + n;
+                            if (a.out_dtype == ABQ_OUT_INT32) {
+                                reinterpret_cast<int *>(a.D)[o] = v[mt][e];
                             } else {
-                                float f = GROUPED ? __int_as_float(v[mt][e]) : (float)v[mt][e] * __half2float(ld_half(a.w_scale + n));
-                                if (a.x_scale)
-                                    f *= a.x_scale[tok];
-                                h = __float2half_rn(f);
+                                __half h;
+                                if (a.scale_mode == ABQ_SCALE_TENSOR_COMPAT) {
+                                    h = __hmul(__int2half_rn(v[mt][e]), ld_half(a.C));
+                                } else {
+                                    float f = GROUPED ? __int_as_float(v[mt][e]) : (float)v[mt][e] * __half2float(ld_half(a.w_scale + n));
+                                    if (a.x_scale)
+                                        f *= a.x_scale[tok];
+                                    h = __float2half_rn(f);
+                                }
+                                reinterpret_cast<__half *>(a.D)[o] = h;
                             }
-                            reinterpret_cast<__half *>(a.D)[o] = h;
                         }
                     }
                 }
@@ -379,16 +516,16 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
     // A wait that expired may have left copies in flight: give them one more bounded chance to land before the
     // shared memory they target is released.
     if (!ok && lane == 0) {
-        for (int slot = 0; slot < a.ring; ++slot)
-            mbar_wait_bounded(&my_full[slot], 0, nullptr, 0);
+        for (int i = 0; i < a.ring; ++i)
+            mbar_wait_bounded(&my_full[i], 0, nullptr, 0);
     }
 }
 
 // ------------------------------------------------------------------------------------------- host side
 
 struct DecodeLayout {
-    int MT, NW, tiles, total_groups, slices, stages_per_slice, ctas_per_slice, ring;
-    size_t smem, off_counters, off_partials, bytes;
+    int MT, NW, tiles, total_groups, slices, stages_per_slice, ctas_per_slice, split, stages_per_split, ring;
+    size_t smem, off_partials, bytes;
 };
 
 static int device_sms()
@@ -399,27 +536,25 @@ static int device_sms()
     return 148;
 }
 
-// Workspace: [activation records][tile counters][split-K partial slots for up to kDecodeMaxSlices slices]
-static void workspace_layout(int M, int N, int K, size_t *off_counters, size_t *off_partials, size_t *total)
+// Workspace (only used when K is split over CTAs): [tile counters][partial slots for kDecodeMaxSlices slices]
+static void workspace_layout(int M, int N, size_t *off_partials, size_t *total)
 {
-    const int MT = M <= 8 ? 1 : 2;
-    const size_t rec = (size_t)(K / 128) * decode_record_bytes(MT);
     const int tiles = (N + 15) / 16;
-    *off_counters = (rec + 255) & ~(size_t)255;
-    *off_partials = (*off_counters + (size_t)tiles * 4 + 255) & ~(size_t)255;
+    *off_partials = ((size_t)tiles * 4 + 255) & ~(size_t)255;
     *total = *off_partials + (size_t)kDecodeMaxSlices * tiles * M * 16 * 4;
 }
 
 size_t decode_workspace_bytes(int M, int N, int K)
 {
-    size_t a, b, total;
-    workspace_layout(M, N, K, &a, &b, &total);
+    (void)K;
+    size_t a, total;
+    workspace_layout(M, N, &a, &total);
     return total;
 }
 
-// Tile shape of a launch: warps per CTA, split-K factor, ring depth.  One CTA per SM; the split is chosen so that
-// every warp of the machine gets about one 16-row tile of its slice (the kernel is latency-bound per warp, so
-// equal tile counts per warp matter more than long slices).
+// Launch shape.  K is split over CTAs only as far as needed for the activation records of a slice to fit beside a
+// ring of at least two stages per warp; the tiles are then shared evenly by the CTAs of a slice, and the warps of
+// a CTA share a tile `split` ways so that the longest warp (rounds x stages per part) is as short as possible.
 static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
 {
     const int Q = p.w_bits;
@@ -430,41 +565,63 @@ static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
     const int sms = device_sms();
     const int stage_bytes = Q * 1024;
     const int rec = decode_record_bytes(L->MT);
-    const int want_nw = env_int("ABQ_DECODE_WARPS", 16);
-    for (int nw = want_nw; nw >= 8; nw -= 8) {
-        int slices = (nw * sms + L->tiles / 2) / L->tiles;
-        slices = slices < 1 ? 1 : slices;
-        slices = slices > kDecodeMaxSlices ? kDecodeMaxSlices : slices;
-        slices = slices > total_stages ? total_stages : slices;
-        slices = env_int("ABQ_DECODE_SLICES", slices);
-        if (slices < 1 || slices > kDecodeMaxSlices || slices > total_stages)
-            return false;
-        const int sps = (total_stages + slices - 1) / slices;
-        slices = (total_stages + sps - 1) / sps; // drop slices that would be empty
-        int cps = sms / slices;
-        cps = cps > L->tiles ? L->tiles : cps;
-        cps = cps < 1 ? 1 : cps;
-        const size_t fixed = 1024 + (size_t)sps * 4 * rec + ((size_t)nw * kMaxRing + 1) * 8;
-        const size_t budget = 226 * 1024;
-        if (fixed >= budget)
-            continue;
-        int ring = (int)((budget - fixed) / ((size_t)nw * stage_bytes));
-        ring = ring > kMaxRing ? kMaxRing : ring;
-        ring = env_int("ABQ_DECODE_RING", ring);
-        if (ring < 2 && nw > 8)
-            continue;
-        if (ring < 1 || ring > kMaxRing)
-            return false;
-        L->NW = nw;
-        L->slices = slices;
-        L->stages_per_slice = sps;
-        L->ctas_per_slice = cps;
-        L->ring = ring;
-        L->smem = fixed + (size_t)nw * ring * stage_bytes;
-        workspace_layout(p.M, p.N, p.K, &L->off_counters, &L->off_partials, &L->bytes);
-        return L->smem <= 227 * 1024;
+    const size_t budget = 226 * 1024;
+    const int forced_slices = env_int("ABQ_DECODE_SLICES", 0);
+    // 16 warps per CTA when two ring stages per warp fit, else 8 (wide weights); the smallest K split that fits
+    int NW = 0, slices = 0, sps = 0, ring = 0;
+    size_t fixed = 0;
+    for (int nw = env_int("ABQ_DECODE_WARPS", kMaxWarps); nw >= 8 && !NW; nw -= 8) {
+        fixed = 1024 + (size_t)nw * 4 * L->MT * 32 * 4 + ((size_t)nw * kMaxRing + 2 * nw) * 8;
+        for (int sl = forced_slices > 0 ? forced_slices : 1; sl <= kDecodeMaxSlices && sl <= total_stages; ++sl) {
+            const int st = (total_stages + sl - 1) / sl;
+            const size_t need = fixed + (size_t)st * 4 * rec;
+            const int rg = need < budget ? (int)((budget - need) / ((size_t)nw * stage_bytes)) : 0;
+            if (rg >= 2 || (rg >= 1 && nw == 8 && (sl == kDecodeMaxSlices || sl == total_stages)) || (forced_slices > 0 && rg >= 1)) {
+                NW = nw;
+                slices = sl;
+                sps = st;
+                ring = rg;
+                break;
+            }
+            if (forced_slices > 0)
+                break;
+        }
     }
-    return false;
+    if (!NW)
+        return false;
+    slices = (total_stages + sps - 1) / sps; // drop slices that would be empty
+    ring = ring > kMaxRing ? kMaxRing : ring;
+    ring = env_int("ABQ_DECODE_RING", ring);
+    if (ring < 1 || ring > kMaxRing)
+        return false;
+    int cps = sms / slices;
+    cps = cps > L->tiles ? L->tiles : cps;
+    cps = cps < 1 ? 1 : cps;
+    const int tiles_per_cta = (L->tiles + cps - 1) / cps;
+    int best_split = 1;
+    long best_cost = -1;
+    for (int sp = 1; sp <= NW && sp <= sps; ++sp) {
+        const int per_round = NW / sp;
+        const long rounds = (tiles_per_cta + per_round - 1) / per_round;
+        const long cost = rounds * ((sps + sp - 1) / sp) * 8 + (sp > 1 ? 1 : 0); // stage time units; a tie goes to the smaller split
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best_split = sp;
+        }
+    }
+    best_split = env_int("ABQ_DECODE_SPLIT", best_split);
+    if (best_split < 1 || best_split > NW)
+        return false;
+    L->NW = NW;
+    L->slices = slices;
+    L->stages_per_slice = sps;
+    L->ctas_per_slice = cps;
+    L->split = best_split;
+    L->stages_per_split = (sps + best_split - 1) / best_split;
+    L->ring = ring;
+    L->smem = fixed + (size_t)sps * 4 * rec + (size_t)NW * ring * stage_bytes;
+    workspace_layout(p.M, p.N, &L->off_partials, &L->bytes);
+    return L->smem <= 227 * 1024;
 }
 
 template <int Q, int MT, bool XU8, int NW>
@@ -500,9 +657,9 @@ static cudaError_t launch_variant(const abq_gemm_state *st, const DecodeArgs &ar
 }
 
 template <int Q>
-static cudaError_t launch_q(const abq_gemm_state *st, const DecodeArgs &args, int MT, bool xu8, int nw, cudaStream_t stream)
+static cudaError_t launch_q(const abq_gemm_state *st, const DecodeArgs &args, int MT, bool xu8, cudaStream_t stream)
 {
-    if (nw == 16) {
+    if (st->block[0] == 16 * 32) {
         if (MT == 1)
             return xu8 ? launch_variant<Q, 1, true, 16>(st, args, stream) : launch_variant<Q, 1, false, 16>(st, args, stream);
         return xu8 ? launch_variant<Q, 2, true, 16>(st, args, stream) : launch_variant<Q, 2, false, 16>(st, args, stream);
@@ -522,7 +679,7 @@ abq_status decode_plan(abq_gemm_state *st)
     DecodeLayout L;
     if (!make_layout(p, &L))
         return ABQ_ERR_UNSUPPORTED;
-    if (!p.workspace || p.workspace_bytes < L.bytes)
+    if (L.slices > 1 && (!p.workspace || p.workspace_bytes < L.bytes))
         return ABQ_ERR_WORKSPACE;
 
     const uint64_t KW = (uint64_t)p.K / 32;
@@ -541,38 +698,44 @@ abq_status decode_plan(abq_gemm_state *st)
     st->tile[0] = L.stages_per_slice;
     st->tile[1] = L.ring;
     st->tile[2] = L.ctas_per_slice;
-    st->tile[3] = L.MT;
+    st->tile[3] = L.split;
     return ABQ_OK;
 }
 
 cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
 {
     const abq_gemm_params &p = st->p;
-    const int MT = st->tile[3];
-    const bool pdl = (p.flags & ABQ_FLAG_PDL) != 0;
-    size_t off_counters, off_partials, total;
-    workspace_layout(p.M, p.N, p.K, &off_counters, &off_partials, &total);
+    const int MT = p.M <= 8 ? 1 : 2;
+    size_t off_partials, total;
+    workspace_layout(p.M, p.N, &off_partials, &total);
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
     const int tiles = (p.N + 15) / 16;
-    cudaError_t e = cudaSuccess;
-    if (!env_int("ABQ_EXPERIMENT_SKIP_XPREP", 0))
-        e = xprep_decode(reinterpret_cast<const uint32_t *>(p.X), ws, reinterpret_cast<int *>(ws + off_counters), tiles, p.M, p.K,
-                         p.x_bits, p.x_signed, MT, pdl, stream);
-    if (e != cudaSuccess)
-        return e;
     DecodeArgs a;
     a.M = p.M;
     a.N = p.N;
     a.K = p.K;
     a.tiles = tiles;
     a.total_groups = p.K / 128;
-    a.stages_per_slice = st->tile[0];
     a.slices = st->cluster;
+    a.stages_per_slice = st->tile[0];
     a.ctas_per_slice = st->tile[2];
+    a.split = st->tile[3];
+    a.stages_per_split = (a.stages_per_slice + a.split - 1) / a.split;
     a.ring = st->tile[1];
-    a.records = ws;
-    a.counters = reinterpret_cast<int *>(ws + off_counters);
-    a.partials = reinterpret_cast<int *>(ws + off_partials);
+    a.X = reinterpret_cast<const uint32_t *>(p.X);
+    a.x_bits = p.x_bits;
+    a.x_signed = p.x_signed;
+    a.counters = nullptr;
+    a.partials = nullptr;
+    if (a.slices > 1) {
+        // the arrival counters must be zero when the kernel starts; it leaves them zero, but nothing guarantees the
+        // state of a caller-owned workspace before the first launch
+        a.counters = reinterpret_cast<int *>(ws);
+        a.partials = reinterpret_cast<int *>(ws + off_partials);
+        cudaError_t e = cudaMemsetAsync(a.counters, 0, (size_t)tiles * 4, stream);
+        if (e != cudaSuccess)
+            return e;
+    }
     a.D = p.D;
     a.w_scale = reinterpret_cast<const __half *>(p.w_scale);
     a.w_zero = p.w_zero;
@@ -586,14 +749,14 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.status = p.status_word;
     const bool xu8 = !p.x_signed && p.x_bits == 8;
     switch (p.w_bits) {
-    case 1: return launch_q<1>(st, a, MT, xu8, st->block[0] / 32, stream);
-    case 2: return launch_q<2>(st, a, MT, xu8, st->block[0] / 32, stream);
-    case 3: return launch_q<3>(st, a, MT, xu8, st->block[0] / 32, stream);
-    case 4: return launch_q<4>(st, a, MT, xu8, st->block[0] / 32, stream);
-    case 5: return launch_q<5>(st, a, MT, xu8, st->block[0] / 32, stream);
-    case 6: return launch_q<6>(st, a, MT, xu8, st->block[0] / 32, stream);
-    case 7: return launch_q<7>(st, a, MT, xu8, st->block[0] / 32, stream);
-    case 8: return launch_q<8>(st, a, MT, xu8, st->block[0] / 32, stream);
+    case 1: return launch_q<1>(st, a, MT, xu8, stream);
+    case 2: return launch_q<2>(st, a, MT, xu8, stream);
+    case 3: return launch_q<3>(st, a, MT, xu8, stream);
+    case 4: return launch_q<4>(st, a, MT, xu8, stream);
+    case 5: return launch_q<5>(st, a, MT, xu8, stream);
+    case 6: return launch_q<6>(st, a, MT, xu8, stream);
+    case 7: return launch_q<7>(st, a, MT, xu8, stream);
+    case 8: return launch_q<8>(st, a, MT, xu8, stream);
     default: return cudaErrorInvalidValue;
     }
 }
