@@ -1,0 +1,74 @@
+"""tcgen05 route (M > 16): int32 bit-exact against the CPU oracle, fp16 epilogues within tolerance."""
+import numpy as np
+import pytest
+
+from helpers import dev, planes_dev, rand_codes, run_gemm
+from test_gpu_gemm_fp16 import check_close
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # M, N, K, x_bits, w_bits, x_signed, w_signed
+    (128, 256, 128, 8, 8, True, True),
+    (128, 256, 512, 4, 4, False, False),
+    (17, 64, 128, 8, 2, True, False),
+    (100, 200, 384, 3, 5, True, True),
+    (300, 520, 1152, 8, 4, True, False),
+    (512, 1024, 4096, 2, 2, True, True),
+    (256, 4096, 2048, 8, 8, False, False),
+    (130, 72, 640, 6, 7, False, True),
+    (128, 4096, 4096, 4, 4, False, False),   # the reference's CPU-checkable configuration (W4A4, unsigned)
+    (128, 4096, 4096, 4, 4, True, True),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "M{}N{}K{}a{}w{}{}{}".format(*c[:5], "s" if c[5] else "u", "s" if c[6] else "u"))
+def test_int32(abq, oracle, cuda, case):
+    M, N, K, p, q, xs, ws = case
+    rng = np.random.default_rng(sum(case[:5]))
+    x, w = rand_codes(rng, M, K, p, xs), rand_codes(rng, N, K, q, ws)
+    got, st = run_gemm(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=xs, w_signed=ws,
+                       route=abq.ROUTE_I8_UMMA)
+    want = oracle.gemm_values_blas(x, w)
+    if M * N * K * p * q <= 1 << 27:
+        assert np.array_equal(oracle.compute_ref(oracle.pack(w, q), oracle.pack(x, p), xs, ws), want)
+    assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} of {got.size} differ"
+
+
+def test_literal_reference_loop_on_sampled_rows(abq, oracle, cuda):
+    """W4A4 128 x 4096 x 4096: the literal plane/bit loop on a sample of rows, the GPU result on all of them."""
+    M, N, K, p, q = 128, 4096, 4096, 4, 4
+    rng = np.random.default_rng(5)
+    x, w = rand_codes(rng, M, K, p, False), rand_codes(rng, N, K, q, False)
+    got, _ = run_gemm(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=False, w_signed=False)
+    rows = [0, 63, 127]
+    lit = oracle.compute_ref(oracle.pack(w, q), oracle.pack(x[rows], p), False, False)
+    assert np.array_equal(got[rows], lit)
+    assert np.array_equal(got, oracle.gemm_values_blas(x, w))
+
+
+@pytest.mark.parametrize("M,N,K,q", [(64, 512, 1024, 4), (512, 4096, 4096, 2), (200, 1000, 2176, 8)])
+@pytest.mark.parametrize("with_zero", [False, True])
+def test_per_channel(abq, oracle, cuda, M, N, K, q, with_zero):
+    rng = np.random.default_rng(N + K + q)
+    x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+    w = rand_codes(rng, N, K, q, False)
+    ws = rng.uniform(0.001, 0.02, size=N).astype(np.float16)
+    wz = rng.integers(0, 1 << q, size=N).astype(np.uint8) if with_zero else None
+    xs = rng.uniform(0.01, 0.05, size=M).astype(np.float32)
+    got, _ = run_gemm(abq, planes_dev(oracle, x, 8), planes_dev(oracle, w, q), M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False,
+                      out_fp16=True, scale_mode=abq.SCALE_CHANNEL, w_scale=dev(ws), w_zero=None if wz is None else dev(wz),
+                      x_scale=dev(xs), route=abq.ROUTE_I8_UMMA)
+    ref = oracle.dequant_gemm(x, w, ws, None if wz is None else wz.astype(np.int32), xs, None)
+    check_close(got, ref)
+
+
+def test_tensor_compat_is_bit_exact(abq, oracle, cuda):
+    M, N, K, p, q = 96, 384, 512, 8, 2
+    rng = np.random.default_rng(3)
+    x, w = rand_codes(rng, M, K, p, True), rand_codes(rng, N, K, q, True)
+    scale = np.float16(0.0123)
+    got, _ = run_gemm(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=True, w_signed=True,
+                      out_fp16=True, scale_mode=abq.SCALE_TENSOR_COMPAT, C=dev(np.array([scale])), route=abq.ROUTE_I8_UMMA)
+    want = oracle.dequant_tensor_compat(oracle.gemm_values_blas(x, w), scale)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
