@@ -72,6 +72,7 @@ def lib() -> ctypes.CDLL:
         L.abq_gemm_init.argtypes = [ctypes.POINTER(GemmParams), ctypes.POINTER(GemmState)]
         L.abq_gemm_exec.argtypes = [ctypes.POINTER(GemmState), ctypes.c_void_p]
         L.abq_gemm.argtypes = [ctypes.POINTER(GemmParams), ctypes.c_void_p]
+        L.abq_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmParams), ctypes.c_void_p]
         L.abq_pack_int32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         L.abq_pack_int4.argtypes = L.abq_pack_int32.argtypes
         L.abq_quantize_pack_half.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
@@ -153,6 +154,14 @@ def gemm_exec(state: GemmState, stream=None) -> None:
 
 def gemm(params: GemmParams, stream=None) -> None:
     _check(lib().abq_gemm(ctypes.byref(params), _stream(stream)), "abq_gemm")
+
+
+STATIC_SCRATCH_BYTES = 16 << 20
+
+
+def gemm_static_scratch(params: GemmParams, stream=None) -> None:
+    """abq_gemm on the library's built-in device scratch array: allocates nothing, ignores params.workspace."""
+    _check(lib().abq_gemm_static_scratch(ctypes.byref(params), _stream(stream)), "abq_gemm_static_scratch")
 
 
 def pack_int32(values, planes, rows: int, K: int, bits: int, stream=None) -> None:

@@ -165,6 +165,26 @@ ABQ_API abq_status abq_quantize_pack_half(const void *in_half, const float *scal
 ABQ_API abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, int K, int bits, int is_signed,
                            abq_stream_t stream);
 
+/*
+ * abq_gemm for callers that cannot supply scratch memory.  No counterpart in the reference.
+ *
+ * Same contract as abq_gemm, except that params->workspace / workspace_bytes are ignored: the scratch the chosen
+ * route needs is taken from one array of ABQ_STATIC_SCRATCH_BYTES bytes that lives in device memory of every GPU
+ * the library is loaded on, from load until the process exits.  The call allocates nothing (no cudaMalloc, no
+ * cudaFree, no allocating library routine), which is what a caller needs that runs inside a stream-ordered forward
+ * pass with a workspace it does not size itself (the FasterTransformer linear layers give the GEMM wrapper only
+ * x_bits * tokens * K / 8 bytes) and must not synchronise the device.
+ *   - Problems whose abq_gemm_workspace_bytes() exceeds ABQ_STATIC_SCRATCH_BYTES are rejected with
+ *     ABQ_ERR_WORKSPACE; use abq_gemm with a caller-owned workspace for those.
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress, with that device current).
+ *     Make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps what the last call left in it.  The kernels
+ *     overwrite what they read before they read it, so nothing needs clearing, but two calls that overlap on the
+ *     GPU (different streams, or graphs replayed concurrently) race on it: serialise them on one stream.
+ */
+#define ABQ_STATIC_SCRATCH_BYTES (16u << 20)
+ABQ_API abq_status abq_gemm_static_scratch(const abq_gemm_params *params, abq_stream_t stream);
+
 /* Text for a status code; cudaError_t of the last failing CUDA call in this thread (0 if none). */
 ABQ_API const char *abq_status_string(abq_status s);
 ABQ_API int abq_last_cuda_error(void);
