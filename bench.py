@@ -203,6 +203,20 @@ def capture_passes(torch, abq, gemms, mode):
     return lambda i: graphs[i % WEIGHT_COPIES].replay()
 
 
+def max_over_ranks(torch, dist, value: float, device) -> float:
+    """The slowest rank's figure (timing rule for every multi-GPU number); identity without a process group."""
+    if dist is None:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_rate(world: int, units_per_rank_step: float, steps: int, ms_max: float) -> float:
+    """Replicas do not exchange data: the job processed world * units in the time of its slowest rank."""
+    return world * units_per_rank_step * steps / (ms_max * 1e-3)
+
+
 def timed(torch, dist, fn, steps, warmup):
     """W warm-up calls, then K timed calls between device events, barrier + synchronize on both sides; max over ranks."""
     for i in range(warmup):
@@ -223,10 +237,7 @@ def timed(torch, dist, fn, steps, warmup):
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    return ms, wall_ms
+    return max_over_ranks(torch, dist, ms, "cuda"), wall_ms
 
 
 def per_config_detail(torch, abq, gemms, reps=20):
@@ -365,8 +376,8 @@ def main():
     if int(status.item()) != 0:
         raise SystemExit(f"device status word {int(status.item())}: a bounded wait expired, the numbers are void")
 
-    value = world * bytes_per_step * args.steps / (ms * 1e-3) / 1e9
-    e2e = world * bytes_per_step * args.steps / (ms_e2e * 1e-3) / 1e9
+    value = whole_job_rate(world, bytes_per_step, args.steps, ms) / 1e9
+    e2e = whole_job_rate(world, bytes_per_step, args.steps, ms_e2e) / 1e9
     h2d = sum(g["host_x"].numel() * 4 for g in gemms if g["copy"] == 0)
     d2h = sum(g["out"].numel() * 2 for g in gemms if g["copy"] == 0)
     peak, peak_kind = measured_peaks()
@@ -380,7 +391,7 @@ def main():
                                f"{n_gemm} GEMMs per step" + (f" (restricted by --only {args.only})" if args.only else ""),
                    "l2": f"two alternating copies of every weight, {bytes_per_step / 1e6:.0f} MB of distinct operands between reuses (> 126 MB L2)",
                    "replicas": world, "pdl": os.environ.get("ABQ_BENCH_PDL", "1") == "1", "cuda_graph_per_pass": use_graph},
-        "effective_TOPS": world * ops_per_step * args.steps / (ms * 1e-3) / 1e12,
+        "effective_TOPS": whole_job_rate(world, ops_per_step, args.steps, ms) / 1e12,
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": 2 * n_gemm * args.steps,
         "clocks": clocks,
