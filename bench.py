@@ -262,6 +262,53 @@ def per_config_detail(torch, abq, gemms, reps=20):
     return rows
 
 
+PREFILL_CASES = [(4, 4, 4096, 4096, 4096), (4, 4, 4096, 11008, 4096), (2, 8, 4096, 12288, 4096), (8, 8, 4096, 4096, 11008),
+                 (4, 4, 2048, 4096, 4096), (4, 4, 512, 12288, 4096)]  # (w bits, x bits, M, N, K)
+
+
+def prefill_leg(torch, abq, reps=10):
+    """Prefill shapes (M >= 512) on the tcgen05 kind::i8 route, per-channel fp16 scale, fp16 output: device time of the
+    whole call (plane -> int8 expansion of both operands, the GEMM with its fused epilogue) per case, effective
+    TOPS = 2*M*N*K / t, and the fraction of twice the measured dense bf16 rate (the int8 rate of the same pipe)."""
+    peak = None
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        peak = 2.0 * float(json.loads(f.read_text())["bf16_tflops"])
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    B = abq.binding
+    rows = []
+    for (q, p, M, N, K) in PREFILL_CASES:
+        def planes_of(rows_, bits):
+            codes = torch.randint(0, 1 << bits, (rows_, K), dtype=torch.int32, device="cuda", generator=gen)
+            out = torch.empty((bits, rows_, K // 32), dtype=torch.int32, device="cuda")
+            abq.pack_int32(codes, out, rows_, K, bits)
+            return out
+        xp, wp = planes_of(M, p), planes_of(N, q)
+        wsc = (torch.rand((N,), device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16)
+        out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        work = torch.empty(abq.gemm_workspace_bytes(M, N, K, p, q), dtype=torch.uint8, device="cuda")
+        prm = B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=False, w_signed=False, out_dtype=abq.OUT_FP16,
+                            scale_mode=abq.SCALE_CHANNEL, w_scale=wsc, workspace=work)
+        st = abq.gemm_init(prm)
+        for _ in range(3):
+            abq.gemm_exec(st)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            abq.gemm_exec(st)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        tops = 2.0 * M * N * K / us / 1e6
+        rows.append({"wxay": f"W{q}A{p}", "M": M, "N": N, "K": K, "us": round(us, 2), "TOPS": round(tops, 1),
+                     "frac_of_int8_peak": round(tops / peak, 3) if peak else None})
+        del xp, wp, out, work
+    return {"route": "tcgen05 kind::i8 (plane->int8 expansion included in the time)", "int8_peak_TOPS": peak,
+            "peak_source": "2 x MEASURED_PEAKS.json bf16_tflops" if peak else None, "cases": rows}
+
+
 def cpu_baseline_sample(kind_pref: str, budget_s: float = 12.0):
     """The reference's CPU loop (`compute_ref`) on a bounded sample of the sweep: its W2A8, M=16, N=4096,
     K=4096 GEMM, repeated until about `budget_s` seconds of host time are spent; all host cores."""
@@ -304,6 +351,10 @@ def cpu_baseline_sample(kind_pref: str, budget_s: float = 12.0):
             "seconds": t}
 
 
+WORKLOAD = ("decode sweep (BASELINE configs[1]): W{2,3,4}A8 x M{1,4,16} x (N,K) in "
+            "{(4096,4096),(12288,4096),(11008,4096),(4096,11008)}, g128 fp16 scale + u8 zero, fp16 out")
+
+
 def run_reference(args, rank, world):
     """`--impl reference`: the reference's own CPU implementation of the path on the host cores."""
     if rank != 0:
@@ -320,8 +371,8 @@ def run_reference(args, rank, world):
     value = statistics.mean(v["value"] for v in vals)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
             "ms_per_step": total_t / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
-            "data": "synthetic", "config": {"workload": "decode sweep W{2,3,4}A8 x M{1,4,16} x 4 LLaMA-7B shapes; each step a bounded "
-                                                        "sample of its first GEMM on the host cores"},
+            "data": "synthetic", "config": {"workload": WORKLOAD + "; each step a bounded sample (one M=16 W2A8 4096x4096 GEMM of the sweep, "
+                                                                   "repeated) on the host cores, reference compute_ref"},
             "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     line["cpu_baseline"]["value"] = value
@@ -336,6 +387,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--detail", action="store_true", help="also time every GEMM of the sweep alone")
     ap.add_argument("--only", default="", help="profiling aid: restrict the sweep to GEMMs 'q:M:N:K[,q:M:N:K...]' (0 = any)")
+    ap.add_argument("--shape", default="", help="profiling aid: replace the sweep by the single GEMM 'q:M:N:K' (any size the route takes)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the short prefill-shape (tcgen05 route) leg")
     ap.add_argument("--no-graph", action="store_true", help="profiling aid: launch kernel by kernel instead of one CUDA graph per pass")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling aid: skip the host-side reference timing")
     args = ap.parse_args()
@@ -357,6 +410,10 @@ def main():
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
     abq = load_package()
+    if args.shape:
+        q, M, N, K = (int(v) for v in args.shape.split(":"))
+        global SHAPES, WBITS, MS
+        SHAPES, WBITS, MS = [(N, K)], [q], [M]
     gemms, status = build_workload(abq, torch, seed=20241 + rank)
     if args.only:
         pats = [tuple(int(v) for v in item.split(":")) for item in args.only.split(",")]
@@ -386,14 +443,12 @@ def main():
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
-        "config": {"workload": "decode sweep (BASELINE configs[1]): W{2,3,4}A8 x M{1,4,16} x (N,K) in "
-                               "{(4096,4096),(12288,4096),(11008,4096),(4096,11008)}, g128 fp16 scale + u8 zero, fp16 out; "
-                               f"{n_gemm} GEMMs per step" + (f" (restricted by --only {args.only})" if args.only else ""),
+        "config": {"workload": WORKLOAD + f"; {n_gemm} GEMMs per step" + (f" (restricted by --only {args.only})" if args.only else ""),
                    "l2": f"two alternating copies of every weight, {bytes_per_step / 1e6:.0f} MB of distinct operands between reuses (> 126 MB L2)",
                    "replicas": world, "pdl": os.environ.get("ABQ_BENCH_PDL", "1") == "1", "cuda_graph_per_pass": use_graph},
         "effective_TOPS": whole_job_rate(world, ops_per_step, args.steps, ms) / 1e12,
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 2 * n_gemm * args.steps,
+        "gpu_launches": n_gemm * args.steps,  # one decode_kernel per GEMM
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "decode_kernel (36 launches per step, all shapes)", "achieved": per_gpu, "peak": peak,
                      "unit": "GB/s", "frac": per_gpu / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
@@ -403,6 +458,10 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         base = cpu_baseline_sample("reference")
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if args.shape:
+        line["config"]["workload"] = f"single GEMM --shape {args.shape} (profiling aid, not the sweep)"
+    if rank == 0 and world == 1 and not args.no_prefill and not args.shape and not args.only:
+        line["prefill"] = prefill_leg(torch, abq)
     if args.detail and rank == 0:
         line["detail"] = per_config_detail(torch, abq, gemms)
     if rank == 0:
