@@ -21,7 +21,10 @@ __host__ __device__ constexpr int decode_record_bytes(int MT) { return 1024 * MT
 
 // ---- gemm_decode.cu (route ABQ_ROUTE_I8_MMA, M <= 16)
 constexpr int kDecodeMaxSlices = 8;  // largest split-K factor (the workspace reserves that many partial slots)
-abq_status decode_plan(abq_gemm_state *st);
+// clear_counters: zero the split-K arrival counters now and wait for it (plans that are launched many times);
+// otherwise the caller queues decode_clear_counters() on its stream before the launch (one-shot calls)
+abq_status decode_plan(abq_gemm_state *st, bool clear_counters);
+cudaError_t decode_clear_counters(const abq_gemm_state *st, cudaStream_t stream);
 cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream);
 size_t decode_workspace_bytes(int M, int N, int K);
 

@@ -146,7 +146,7 @@ size_t abq_gemm_workspace_bytes(int M, int N, int K, int x_bits, int w_bits, int
     return (need + 255) & ~(size_t)255;
 }
 
-abq_status abq_gemm_init(const abq_gemm_params *params, abq_gemm_state *state)
+static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state, bool clear_counters)
 {
     if (!params || !state)
         return ABQ_ERR_INVALID_ARG;
@@ -160,7 +160,7 @@ abq_status abq_gemm_init(const abq_gemm_params *params, abq_gemm_state *state)
         route = params->M <= 16 ? ABQ_ROUTE_I8_MMA : ABQ_ROUTE_I8_UMMA;
     switch (route) {
     case ABQ_ROUTE_B1_MMA: s = b1_plan(state); break;
-    case ABQ_ROUTE_I8_MMA: s = decode_plan(state); break;
+    case ABQ_ROUTE_I8_MMA: s = decode_plan(state, clear_counters); break;
     case ABQ_ROUTE_I8_UMMA: s = umma_plan(state); break;
     default: s = ABQ_ERR_INVALID_ARG;
     }
@@ -190,12 +190,24 @@ abq_status abq_gemm_exec(const abq_gemm_state *state, abq_stream_t stream)
     return ABQ_OK;
 }
 
+abq_status abq_gemm_init(const abq_gemm_params *params, abq_gemm_state *state)
+{
+    return plan_gemm(params, state, true);
+}
+
 abq_status abq_gemm(const abq_gemm_params *params, abq_stream_t stream)
 {
     abq_gemm_state st;
-    abq_status s = abq_gemm_init(params, &st);
+    abq_status s = plan_gemm(params, &st, false); // one-shot: everything, the counter reset included, goes on the stream
     if (s != ABQ_OK)
         return s;
+    if (st.route == ABQ_ROUTE_I8_MMA) {
+        cudaError_t e = decode_clear_counters(&st, reinterpret_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) {
+            set_last_cuda_error(e);
+            return ABQ_ERR_CUDA;
+        }
+    }
     return abq_gemm_exec(&st, stream);
 }
 

@@ -603,7 +603,9 @@ static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
     for (int sp = 1; sp <= NW && sp <= sps; ++sp) {
         const int per_round = NW / sp;
         const long rounds = (tiles_per_cta + per_round - 1) / per_round;
-        const long cost = rounds * ((sps + sp - 1) / sp) * 8 + (sp > 1 ? 1 : 0); // stage time units; a tie goes to the smaller split
+        // in eighths of a stage time: the stages of the longest part, plus per round about one and a half stage times of
+        // tile set-up (first scales, output) and, when the tile is shared, of the hand-shake in shared memory
+        const long cost = rounds * (((sps + sp - 1) / sp) * 8 + 6 + (sp > 1 ? 6 : 0));
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best_split = sp;
@@ -669,7 +671,7 @@ static cudaError_t launch_q(const abq_gemm_state *st, const DecodeArgs &args, in
     return xu8 ? launch_variant<Q, 2, true, 8>(st, args, stream) : launch_variant<Q, 2, false, 8>(st, args, stream);
 }
 
-abq_status decode_plan(abq_gemm_state *st)
+abq_status decode_plan(abq_gemm_state *st, bool clear_counters)
 {
     const abq_gemm_params &p = st->p;
     if (p.M > 16)
@@ -681,6 +683,14 @@ abq_status decode_plan(abq_gemm_state *st)
         return ABQ_ERR_UNSUPPORTED;
     if (L.slices > 1 && (!p.workspace || p.workspace_bytes < L.bytes))
         return ABQ_ERR_WORKSPACE;
+    if (L.slices > 1 && clear_counters) {
+        // K split over CTAs: one arrival counter per tile, zero between launches (every launch leaves them zero).
+        // Cleared once here and waited for, so that launches on any stream may follow; a memset node per launch would
+        // cost several microseconds and break the programmatic chain between consecutive kernels.
+        if (cudaMemsetAsync(p.workspace, 0, (size_t)L.tiles * 4, cudaStreamPerThread) != cudaSuccess ||
+            cudaStreamSynchronize(cudaStreamPerThread) != cudaSuccess)
+            return ABQ_ERR_CUDA;
+    }
 
     const uint64_t KW = (uint64_t)p.K / 32;
     const uint64_t dims[3] = { KW, (uint64_t)p.N, (uint64_t)p.w_bits };
@@ -700,6 +710,13 @@ abq_status decode_plan(abq_gemm_state *st)
     st->tile[2] = L.ctas_per_slice;
     st->tile[3] = L.split;
     return ABQ_OK;
+}
+
+cudaError_t decode_clear_counters(const abq_gemm_state *st, cudaStream_t stream)
+{
+    if (st->cluster <= 1)
+        return cudaSuccess;
+    return cudaMemsetAsync(st->p.workspace, 0, (size_t)((st->p.N + 15) / 16) * 4, stream);
 }
 
 cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
@@ -728,13 +745,10 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.counters = nullptr;
     a.partials = nullptr;
     if (a.slices > 1) {
-        // the arrival counters must be zero when the kernel starts; it leaves them zero, but nothing guarantees the
-        // state of a caller-owned workspace before the first launch
+        // the arrival counters are zero here: planning (or the one-shot call) cleared them, every launch leaves them zero
         a.counters = reinterpret_cast<int *>(ws);
         a.partials = reinterpret_cast<int *>(ws + off_partials);
-        cudaError_t e = cudaMemsetAsync(a.counters, 0, (size_t)tiles * 4, stream);
-        if (e != cudaSuccess)
-            return e;
+
     }
     a.D = p.D;
     a.w_scale = reinterpret_cast<const __half *>(p.w_scale);

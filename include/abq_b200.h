@@ -119,8 +119,10 @@ typedef struct abq_gemm_state {
 ABQ_API size_t abq_gemm_workspace_bytes(int M, int N, int K, int x_bits, int w_bits, int route);
 
 /*
- * Plan a GEMM: validates, picks the route and tile, encodes TMA descriptors, sets kernel
- * attributes.  Host work only, no launch.  Replaces `AqBMMAInitFn_t` / `AqBWMMAInitFn_t`
+ * Plan a GEMM: validates, picks the route and tile, encodes TMA descriptors.  Host work, except that a
+ * decode-shape plan which splits K over CTAs clears its arrival counters (the first 4 * ceil(N / 16) bytes of the
+ * workspace) and waits for that: call it outside stream capture and not while a GEMM on the same workspace is
+ * running; launches leave the counters cleared, so plans may share a workspace.  Replaces `AqBMMAInitFn_t` / `AqBWMMAInitFn_t`
  * (engine/mma_any/aq_bmma_op.h:141-151,163; aq_wmma_op.h) and the per-config
  * `AqBMMA_..._InitFn` globals (engine/common/base.h:144-166): tile shape is chosen here, not by name.
  */

@@ -41,3 +41,39 @@ def test_int32_small_m(abq, oracle, cuda, case, route):
         lit = oracle.compute_ref(oracle.pack(w, q), oracle.pack(x, p), xs, ws)
         assert np.array_equal(lit, want)
     assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} of {got.size} differ"
+
+
+@pytest.mark.parametrize("one_shot", [False, True], ids=["plan_exec", "one_shot"])
+def test_split_k_counters_on_dirty_workspace(abq, oracle, cuda, one_shot):
+    """K split over CTAs (activation records of all of K do not fit one CTA): the arrival counters live in the
+    caller's workspace, which here starts as garbage.  Planning (or the one-shot call) must clear them, and
+    repeated launches of one plan must leave them ready for the next launch."""
+    import torch
+    from abq_llm_b200 import binding as B
+    M, N, K, p, q = 16, 520, 11008, 8, 4
+    rng = np.random.default_rng(77)
+    x = rand_codes(rng, M, K, p, True)
+    w = rand_codes(rng, N, K, q, False)
+    xp, wp = planes_dev(oracle, x, p), planes_dev(oracle, w, q)
+    want = oracle.gemm_values_blas(x, w)
+    out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    ws = torch.full((max(256, abq.gemm_workspace_bytes(M, N, K, p, q, abq.ROUTE_I8_MMA)),), 0xA5, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    prm = B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=True, w_signed=False, route=abq.ROUTE_I8_MMA,
+                        workspace=ws, status_word=status)
+    torch.cuda.synchronize()
+    if one_shot:
+        for _ in range(3):
+            out.fill_(-1)
+            abq.gemm(prm)
+            torch.cuda.synchronize()
+            assert np.array_equal(out.cpu().numpy(), want)
+    else:
+        st = abq.gemm_init(prm)
+        assert st.cluster > 1, "this shape is meant to split K over CTAs"
+        for _ in range(3):
+            out.fill_(-1)
+            abq.gemm_exec(st)
+            torch.cuda.synchronize()
+            assert np.array_equal(out.cpu().numpy(), want)
+    assert int(status.item()) == 0
