@@ -44,6 +44,9 @@ XBITS = 8
 GROUP = 128
 WEIGHT_COPIES = 2  # every weight exists twice and the copies alternate, so a pass never finds its planes in L2
 METRIC = "quant_gemm_decode_sweep_algorithmic_GBps"
+# dram__bytes_read + dram__bytes_write over algorithmic bytes, from the ncu capture of decode_kernel summarised in
+# profiles/decode_kernel_sweep_and_w4a8_m1_32768x4096.md (a smaller single-shape case; traffic grows with the bytes)
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.018
 
 
 def load_package():
@@ -452,7 +455,9 @@ def main():
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "decode_kernel (36 launches per step, all shapes)", "achieved": per_gpu, "peak": peak,
                      "unit": "GB/s", "frac": per_gpu / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
-                     "traffic": None},
+                     "bytes_per_launch": bytes_per_step / max(1, n_gemm), "us_per_launch": ms * 1e3 / args.steps / max(1, n_gemm),
+                     "traffic": DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per_step / max(1, n_gemm),
+                     "traffic_source": "ncu dram bytes of a single-shape capture, scaled by algorithmic bytes (mean launch of the sweep)"},
         "wall_ms_per_step": wall_ms / args.steps,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
