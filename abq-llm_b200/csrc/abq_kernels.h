@@ -16,6 +16,9 @@ cudaError_t quantize_pack_half(const __half *in, const float *scale, uint32_t *p
 
 // ---- xprep.cu
 cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream);
+// both operands of a GEMM (same K) in one launch
+cudaError_t unpack_pair_i8(const uint32_t *planes_a, void *out_a, int rows_a, int bits_a, int signed_a, const uint32_t *planes_b, void *out_b,
+                           int rows_b, int bits_b, int signed_b, int K, cudaStream_t stream);
 // Bytes of one decode-route activation record (one per 128 input features): MT token tiles of 8.
 __host__ __device__ constexpr int decode_record_bytes(int MT) { return 1024 * MT + 64; }
 

@@ -6,12 +6,15 @@
 // 128 x BN x 32 block replaces the p*q plane-pair MMAs, with a bit-identical int32 result
 // (|acc| <= 255 * 255 * K < 2^31 for K <= 33 000).
 //
-// Kernel: one CTA per 128 x BN output tile.
+// Kernel: persistent, one CTA per SM, 128 x BN output tiles dealt round-robin (consecutive tiles share a weight tile).
 //   warp 0      TMA producer: A (activations, 128 rows x 128 B) and B (weights, BN rows x 128 B) tiles of a
-//               K block into a ring of 128B-swizzled stages, completion on mbarriers
-//   warp 1      allocates TMEM, one elected thread issues four 128 x BN x 32 UMMAs per stage (smem descriptors
-//               advanced by 32 B inside the swizzle atom), tcgen05.commit frees the stage / signals the epilogue
-//   warps 2..5  epilogue: tcgen05.ld the int32 accumulators (lane = output row), fused dequantisation, stores
+//               K block into a ring of 128B-swizzled stages that runs on across tile boundaries
+//   warp 1      allocates TMEM (two accumulators of BN columns); one elected thread issues four 128 x BN x 32 UMMAs
+//               per stage (smem descriptors advanced by 32 B inside the swizzle atom); tcgen05.commit frees the
+//               stage and, after the last K block, hands the accumulator to the epilogue
+//   warps 2..5  epilogue of the previous tile while the next one is being multiplied: channel scales / zero
+//               points staged in shared memory, tcgen05.ld of the int32 accumulators (lane = output row), fused
+//               dequantisation, 16-byte stores; then the accumulator goes back to the MMA warp
 // Every wait is bounded (abq_common.cuh); on expiry the status word is set, the roles leave their loops, the
 // CTA still meets at the final barrier and TMEM is released.
 #include <cuda.h>
@@ -84,28 +87,101 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Epilogue of 32 accumulator columns of one output row.  MODE 0: int32, 1: fp16 times one fp16 factor (the
+// reference's arithmetic: the accumulator rounded to fp16, then an fp16 multiply), 2: per-channel scale (and zero
+// point) from shared memory, per-token scale from a register.
+template <int MODE>
+__device__ __forceinline__ void store_chunk(const UmmaArgs &a, const int (&v)[32], int row, int nb, const float *s_scale, const int *s_zero,
+                                            float xs, int xsum, __half cscale, bool has_zero)
+{
+    if (MODE == 0) {
+        int *dst = reinterpret_cast<int *>(a.D) + (size_t)row * a.N + nb;
+        if (nb + 32 <= a.N && (a.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<int4 *>(dst + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (nb + j < a.N)
+                    dst[j] = v[j];
+        }
+        return;
+    }
+    uint32_t h[16]; // 32 fp16 values, two per register
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        float f[4];
+        if (MODE == 1) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                f[e] = 0.f;
+            const __half2 c2 = __half2half2(cscale);
+            const __half2 lo = __hmul2(__halves2half2(__int2half_rn(v[j]), __int2half_rn(v[j + 1])), c2);
+            const __half2 hi = __hmul2(__halves2half2(__int2half_rn(v[j + 2]), __int2half_rn(v[j + 3])), c2);
+            h[j / 2] = *reinterpret_cast<const uint32_t *>(&lo);
+            h[j / 2 + 1] = *reinterpret_cast<const uint32_t *>(&hi);
+        } else {
+            const float4 sc = *reinterpret_cast<const float4 *>(s_scale + j); // same address in every lane: a broadcast
+            int x[4] = { v[j], v[j + 1], v[j + 2], v[j + 3] };
+            if (has_zero) {
+                const int4 z = *reinterpret_cast<const int4 *>(s_zero + j);
+                x[0] -= z.x * xsum;
+                x[1] -= z.y * xsum;
+                x[2] -= z.z * xsum;
+                x[3] -= z.w * xsum;
+            }
+            f[0] = (float)x[0] * sc.x * xs; // same order of roundings as the reference-side formula: (acc * scale) * x_scale
+            f[1] = (float)x[1] * sc.y * xs;
+            f[2] = (float)x[2] * sc.z * xs;
+            f[3] = (float)x[3] * sc.w * xs;
+            const __half2 lo = __floats2half2_rn(f[0], f[1]), hi = __floats2half2_rn(f[2], f[3]);
+            h[j / 2] = *reinterpret_cast<const uint32_t *>(&lo);
+            h[j / 2 + 1] = *reinterpret_cast<const uint32_t *>(&hi);
+        }
+    }
+    __half *dst = reinterpret_cast<__half *>(a.D) + (size_t)row * a.N + nb;
+    if (nb + 32 <= a.N && (a.N & 7) == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(h[j], h[j + 1], h[j + 2], h[j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (nb + j < a.N)
+                dst[j] = __ushort_as_half((unsigned short)(h[j >> 1] >> ((j & 1) * 16)));
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                                                                const UmmaArgs a)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int kABytes = kUmmaBM * kUmmaBK, kBBytes = BN * kUmmaBK, kStageBytes = kABytes + kBBytes;
-    constexpr int kTmemCols = BN < 32 ? 32 : BN; // power of two >= 32
+    constexpr int kTmemCols = 2 * BN; // two accumulators: the epilogue drains one while the next tile fills the other
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)a.stages * kStageBytes);
-    uint64_t *full = bars, *empty = bars + 8, *acc_full = bars + 16;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 17);
+    float *s_scale = reinterpret_cast<float *>(smem + (size_t)a.stages * kStageBytes); // [2][BN] channel scales of a tile
+    int *s_zero = reinterpret_cast<int *>(s_scale + 2 * BN);                            // [2][BN] channel zero points
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_zero + 2 * BN);
+    uint64_t *full = bars, *empty = bars + 8, *acc_full = bars + 16, *acc_empty = bars + 18, *par_ready = bars + 20;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 22);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * kUmmaBM, n0 = blockIdx.x * BN;
     const int k_blocks = a.K / kUmmaBK;
+    const int m_tiles = (a.M + kUmmaBM - 1) / kUmmaBM;
+    const int total_tiles = m_tiles * ((a.N + BN - 1) / BN);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);    // one arrival per epilogue warp
+            mbar_init(&par_ready[b], 128);  // every epilogue thread has staged its channel parameters
+        }
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
@@ -118,46 +194,96 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_cons
     __syncthreads();
     tmem_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait_prior_grid(); // operand codes and token sums come from the kernels launched just before
 
+    // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ...; consecutive tiles share the weight (N) tile, so
+    // the CTAs running at one time read few distinct weight tiles and all of the activations out of L2.
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % a.stages;
-                if (kb >= a.stages && !mbar_wait_bounded(&empty[s], ((kb / a.stages) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE))
-                    break;
-                uint8_t *sa = smem + (size_t)s * kStageBytes, *sb = sa + kABytes;
-                mbar_arrive_expect_tx(&full[s], kStageBytes);
-                tma_load_2d(sa, &tmap_a, kb * kUmmaBK, m0, &full[s]);
-                tma_load_2d(sb, &tmap_b, kb * kUmmaBK, n0, &full[s]);
+            int kc = 0; // k-blocks requested so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * kUmmaBM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++kc) {
+                    const int s = kc % a.stages;
+                    if (kc >= a.stages && !mbar_wait_bounded(&empty[s], ((kc / a.stages) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sa = smem + (size_t)s * kStageBytes, *sb = sa + kABytes;
+                    mbar_arrive_expect_tx(&full[s], kStageBytes);
+                    tma_load_2d(sa, &tmap_a, kb * kUmmaBK, m0, &full[s]);
+                    tma_load_2d(sb, &tmap_b, kb * kUmmaBK, n0, &full[s]);
+                }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
+            int kc = 0, it = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % a.stages;
-                ok = mbar_wait_bounded(&full[s], (kb / a.stages) & 1, a.status, STATUS_TIMEOUT_TMA);
-                if (!ok)
-                    break;
-                tmem_fence_after();
-                const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
-                const uint64_t da = make_smem_desc_sw128(sa), db = make_smem_desc_sw128(sb);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const int b = it & 1;
+                if (it >= 2) { // the epilogue has drained this accumulator's previous tile
+                    ok = mbar_wait_bounded(&acc_empty[b], ((it >> 1) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE);
+                    if (!ok)
+                        break;
+                    tmem_fence_after();
+                }
+                const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++kc) {
+                    const int s = kc % a.stages;
+                    ok = mbar_wait_bounded(&full[s], (kc / a.stages) & 1, a.status, STATUS_TIMEOUT_TMA);
+                    if (!ok)
+                        break;
+                    tmem_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
+                    const uint64_t da = make_smem_desc_sw128(sa), db = make_smem_desc_sw128(sb);
 #pragma unroll
-                for (int k = 0; k < kUmmaBK / 32; ++k) // 32 bytes of K per instruction: advance the start address inside the atom
-                    umma_i8(tmem_base, da + (uint64_t)(k * 32 >> 4), db + (uint64_t)(k * 32 >> 4), a.idesc, (kb | k) != 0);
-                umma_commit(&empty[s]); // arrives when the MMAs above have finished reading this stage
+                    for (int k = 0; k < kUmmaBK / 32; ++k) // 32 bytes of K per instruction: advance the start address inside the atom
+                        umma_i8(tmem_d, da + (uint64_t)(k * 32 >> 4), db + (uint64_t)(k * 32 >> 4), a.idesc, (kb | k) != 0);
+                    umma_commit(&empty[s]); // arrives when the MMAs above have finished reading this stage
+                }
+                if (ok)
+                    umma_commit(&acc_full[b]); // arrives when all MMAs of the tile have written the accumulator
             }
-            umma_commit(acc_full); // arrives when all MMAs have written the accumulator
         }
         __syncwarp();
     } else {
         // epilogue warps 2..5: a warp may only touch the TMEM lane quarter (warp id % 4)
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        const bool ok = mbar_wait_bounded(acc_full, 0, a.status, STATUS_TIMEOUT_MMA);
-        tmem_fence_after();
-        if (ok) {
+        const int et = threadIdx.x - 64; // 0..127 among the epilogue threads
+        const bool channel = a.out_dtype != ABQ_OUT_INT32 && a.scale_mode != ABQ_SCALE_TENSOR_COMPAT;
+        const bool has_zero = channel && a.scale_mode == ABQ_SCALE_CHANNEL && a.w_zero != nullptr;
+        const __half cscale = a.scale_mode == ABQ_SCALE_TENSOR_COMPAT && a.out_dtype != ABQ_OUT_INT32 ? ld_half(a.C) : __half();
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            const int b = it & 1;
+            const int m0 = (tile % m_tiles) * kUmmaBM, n0 = (tile / m_tiles) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            float *ts = s_scale + b * BN;
+            int *tz = s_zero + b * BN;
+            if (channel) { // stage the tile's channel parameters while its MMAs still run
+                for (int c = et; c < BN; c += 128) {
+                    const int n = n0 + c;
+                    float sv = 1.f;
+                    int zv = 0;
+                    if (n < a.N) {
+                        if (a.scale_mode == ABQ_SCALE_CHANNEL && a.w_scale)
+                            sv = __half2float(a.w_scale[n]);
+                        if (has_zero)
+                            zv = a.w_zero[n];
+                    }
+                    ts[c] = sv;
+                    tz[c] = zv;
+                }
+                // epilogue threads only, and bounded like every other wait; the other buffer (tile it - 1) stays untouched
+                mbar_arrive(&par_ready[b]);
+                ok = mbar_wait_bounded(&par_ready[b], (it >> 1) & 1, a.status, STATUS_TIMEOUT_PIPE);
+                if (!ok)
+                    break;
+            }
             float xs = 1.f;
             int xsum = 0;
             if (row < a.M) {
@@ -166,57 +292,27 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_cons
                 if (a.xsum)
                     xsum = a.xsum[row];
             }
-            const __half cscale = a.scale_mode == ABQ_SCALE_TENSOR_COMPAT ? ld_half(a.C) : __half();
+            ok = mbar_wait_bounded(&acc_full[b], (it >> 1) & 1, a.status, STATUS_TIMEOUT_MMA);
+            if (!ok)
+                break;
+            tmem_fence_after();
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 int v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + c), v);
                 if (row >= a.M)
                     continue;
-                const int nb = n0 + c;
-                if (a.out_dtype == ABQ_OUT_INT32) {
-                    int *dst = reinterpret_cast<int *>(a.D) + (size_t)row * a.N + nb;
-                    if (nb + 32 <= a.N && (a.N & 3) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<int4 *>(dst + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nb + j < a.N)
-                                dst[j] = v[j];
-                    }
-                } else {
-                    __half h[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int n = nb + j;
-                        if (a.scale_mode == ABQ_SCALE_TENSOR_COMPAT) {
-                            h[j] = __hmul(__int2half_rn(v[j]), cscale);
-                        } else {
-                            float f = 0.f;
-                            if (n < a.N) {
-                                int x = v[j];
-                                if (a.w_zero)
-                                    x -= (int)a.w_zero[n] * xsum;
-                                f = (float)x * __half2float(ld_half(a.w_scale + n)) * xs;
-                            }
-                            h[j] = __float2half_rn(f);
-                        }
-                    }
-                    __half *dst = reinterpret_cast<__half *>(a.D) + (size_t)row * a.N + nb;
-                    if (nb + 32 <= a.N && (a.N & 7) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            *reinterpret_cast<uint4 *>(dst + j) = *reinterpret_cast<const uint4 *>(&h[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nb + j < a.N)
-                                dst[j] = h[j];
-                    }
-                }
+                if (a.out_dtype == ABQ_OUT_INT32)
+                    store_chunk<0>(a, v, row, n0 + c, ts + c, tz + c, xs, xsum, cscale, has_zero);
+                else if (!channel)
+                    store_chunk<1>(a, v, row, n0 + c, ts + c, tz + c, xs, xsum, cscale, has_zero);
+                else
+                    store_chunk<2>(a, v, row, n0 + c, ts + c, tz + c, xs, xsum, cscale, has_zero);
             }
+            tmem_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&acc_empty[b]); // this warp's quarter of the accumulator is free again
         }
     }
 
@@ -234,11 +330,25 @@ __global__ void __launch_bounds__(256) rowsum_kernel(const uint8_t *__restrict__
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= M)
         return;
-    const uint32_t *p = reinterpret_cast<const uint32_t *>(x + (size_t)row * K);
+    const uint4 *p = reinterpret_cast<const uint4 *>(x + (size_t)row * K); // K is a multiple of 128: rows are 16-byte aligned
     int s = 0;
-    for (int i = lane; i < K / 4; i += 32) {
-        const uint32_t w = __ldg(p + i);
-        s = is_signed ? __dp4a((int)w, 0x01010101, s) : (int)__dp4a(w, 0x01010101u, (unsigned)s);
+    const int n16 = K / 16;
+#pragma unroll 8
+    for (int i = lane; i < n16; i += 32) {
+        const uint4 w = __ldg(p + i);
+        if (is_signed) {
+            s = __dp4a((int)w.x, 0x01010101, s);
+            s = __dp4a((int)w.y, 0x01010101, s);
+            s = __dp4a((int)w.z, 0x01010101, s);
+            s = __dp4a((int)w.w, 0x01010101, s);
+        } else {
+            unsigned u = (unsigned)s;
+            u = __dp4a(w.x, 0x01010101u, u);
+            u = __dp4a(w.y, 0x01010101u, u);
+            u = __dp4a(w.z, 0x01010101u, u);
+            u = __dp4a(w.w, 0x01010101u, u);
+            s = (int)u;
+        }
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1)
@@ -281,16 +391,26 @@ abq_status umma_plan(abq_gemm_state *st)
         if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
             sms = v;
     }
-    // widest N tile that still gives every SM a CTA
+    // N tile: the persistent CTAs run ceil(tiles / SMs) tiles each.  Narrower tiles balance better, but measured per
+    // output column they cost almost twice as much (operand fetch per operation doubles), so they only win on small grids
     const int m_tiles = (p.M + kUmmaBM - 1) / kUmmaBM;
     int BN = 256;
-    while (BN > 64 && (long)m_tiles * ((p.N + BN - 1) / BN) < sms)
-        BN >>= 1;
+    {
+        double best = 0;
+        for (int bn = 256; bn >= 64; bn >>= 1) {
+            const long tiles = (long)m_tiles * ((p.N + bn - 1) / bn);
+            const double t = (double)((tiles + sms - 1) / sms) * bn * (bn == 256 ? 1.0 : (bn == 128 ? 1.85 : 3.5));
+            if (best == 0 || t < best) {
+                best = t;
+                BN = bn;
+            }
+        }
+    }
     BN = env_int("ABQ_UMMA_BN", BN);
     if (BN != 64 && BN != 128 && BN != 256)
         return ABQ_ERR_INVALID_ARG;
     const int stage_bytes = (kUmmaBM + BN) * kUmmaBK;
-    int stages = (200 * 1024) / stage_bytes;
+    int stages = (216 * 1024) / stage_bytes;
     stages = stages > 8 ? 8 : stages;
     const int k_blocks = p.K / kUmmaBK;
     stages = stages > k_blocks ? k_blocks : stages;
@@ -305,13 +425,14 @@ abq_status umma_plan(abq_gemm_state *st)
     if (!encode_tmap(st->tmap[0], TMAP_U8, 2, ws, dims_a, strides, box_a, TMAP_SWIZZLE_128B) ||
         !encode_tmap(st->tmap[1], TMAP_U8, 2, ws + off_w, dims_b, strides, box_b, TMAP_SWIZZLE_128B))
         return ABQ_ERR_CUDA;
-    st->grid[0] = (p.N + BN - 1) / BN;
-    st->grid[1] = m_tiles;
+    const long tiles = (long)m_tiles * ((p.N + BN - 1) / BN);
+    st->grid[0] = (unsigned)(tiles < sms ? tiles : sms); // persistent: a CTA per SM, tiles dealt round-robin
+    st->grid[1] = 1;
     st->grid[2] = 1;
     st->block[0] = kUmmaThreads;
     st->block[1] = st->block[2] = 1;
     st->cluster = 1;
-    st->shared_mem_size = 1024 + (size_t)stages * stage_bytes + 256;
+    st->shared_mem_size = 1024 + (size_t)stages * stage_bytes + (size_t)4 * BN * 4 + 256;
     st->tile[0] = BN;
     st->tile[1] = stages;
     return ABQ_OK;
@@ -331,8 +452,19 @@ static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cud
     CUtensorMap ta, tb;
     memcpy(&ta, st->tmap[0], sizeof(ta));
     memcpy(&tb, st->tmap[1], sizeof(tb));
-    kern<<<dim3(st->grid[0], st->grid[1]), kUmmaThreads, st->shared_mem_size, stream>>>(ta, tb, args);
-    return cudaGetLastError();
+    // programmatic launch: barrier set-up, TMEM allocation and descriptor prefetch overlap the tail of the expansion
+    // kernel; every thread passes griddepcontrol.wait before it touches what that kernel (or the token sums) wrote
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(st->grid[0], 1, 1);
+    cfg.blockDim = dim3(kUmmaThreads);
+    cfg.dynamicSmemBytes = st->shared_mem_size;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, args);
 }
 
 cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
@@ -341,10 +473,8 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
     size_t off_w, off_sum, total;
     umma_layout(p.M, p.N, p.K, &off_w, &off_sum, &total);
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
-    cudaError_t e = unpack_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.K, p.x_bits, p.x_signed, stream);
-    if (e != cudaSuccess)
-        return e;
-    e = unpack_i8(reinterpret_cast<const uint32_t *>(p.W), ws + off_w, p.N, p.K, p.w_bits, p.w_signed, stream);
+    cudaError_t e = unpack_pair_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.x_bits, p.x_signed,
+                                   reinterpret_cast<const uint32_t *>(p.W), ws + off_w, p.N, p.w_bits, p.w_signed, p.K, stream);
     if (e != cudaSuccess)
         return e;
     UmmaArgs a;

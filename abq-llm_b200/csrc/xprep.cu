@@ -22,38 +22,105 @@ __device__ __forceinline__ void transpose4(uint32_t a, uint32_t b, uint32_t c, u
     o[3] = __byte_perm(u1, v1, 0x7632);
 }
 
+// 32-element runs, one per lane and step: BITS plane words -> 32 code bytes in element order.  Called by whole warps
+// (runs past the end are skipped lane by lane): neighbouring lanes swap halves so that every store instruction writes complete 32-byte
+// sectors (each lane alone would write its 32 bytes as two half sectors).
+constexpr int kUnpackRuns = 4; // runs per thread, 256 threads apart: all their plane loads are in flight before the first is used
+
+template <int BITS>
+__device__ __forceinline__ void unpack_run(const uint32_t *__restrict__ planes, uint32_t *__restrict__ out, long L, long idx0, int is_signed)
+{
+    uint32_t p[kUnpackRuns][BITS];
+    bool live[kUnpackRuns];
+#pragma unroll
+    for (int u = 0; u < kUnpackRuns; ++u) {
+        const long idx = idx0 + u * 256;
+        live[u] = idx < L;
+#pragma unroll
+        for (int b = 0; b < BITS; ++b)
+            p[u][b] = live[u] ? __ldg(planes + (long)b * L + idx) : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnpackRuns; ++u) {
+        const long idx = idx0 + u * 256;
+        uint32_t r[8];
+        planes_to_bytes<BITS>(p[u], false, r);
+        if (is_signed && BITS < 8) {
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                r[s] = sign_extend_bytes(r[s], BITS);
+        }
+        // byte y of r[s] is element 31 - 8y - s.  Output word (7 - 2y) holds elements 28-8y .. 31-8y =
+        // (r3.y, r2.y, r1.y, r0.y); word (6 - 2y) holds (r7.y, r6.y, r5.y, r4.y).
+        uint32_t hi[4], lo[4];
+        transpose4(r[3], r[2], r[1], r[0], hi);
+        transpose4(r[7], r[6], r[5], r[4], lo);
+        const uint4 q0 = make_uint4(lo[3], hi[3], lo[2], hi[2]), q1 = make_uint4(lo[1], hi[1], lo[0], hi[0]);
+        const bool odd = threadIdx.x & 1;
+        const uint4 give = odd ? q0 : q1; // the even lane hands over its second half, the odd lane its first half
+        uint4 got;
+        got.x = __shfl_xor_sync(0xffffffffu, give.x, 1);
+        got.y = __shfl_xor_sync(0xffffffffu, give.y, 1);
+        got.z = __shfl_xor_sync(0xffffffffu, give.z, 1);
+        got.w = __shfl_xor_sync(0xffffffffu, give.w, 1);
+        if (live[u]) { // L is even and lane pairs are aligned: a live lane's neighbour is live
+            uint4 *pair = reinterpret_cast<uint4 *>(out + (idx & ~1L) * 8); // 64 bytes of the lane pair: [even q0][even q1][odd q0][odd q1]
+            pair[odd ? 1 : 0] = odd ? got : q0;
+            pair[odd ? 3 : 2] = odd ? q1 : got;
+        }
+    }
+}
+
+__device__ __forceinline__ void unpack_any(const uint32_t *planes, uint32_t *out, long L, long idx, int bits, int is_signed)
+{
+    switch (bits) { // uniform per block
+    case 1: unpack_run<1>(planes, out, L, idx, is_signed); break;
+    case 2: unpack_run<2>(planes, out, L, idx, is_signed); break;
+    case 3: unpack_run<3>(planes, out, L, idx, is_signed); break;
+    case 4: unpack_run<4>(planes, out, L, idx, is_signed); break;
+    case 5: unpack_run<5>(planes, out, L, idx, is_signed); break;
+    case 6: unpack_run<6>(planes, out, L, idx, is_signed); break;
+    case 7: unpack_run<7>(planes, out, L, idx, is_signed); break;
+    default: unpack_run<8>(planes, out, L, idx, is_signed); break;
+    }
+}
+
 template <int BITS>
 __global__ void __launch_bounds__(256) unpack_i8_kernel(const uint32_t *__restrict__ planes, uint32_t *__restrict__ out, long L,
                                                         int is_signed)
 {
-    const long idx = (long)blockIdx.x * 256 + threadIdx.x; // one 32-element run per thread
-    if (idx >= L)
-        return;
-    uint32_t p[BITS];
-#pragma unroll
-    for (int b = 0; b < BITS; ++b)
-        p[b] = __ldg(planes + (long)b * L + idx);
-    uint32_t r[8];
-    planes_to_bytes<BITS>(p, false, r);
-    if (is_signed && BITS < 8) {
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-            r[s] = sign_extend_bytes(r[s], BITS);
+    unpack_run<BITS>(planes, out, L, (long)blockIdx.x * (256 * kUnpackRuns) + threadIdx.x, is_signed);
+}
+
+// Both operands of a GEMM in one launch: blocks [0, blocks_a) expand operand a, the rest operand b.  Lets the
+// dependent GEMM kernel start its set-up early (programmatic launch) and saves a launch per GEMM.
+__global__ void __launch_bounds__(256) unpack_pair_kernel(const uint32_t *__restrict__ pa, uint32_t *__restrict__ oa, long La, int bits_a,
+                                                          int signed_a, unsigned blocks_a, const uint32_t *__restrict__ pb,
+                                                          uint32_t *__restrict__ ob, long Lb, int bits_b, int signed_b)
+{
+    pdl_launch_dependents();
+    if (blockIdx.x < blocks_a) {
+        unpack_any(pa, oa, La, (long)blockIdx.x * (256 * kUnpackRuns) + threadIdx.x, bits_a, signed_a);
+    } else {
+        unpack_any(pb, ob, Lb, (long)(blockIdx.x - blocks_a) * (256 * kUnpackRuns) + threadIdx.x, bits_b, signed_b);
     }
-    // byte y of r[s] is element 31 - 8y - s.  Output word (7 - 2y) holds elements 28-8y .. 31-8y =
-    // (r3.y, r2.y, r1.y, r0.y); word (6 - 2y) holds (r7.y, r6.y, r5.y, r4.y).
-    uint32_t hi[4], lo[4];
-    transpose4(r[3], r[2], r[1], r[0], hi);
-    transpose4(r[7], r[6], r[5], r[4], lo);
-    uint4 *dst = reinterpret_cast<uint4 *>(out + idx * 8);
-    dst[0] = make_uint4(lo[3], hi[3], lo[2], hi[2]);
-    dst[1] = make_uint4(lo[1], hi[1], lo[0], hi[0]);
+}
+
+cudaError_t unpack_pair_i8(const uint32_t *planes_a, void *out_a, int rows_a, int bits_a, int signed_a, const uint32_t *planes_b, void *out_b,
+                           int rows_b, int bits_b, int signed_b, int K, cudaStream_t stream)
+{
+    const long La = (long)rows_a * (K / 32), Lb = (long)rows_b * (K / 32);
+    const long per = 256 * kUnpackRuns;
+    const unsigned blocks_a = (unsigned)((La + per - 1) / per), blocks_b = (unsigned)((Lb + per - 1) / per);
+    unpack_pair_kernel<<<blocks_a + blocks_b, 256, 0, stream>>>(planes_a, reinterpret_cast<uint32_t *>(out_a), La, bits_a, signed_a, blocks_a,
+                                                                planes_b, reinterpret_cast<uint32_t *>(out_b), Lb, bits_b, signed_b);
+    return cudaGetLastError();
 }
 
 cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream)
 {
     const long L = (long)rows * (K / 32);
-    const unsigned blocks = (unsigned)((L + 255) / 256);
+    const unsigned blocks = (unsigned)((L + 256 * kUnpackRuns - 1) / (256 * kUnpackRuns));
 #define CALL(B) (unpack_i8_kernel<B><<<blocks, 256, 0, stream>>>(planes, reinterpret_cast<uint32_t *>(out), L, is_signed), cudaGetLastError())
     switch (bits) {
     case 1: return CALL(1);
