@@ -151,8 +151,9 @@ def build_workload(abq, torch, seed):
     torch.cuda.synchronize()
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     gemms = []
-    for M in MS:
-        for q in WBITS:
+    # one bit width after the other, as a model with one weight format runs them: consecutive GEMMs use the same kernel
+    for q in WBITS:
+        for M in MS:
             for (N, K) in SHAPES:
                 ws_bytes = abq.gemm_workspace_bytes(M, N, K, XBITS, q)
                 for c in range(WEIGHT_COPIES):

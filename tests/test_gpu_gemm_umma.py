@@ -72,3 +72,51 @@ def test_tensor_compat_is_bit_exact(abq, oracle, cuda):
                       out_fp16=True, scale_mode=abq.SCALE_TENSOR_COMPAT, C=dev(np.array([scale])), route=abq.ROUTE_I8_UMMA)
     want = oracle.dequant_tensor_compat(oracle.gemm_values_blas(x, w), scale)
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("case", [(4096, 4096, 256, 4, 4, False, False), (1000, 12000, 384, 8, 3, True, False), (2100, 6000, 128, 2, 2, True, True)],
+                         ids=lambda c: "M{}N{}K{}a{}w{}".format(*c[:5]))
+def test_persistent_many_tiles_per_cta(abq, oracle, cuda, case):
+    """More output tiles than three rounds of CTAs: every CTA reuses both TMEM accumulators and wraps its TMA ring
+    across tile boundaries; ragged last tiles in both directions."""
+    M, N, K, p, q, xs, ws = case
+    rng = np.random.default_rng(M + N)
+    x, w = rand_codes(rng, M, K, p, xs), rand_codes(rng, N, K, q, ws)
+    got, st = run_gemm(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=xs, w_signed=ws,
+                       route=abq.ROUTE_I8_UMMA)
+    tiles = -(-M // 128) * -(-N // st.tile[0])
+    assert tiles > 2 * st.grid[0], "meant to give every CTA several tiles"
+    assert np.array_equal(got, oracle.gemm_values_blas(x, w))
+
+
+def test_persistent_channel_parameters_follow_the_tile(abq, oracle, cuda):
+    """Per-channel scale and zero point are staged per tile in two alternating shared-memory buffers: many tiles per CTA."""
+    M, N, K, p, q = 2048, 6000, 256, 8, 4
+    rng = np.random.default_rng(11)
+    x, w = rand_codes(rng, M, K, p, True), rand_codes(rng, N, K, q, False)
+    scale = rng.uniform(0.001, 0.02, size=N).astype(np.float16)
+    zero = rng.integers(0, 1 << q, size=N, dtype=np.uint8)
+    xs = rng.uniform(0.5, 2.0, size=M).astype(np.float32)
+    got, _ = run_gemm(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=True, w_signed=False,
+                      route=abq.ROUTE_I8_UMMA, out_fp16=True, scale_mode=abq.SCALE_CHANNEL, w_scale=dev(scale), w_zero=dev(zero), x_scale=dev(xs))
+    acc = oracle.gemm_values_blas(x, w).astype(np.float64) - zero.astype(np.float64)[None, :] * x.sum(axis=1, dtype=np.int64)[:, None]
+    check_close(got, acc * scale.astype(np.float64)[None, :] * xs.astype(np.float64)[:, None])
+
+
+def test_full_size_prefill_rows_match_decode_route(abq, oracle, cuda):
+    """W2A6 at a full prefill size (M=2048, N=11008, K=4096): blocks of 16 rows of the tcgen05 result equal, bit for bit,
+    the mma.sync decode route on the same rows and the oracle's product of the code matrices."""
+    M, N, K, p, q = 2048, 11008, 4096, 6, 2
+    rng = np.random.default_rng(2048)
+    x, w = rand_codes(rng, M, K, p, True), rand_codes(rng, N, K, q, False)
+    wp = planes_dev(oracle, w, q)
+    got, _ = run_gemm(abq, planes_dev(oracle, x, p), wp, M, N, K, x_bits=p, w_bits=q, x_signed=True, w_signed=False, route=abq.ROUTE_I8_UMMA)
+    for r0 in (0, 1008, 2032):
+        rows = slice(r0, r0 + 16)
+        small, _ = run_gemm(abq, planes_dev(oracle, x[rows], p), wp, 16, N, K, x_bits=p, w_bits=q, x_signed=True, w_signed=False,
+                            route=abq.ROUTE_I8_MMA)
+        assert np.array_equal(got[rows], small)
+        assert np.array_equal(small, oracle.gemm_values_blas(x[rows], w))
+    # linearity over all rows: row sums of the result = (sum of the token codes) x W
+    total = oracle.gemm_values_blas(x.sum(axis=0, dtype=np.int64)[None, :].astype(np.int64), w.astype(np.int64))
+    assert np.array_equal(got.astype(np.int64).sum(axis=0)[None, :], total)
