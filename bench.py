@@ -359,6 +359,54 @@ WORKLOAD = ("decode sweep (BASELINE configs[1]): W{2,3,4}A8 x M{1,4,16} x (N,K) 
             "{(4096,4096),(12288,4096),(11008,4096),(4096,11008)}, g128 fp16 scale + u8 zero, fp16 out")
 
 
+REF_GPU_CASES = [(1, 1, 4096, 4096), (1, 1, 12288, 4096), (1, 1, 11008, 4096), (3, 8, 12288, 4096)]  # (kernel id, M, N, K), unsigned W2A8
+
+
+def reference_gpu_kernels():
+    """Device time of the reference's own W2A8 GPU kernels (the two tiles its FasterTransformer wrapper hard-codes,
+    compiled from its headers into oracle/_ref/libabq_ref_gpu.so) on sweep shapes: int32 output, no scales (it has
+    none), weight copies rotating so that no launch finds its planes in L2, one CUDA graph of all launches."""
+    from oracle import oracle as O
+    try:
+        import torch
+    except ImportError:
+        return None
+    if not (O.ref_gpu_available() and torch.cuda.is_available()):
+        return None
+    rng = np.random.default_rng(3)
+    rows = []
+    for (cfg, M, N, K) in REF_GPU_CASES:
+        p, q, signed = O.ref_gpu_config(cfg)
+        copies = max(2, int(160e6 // (q * N * K // 8)) + 1)
+        xp = torch.from_numpy(O.pack(rng.integers(0, 1 << p, size=(M, K), dtype=np.int32), p).view(np.int32)).cuda()
+        base = torch.from_numpy(O.pack(rng.integers(0, 1 << q, size=(N, K), dtype=np.int32), q).view(np.int32)).cuda()
+        ws = [base] + [torch.roll(base, c, dims=1) for c in range(1, copies)]
+        out = torch.empty((M, N), dtype=torch.int32, device="cuda")
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            O.ref_gpu_gemm(cfg, xp.data_ptr(), ws[0].data_ptr(), M, N, K, out.data_ptr(), 1, side.cuda_stream)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for w in ws:
+                    O.ref_gpu_gemm(cfg, xp.data_ptr(), w.data_ptr(), M, N, K, out.data_ptr(), 1, side.cuda_stream)
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (3 * copies)
+        nbytes = q * N * K // 8 + p * M * K // 8 + 4 * M * N
+        rows.append({"kernel": O.REF_GPU_CONFIGS[cfg], "M": M, "N": N, "K": K, "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
+                     "TOPS": round(2 * M * N * K / us / 1e6, 3)})
+        del ws, base
+    return rows
+
+
 def run_reference(args, rank, world):
     """`--impl reference`: the reference's own CPU implementation of the path on the host cores."""
     if rank != 0:
@@ -380,6 +428,9 @@ def run_reference(args, rank, world):
             "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     line["cpu_baseline"]["value"] = value
+    gpu_rows = reference_gpu_kernels()  # context only: the arm's value stays the reference's CPU implementation
+    if gpu_rows:
+        line["reference_gpu_kernels"] = gpu_rows
     print(json.dumps(line))
 
 

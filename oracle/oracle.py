@@ -19,6 +19,7 @@ import numpy as np
 _HERE = Path(__file__).resolve().parent
 _LIB_PATH = _HERE / "_build" / "libabq_oracle.so"
 _REF_PATH = _HERE / "_ref" / "libabq_ref.so"
+_REF_GPU_PATH = _HERE / "_ref" / "libabq_ref_gpu.so"
 
 _i32p = ctypes.POINTER(ctypes.c_int32)
 _u32p = ctypes.POINTER(ctypes.c_uint32)
@@ -34,6 +35,8 @@ def build(force: bool = False) -> None:
     ref_root = os.environ.get("ABQ_REFERENCE_ROOT", "/root/reference")
     if os.path.isdir(os.path.join(ref_root, "engine")) and (force or not _REF_PATH.exists()):
         subprocess.run(["make", "-C", str(_HERE), "ref", f"REF={ref_root}"], check=True, capture_output=True)
+    if os.path.isdir(os.path.join(ref_root, "engine")) and (force or not _REF_GPU_PATH.exists()):
+        subprocess.run(["make", "-C", str(_HERE), "refgpu", f"REF={ref_root}"], check=True, capture_output=True)
 
 
 _lib = None
@@ -69,6 +72,49 @@ def lib() -> ctypes.CDLL:
 
 def ref_available() -> bool:
     return _REF_PATH.exists()
+
+
+# ---- the reference's own GPU kernels (ref_gpu.cu): configurations by id
+REF_GPU_CONFIGS = {
+    0: "AqBMMA W2A8 signed   cta<1,48,512> warp<8,24,128> mma<8,8,128> 4 stages (FasterTransformer, M == 1)",
+    1: "AqBMMA W2A8 unsigned cta<1,48,512> warp<8,24,128> mma<8,8,128> 4 stages (FasterTransformer, M == 1)",
+    2: "AqBMMA W2A8 signed   cta<8,48,256> warp<32,48,128> mma<8,8,128> 5 stages (FasterTransformer, M > 1)",
+    3: "AqBMMA W2A8 unsigned cta<8,48,256> warp<32,48,128> mma<8,8,128> 5 stages (FasterTransformer, M > 1)",
+    4: "AqBMMA W4A4 signed   cta<2,32,256> warp<8,64,128> mma<8,8,128> 2 stages (engine search space)",
+}
+_ref_gpu = None
+
+
+def ref_gpu_available() -> bool:
+    return _REF_GPU_PATH.exists()
+
+
+def ref_gpu() -> ctypes.CDLL:
+    global _ref_gpu
+    if _ref_gpu is None:
+        L = ctypes.CDLL(str(_REF_GPU_PATH))
+        L.abq_ref_gpu_gemm.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                       ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        L.abq_ref_gpu_gemm.restype = ctypes.c_int
+        L.abq_ref_gpu_config.argtypes = [ctypes.c_int] + [ctypes.POINTER(ctypes.c_int)] * 3
+        L.abq_ref_gpu_config.restype = ctypes.c_int
+        _ref_gpu = L
+    return _ref_gpu
+
+
+def ref_gpu_config(cfg: int):
+    """(x_bits, w_bits, signed) of a reference GPU kernel configuration."""
+    a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    if not ref_gpu().abq_ref_gpu_config(cfg, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)):
+        raise KeyError(cfg)
+    return a.value, b.value, bool(c.value)
+
+
+def ref_gpu_gemm(cfg: int, x_planes_ptr: int, w_planes_ptr: int, M: int, N: int, K: int, out_ptr: int, repeats: int = 1, stream: int = 0):
+    """Launch the reference's kernel `cfg` on device pointers (int32 out [M][N]); raises on its own refusal."""
+    rc = ref_gpu().abq_ref_gpu_gemm(cfg, x_planes_ptr, w_planes_ptr, M, N, K, out_ptr, repeats, stream)
+    if rc != 0:
+        raise RuntimeError(f"reference GPU kernel {cfg}: error {rc}")
 
 
 def ref() -> ctypes.CDLL:
