@@ -137,7 +137,7 @@ size_t abq_gemm_workspace_bytes(int M, int N, int K, int x_bits, int w_bits, int
     (void)x_bits;
     (void)w_bits;
     size_t need = 0;
-    if ((route == ABQ_ROUTE_AUTO || route == ABQ_ROUTE_I8_MMA) && M <= 16)
+    if (route == ABQ_ROUTE_AUTO || route == ABQ_ROUTE_I8_MMA) // AUTO may take this route at any M (per-group scales)
         need = decode_workspace_bytes(M, N, K);
     if (route == ABQ_ROUTE_I8_UMMA || (route == ABQ_ROUTE_AUTO && M > 16)) {
         size_t u = umma_workspace_bytes(M, N, K);
@@ -157,7 +157,8 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
         return s;
     int route = params->route;
     if (route == ABQ_ROUTE_AUTO)
-        route = params->M <= 16 ? ABQ_ROUTE_I8_MMA : ABQ_ROUTE_I8_UMMA;
+        // per-group scales need the accumulator per group: only the mma.sync route folds them (16 rows per launch)
+        route = params->M <= 16 || params->scale_mode == ABQ_SCALE_GROUP ? ABQ_ROUTE_I8_MMA : ABQ_ROUTE_I8_UMMA;
     switch (route) {
     case ABQ_ROUTE_B1_MMA: s = b1_plan(state); break;
     case ABQ_ROUTE_I8_MMA: s = decode_plan(state, clear_counters); break;

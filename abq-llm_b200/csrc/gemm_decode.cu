@@ -48,7 +48,8 @@ struct DecodeArgs {
     int split;             // warps sharing one tile
     int stages_per_split;  // stages per warp of a tile
     int ring;              // TMA stages per warp
-    const uint32_t *X;     // activation planes [x_bits][M][K/32]
+    const uint32_t *X;     // activation planes [x_bits][rows][K/32], first row of this launch
+    size_t x_plane_words;  // words between two planes (all rows of the operand, not only the M of this launch)
     int x_bits, x_signed;
     int *counters;         // one per tile (slices > 1), zero before the launch, left zero after it
     int *partials;         // [slice][tile][token][16 rows] int32 or fp32 bit patterns (slices > 1)
@@ -100,7 +101,7 @@ __device__ __forceinline__ void build_records(const DecodeArgs &a, uint8_t *rec_
     const int KW = a.K >> 5;
     const int words = n_groups * 4;
     const int items = MT * 8 * words;
-    const size_t plane = (size_t)a.M * KW;
+    const size_t plane = a.x_plane_words;
     for (int idx = threadIdx.x; idx < items; idx += NW * 32) {
         const int m = idx / words, kwl = idx - m * words;
         uint32_t r[8];
@@ -540,8 +541,9 @@ static int device_sms()
 static void workspace_layout(int M, int N, size_t *off_partials, size_t *total)
 {
     const int tiles = (N + 15) / 16;
+    const int rows = M < 16 ? M : 16; // taller problems run as launches of 16 rows, one after the other
     *off_partials = ((size_t)tiles * 4 + 255) & ~(size_t)255;
-    *total = *off_partials + (size_t)kDecodeMaxSlices * tiles * M * 16 * 4;
+    *total = *off_partials + (size_t)kDecodeMaxSlices * tiles * rows * 16 * 4;
 }
 
 size_t decode_workspace_bytes(int M, int N, int K)
@@ -558,13 +560,15 @@ size_t decode_workspace_bytes(int M, int N, int K)
 static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
 {
     const int Q = p.w_bits;
-    L->MT = p.M <= 8 ? 1 : 2;
+    const int rows = p.M < 16 ? p.M : 16; // rows per launch
+    L->MT = rows <= 8 ? 1 : 2;
     L->tiles = (p.N + 15) / 16;
     L->total_groups = p.K / 128;
     const int total_stages = (L->total_groups + 3) / 4;
     const int sms = device_sms();
     const int stage_bytes = Q * 1024;
     const int rec = decode_record_bytes(L->MT);
+    (void)rows;
     const size_t budget = 226 * 1024;
     const int forced_slices = env_int("ABQ_DECODE_SLICES", 0);
     // 16 warps per CTA when two ring stages per warp fit, else 8 (wide weights); the smallest K split that fits
@@ -674,8 +678,6 @@ static cudaError_t launch_q(const abq_gemm_state *st, const DecodeArgs &args, in
 abq_status decode_plan(abq_gemm_state *st, bool clear_counters)
 {
     const abq_gemm_params &p = st->p;
-    if (p.M > 16)
-        return ABQ_ERR_UNSUPPORTED;
     if (p.scale_mode == ABQ_SCALE_GROUP && (p.group_size % 128 != 0))
         return ABQ_ERR_UNSUPPORTED;
     DecodeLayout L;
@@ -722,7 +724,7 @@ cudaError_t decode_clear_counters(const abq_gemm_state *st, cudaStream_t stream)
 cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
 {
     const abq_gemm_params &p = st->p;
-    const int MT = p.M <= 8 ? 1 : 2;
+    const int MT = (p.M < 16 ? p.M : 16) <= 8 ? 1 : 2; // as planned: by the rows of a full launch
     size_t off_partials, total;
     workspace_layout(p.M, p.N, &off_partials, &total);
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
@@ -740,6 +742,7 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.stages_per_split = (a.stages_per_slice + a.split - 1) / a.split;
     a.ring = st->tile[1];
     a.X = reinterpret_cast<const uint32_t *>(p.X);
+    a.x_plane_words = (size_t)p.M * (p.K / 32);
     a.x_bits = p.x_bits;
     a.x_signed = p.x_signed;
     a.counters = nullptr;
@@ -762,17 +765,30 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.w_signed = p.w_signed;
     a.status = p.status_word;
     const bool xu8 = !p.x_signed && p.x_bits == 8;
-    switch (p.w_bits) {
-    case 1: return launch_q<1>(st, a, MT, xu8, stream);
-    case 2: return launch_q<2>(st, a, MT, xu8, stream);
-    case 3: return launch_q<3>(st, a, MT, xu8, stream);
-    case 4: return launch_q<4>(st, a, MT, xu8, stream);
-    case 5: return launch_q<5>(st, a, MT, xu8, stream);
-    case 6: return launch_q<6>(st, a, MT, xu8, stream);
-    case 7: return launch_q<7>(st, a, MT, xu8, stream);
-    case 8: return launch_q<8>(st, a, MT, xu8, stream);
-    default: return cudaErrorInvalidValue;
+    // M > 16: one launch per 16 rows, in stream order (they share the workspace); the weights of the later launches
+    // come out of L2 where they fit
+    const size_t out_row_bytes = (size_t)p.N * (p.out_dtype == ABQ_OUT_INT32 ? 4 : 2);
+    for (int m0 = 0; m0 < p.M; m0 += 16) {
+        a.M = p.M - m0 < 16 ? p.M - m0 : 16;
+        a.X = reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
+        a.D = reinterpret_cast<uint8_t *>(p.D) + (size_t)m0 * out_row_bytes;
+        a.x_scale = p.x_scale ? p.x_scale + m0 : nullptr;
+        cudaError_t e;
+        switch (p.w_bits) {
+        case 1: e = launch_q<1>(st, a, MT, xu8, stream); break;
+        case 2: e = launch_q<2>(st, a, MT, xu8, stream); break;
+        case 3: e = launch_q<3>(st, a, MT, xu8, stream); break;
+        case 4: e = launch_q<4>(st, a, MT, xu8, stream); break;
+        case 5: e = launch_q<5>(st, a, MT, xu8, stream); break;
+        case 6: e = launch_q<6>(st, a, MT, xu8, stream); break;
+        case 7: e = launch_q<7>(st, a, MT, xu8, stream); break;
+        case 8: e = launch_q<8>(st, a, MT, xu8, stream); break;
+        default: e = cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess)
+            return e;
     }
+    return cudaSuccess;
 }
 
 } // namespace abq

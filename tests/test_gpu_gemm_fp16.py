@@ -51,7 +51,8 @@ def test_per_channel(abq, oracle, cuda, M, N, K, q, with_zero):
 
 
 @pytest.mark.parametrize("M,N,K,q,group", [(1, 4096, 4096, 2, 128), (4, 512, 4096, 3, 128), (16, 320, 11008, 4, 128), (8, 128, 2048, 4, 256),
-                                           (3, 64, 1536, 2, 384), (16, 4096, 4096, 4, 128)])
+                                           (3, 64, 1536, 2, 384), (16, 4096, 4096, 4, 128),
+                                           (40, 320, 1024, 4, 128), (100, 512, 4096, 2, 128), (33, 96, 11008, 3, 256)])
 @pytest.mark.parametrize("w_signed", [False, True])
 def test_per_group(abq, oracle, cuda, M, N, K, q, group, w_signed):
     rng = np.random.default_rng(N + K + q + group)
@@ -62,6 +63,7 @@ def test_per_group(abq, oracle, cuda, M, N, K, q, group, w_signed):
     wz = rng.integers(0, 1 << q, size=(N, G)).astype(np.uint8)
     got, st = run_gemm(abq, planes_dev(oracle, x, 8), planes_dev(oracle, w, q), M, N, K, x_bits=8, w_bits=q, x_signed=True,
                        w_signed=w_signed, out_fp16=True, scale_mode=abq.SCALE_GROUP, group_size=group, w_scale=dev(ws), w_zero=dev(wz),
-                       route=abq.ROUTE_I8_MMA)
+                       route=abq.ROUTE_I8_MMA if M <= 16 else abq.ROUTE_AUTO)  # taller: 16 rows per launch, chosen automatically
+    assert st.route == abq.ROUTE_I8_MMA
     ref = oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), None, group)
     check_close(got, ref)

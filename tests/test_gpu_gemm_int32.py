@@ -21,6 +21,8 @@ DECODE_CASES = [
     (1, 4096, 4096, 8, 2, True, False),
     (16, 1024, 11008, 8, 4, True, True),
     (3, 200, 256, 1, 1, False, False),
+    (37, 200, 640, 8, 3, True, False),      # taller than one launch of the mma.sync route: 16 rows per launch
+    (48, 64, 11008, 8, 4, True, True),
 ]
 
 
