@@ -11,6 +11,7 @@ ROUTE_AUTO, ROUTE_B1_MMA, ROUTE_I8_MMA, ROUTE_I8_UMMA = 0, 1, 2, 3
 OUT_INT32, OUT_FP16 = 0, 1
 SCALE_NONE, SCALE_TENSOR_COMPAT, SCALE_CHANNEL, SCALE_GROUP = 0, 1, 2, 3
 FLAG_PDL = 1
+FLAG_WEIGHTS_PREPARED = 2
 
 _PKG = Path(__file__).resolve().parent
 
@@ -71,6 +72,7 @@ def lib() -> ctypes.CDLL:
         L.abq_gemm_workspace_bytes.argtypes = [ctypes.c_int] * 6
         L.abq_gemm_init.argtypes = [ctypes.POINTER(GemmParams), ctypes.POINTER(GemmState)]
         L.abq_gemm_exec.argtypes = [ctypes.POINTER(GemmState), ctypes.c_void_p]
+        L.abq_gemm_prepare_weights.argtypes = [ctypes.POINTER(GemmState), ctypes.c_void_p]
         L.abq_gemm.argtypes = [ctypes.POINTER(GemmParams), ctypes.c_void_p]
         L.abq_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmParams), ctypes.c_void_p]
         L.abq_pack_int32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
@@ -150,6 +152,10 @@ def gemm_init(params: GemmParams) -> GemmState:
 
 def gemm_exec(state: GemmState, stream=None) -> None:
     _check(lib().abq_gemm_exec(ctypes.byref(state), _stream(stream)), "abq_gemm_exec")
+
+
+def gemm_prepare_weights(state: GemmState, stream=None) -> None:
+    _check(lib().abq_gemm_prepare_weights(ctypes.byref(state), _stream(stream)), "abq_gemm_prepare_weights")
 
 
 def gemm(params: GemmParams, stream=None) -> None:

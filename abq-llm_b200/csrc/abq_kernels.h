@@ -37,6 +37,7 @@ cudaError_t b1_launch(const abq_gemm_state *st, cudaStream_t stream);
 
 // ---- gemm_umma.cu (route ABQ_ROUTE_I8_UMMA)
 abq_status umma_plan(abq_gemm_state *st);
+cudaError_t umma_prepare_weights(const abq_gemm_state *st, cudaStream_t stream);
 cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream);
 size_t umma_workspace_bytes(int M, int N, int K);
 

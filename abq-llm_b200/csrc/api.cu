@@ -196,6 +196,20 @@ abq_status abq_gemm_init(const abq_gemm_params *params, abq_gemm_state *state)
     return plan_gemm(params, state, true);
 }
 
+abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_stream_t stream)
+{
+    if (!state || !state->init_success)
+        return ABQ_ERR_NOT_INITIALIZED;
+    if (state->route != ABQ_ROUTE_I8_UMMA)
+        return ABQ_OK;
+    cudaError_t e = umma_prepare_weights(state, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        set_last_cuda_error(e);
+        return ABQ_ERR_CUDA;
+    }
+    return ABQ_OK;
+}
+
 abq_status abq_gemm(const abq_gemm_params *params, abq_stream_t stream)
 {
     abq_gemm_state st;

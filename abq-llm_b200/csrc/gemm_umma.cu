@@ -467,14 +467,27 @@ static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cud
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, args);
 }
 
+cudaError_t umma_prepare_weights(const abq_gemm_state *st, cudaStream_t stream)
+{
+    const abq_gemm_params &p = st->p;
+    size_t off_w, off_sum, total;
+    umma_layout(p.M, p.N, p.K, &off_w, &off_sum, &total);
+    return unpack_i8(reinterpret_cast<const uint32_t *>(p.W), reinterpret_cast<uint8_t *>(p.workspace) + off_w, p.N, p.K, p.w_bits, p.w_signed,
+                     stream);
+}
+
 cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
 {
     const abq_gemm_params &p = st->p;
     size_t off_w, off_sum, total;
     umma_layout(p.M, p.N, p.K, &off_w, &off_sum, &total);
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
-    cudaError_t e = unpack_pair_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.x_bits, p.x_signed,
-                                   reinterpret_cast<const uint32_t *>(p.W), ws + off_w, p.N, p.w_bits, p.w_signed, p.K, stream);
+    cudaError_t e;
+    if (p.flags & ABQ_FLAG_WEIGHTS_PREPARED) // the weight codes are in place: expand the activations only
+        e = unpack_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.K, p.x_bits, p.x_signed, stream);
+    else
+        e = unpack_pair_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.x_bits, p.x_signed, reinterpret_cast<const uint32_t *>(p.W),
+                           ws + off_w, p.N, p.w_bits, p.w_signed, p.K, stream);
     if (e != cudaSuccess)
         return e;
     UmmaArgs a;

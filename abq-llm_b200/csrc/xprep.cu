@@ -89,6 +89,7 @@ template <int BITS>
 __global__ void __launch_bounds__(256) unpack_i8_kernel(const uint32_t *__restrict__ planes, uint32_t *__restrict__ out, long L,
                                                         int is_signed)
 {
+    pdl_launch_dependents(); // a GEMM kernel launched programmatically behind this one may start its set-up
     unpack_run<BITS>(planes, out, L, (long)blockIdx.x * (256 * kUnpackRuns) + threadIdx.x, is_signed);
 }
 

@@ -68,7 +68,11 @@ typedef enum abq_route {
 } abq_route;
 
 enum {
-    ABQ_FLAG_PDL = 1 /* launch with programmatic dependent launch so that consecutive GEMMs overlap */
+    ABQ_FLAG_PDL = 1, /* launch with programmatic dependent launch so that consecutive GEMMs overlap */
+    /* Route I8_UMMA only: the int8 expansion of W already sits in this plan's workspace (abq_gemm_prepare_weights
+     * put it there and nothing has overwritten it since): abq_gemm_exec expands the activations only.  For weights
+     * that stay the same from call to call, with a workspace of their own. */
+    ABQ_FLAG_WEIGHTS_PREPARED = 2
 };
 
 /*
@@ -161,6 +165,13 @@ ABQ_API abq_status abq_pack_int4(const void *in, void *planes, int rows, int K, 
  */
 ABQ_API abq_status abq_quantize_pack_half(const void *in_half, const float *scale, void *planes, int rows, int K,
                                   int bits, int mode, abq_stream_t stream);
+
+/*
+ * Expand the weight planes of a planned GEMM into its workspace once, for plans with ABQ_FLAG_WEIGHTS_PREPARED
+ * (a no-op returning ABQ_OK on routes that read the planes directly).  No reference counterpart: the reference
+ * multiplies the planes themselves.
+ */
+ABQ_API abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_stream_t stream);
 
 /* Bit-planes -> int8 codes, row-major [rows][K] (two's complement for signed; unsigned 8-bit codes are
  * stored as uint8).  Used by route B; exported because weight planes can be expanded once and cached. */

@@ -120,3 +120,27 @@ def test_full_size_prefill_rows_match_decode_route(abq, oracle, cuda):
     # linearity over all rows: row sums of the result = (sum of the token codes) x W
     total = oracle.gemm_values_blas(x.sum(axis=0, dtype=np.int64)[None, :].astype(np.int64), w.astype(np.int64))
     assert np.array_equal(got.astype(np.int64).sum(axis=0)[None, :], total)
+
+
+def test_prepared_weights_give_the_same_result(abq, oracle, cuda):
+    """ABQ_FLAG_WEIGHTS_PREPARED: the weight codes are expanded once into the plan's workspace, later calls expand the
+    activations only (new activations each call, same weights)."""
+    import torch
+    from abq_llm_b200 import binding as B
+    M, N, K, p, q = 300, 1000, 1152, 8, 3
+    rng = np.random.default_rng(9)
+    w = rand_codes(rng, N, K, q, False)
+    wp = planes_dev(oracle, w, q)
+    ws = torch.empty(abq.gemm_workspace_bytes(M, N, K, p, q, abq.ROUTE_I8_UMMA), dtype=torch.uint8, device="cuda")
+    out = torch.empty((M, N), dtype=torch.int32, device="cuda")
+    xbuf = torch.empty((p, M, K // 32), dtype=torch.int32, device="cuda")
+    prm = B.make_params(M, N, K, xbuf, wp, out, x_bits=p, w_bits=q, x_signed=True, w_signed=False, route=abq.ROUTE_I8_UMMA,
+                        flags=abq.FLAG_WEIGHTS_PREPARED, workspace=ws)
+    st = abq.gemm_init(prm)
+    abq.gemm_prepare_weights(st)
+    for i in range(3):
+        x = rand_codes(rng, M, K, p, True)
+        xbuf.copy_(planes_dev(oracle, x, p))
+        abq.gemm_exec(st)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), oracle.gemm_values_blas(x, w)), f"call {i}"
