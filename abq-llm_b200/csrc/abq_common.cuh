@@ -209,6 +209,23 @@ __device__ __forceinline__ void planes_to_bytes(const uint32_t (&p)[BITS], bool 
     }
 }
 
+// The inverse: eight registers of code bytes in the layout above -> the BITS plane words (bits above BITS ignored).
+template <int BITS>
+__device__ __forceinline__ void bytes_to_planes(const uint32_t (&r)[8], uint32_t (&p)[BITS])
+{
+#pragma unroll
+    for (int b = 0; b < BITS; ++b) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            // bit (8y + b) of r[s] goes to bit (8y + s) of the plane word
+            const uint32_t t = (s >= b) ? (r[s] << (s - b)) : (r[s] >> (b - s));
+            w |= t & (0x01010101u << s);
+        }
+        p[b] = w;
+    }
+}
+
 // 8-bit lanes: (v ^ m) - m for every byte (sign extension of a BITS-wide two's complement field).
 __device__ __forceinline__ uint32_t sign_extend_bytes(uint32_t v, int bits)
 {

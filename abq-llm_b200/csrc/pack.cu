@@ -3,51 +3,51 @@
 // Replaces the reference's `pack` / `pack4` (engine/common/pack.cu:18-64) and the FasterTransformer
 // wrapper's `pack_half` (fastertransformer/.../abqgemm/abq_gemm_wrapper.cu:29-54).  The reference
 // launches one block row per plane, so the input is re-read (and for fp16 re-quantised) once per
-// plane; here every value is read once: a warp loads 32 consecutive codes with one coalesced
-// request, one __ballot_sync per plane turns them into a plane word, and the words of 32 consecutive
-// runs are collected across lanes so that every plane is written with full 128-byte stores.
+// plane; here every value is read once: a thread loads one run of 32 consecutive values with
+// 16-byte loads, quantises them, collects the code bytes in eight registers and transposes them into
+// the plane words in registers (two operations per byte register and plane); consecutive threads
+// write consecutive words of every plane.  (A ballot per plane and run, the first version, was bound
+// by the vote instruction: 15 % of the HBM rate for 8-bit activations.)
 #include "abq_common.cuh"
 
 namespace abq {
 
 constexpr int kPackThreads = 256;
 
-// One warp per 32 consecutive output words (= 1024 codes).  `L` = rows * K / 32 words per plane.
+// Place the low byte of code j (element index in the run) where bytes_to_planes expects it: byte y of r[s] holds
+// element 31 - 8y - s.
+__device__ __forceinline__ void put_code(uint32_t (&r)[8], int j, uint32_t code)
+{
+    const int pos = 31 - j, s = pos & 7, y = pos >> 3;
+    r[s] |= (code & 0xffu) << (8 * y);
+}
+
+// One thread per output word (= 32 codes).  `L` = rows * K / 32 words per plane.
 template <int BITS>
 __global__ void __launch_bounds__(kPackThreads) pack_int32_kernel(const int32_t *__restrict__ in, uint32_t *__restrict__ planes,
                                                                   long L)
 {
-    const int lane = threadIdx.x & 31;
-    const long warp = (long)blockIdx.x * (kPackThreads / 32) + (threadIdx.x >> 5);
-    const long w0 = warp * 32;
-    if (w0 >= L)
+    const long idx = (long)blockIdx.x * kPackThreads + threadIdx.x;
+    if (idx >= L)
         return;
-    const int nwords = (int)min((long)32, L - w0);
-    uint32_t keep[BITS];
+    const int4 *src = reinterpret_cast<const int4 *>(in + idx * 32);
+    int4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        v[i] = __ldg(src + i);
+    uint32_t r[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        put_code(r, 4 * i + 0, (uint32_t)v[i].x);
+        put_code(r, 4 * i + 1, (uint32_t)v[i].y);
+        put_code(r, 4 * i + 2, (uint32_t)v[i].z);
+        put_code(r, 4 * i + 3, (uint32_t)v[i].w);
+    }
+    uint32_t p[BITS];
+    bytes_to_planes<BITS>(r, p);
 #pragma unroll
     for (int b = 0; b < BITS; ++b)
-        keep[b] = 0;
-    const int32_t *src = in + w0 * 32;
-    for (int c = 0; c < nwords; c += 4) {
-        int32_t v[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            v[u] = (c + u < nwords) ? __ldg(src + (long)(c + u) * 32 + lane) : 0;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-#pragma unroll
-            for (int b = 0; b < BITS; ++b) {
-                uint32_t word = __brev(__ballot_sync(0xffffffffu, (v[u] >> b) & 1));
-                if (lane == c + u)
-                    keep[b] = word;
-            }
-        }
-    }
-    if (lane < nwords) {
-#pragma unroll
-        for (int b = 0; b < BITS; ++b)
-            planes[(long)b * L + w0 + lane] = keep[b];
-    }
+        planes[(long)b * L + idx] = p[b];
 }
 
 // Nibble-packed 4-bit codes: one thread per output word, 16-byte load (first element = top nibble).
@@ -75,8 +75,7 @@ __global__ void __launch_bounds__(kPackThreads) pack_int4_kernel(const uint4 *__
     }
 }
 
-// fp16 -> code -> planes.  A warp covers 64 consecutive halves per step with one half2 load per lane;
-// two shuffles hand lane l the elements l and 32+l, so that one ballot yields one finished plane word.
+// fp16 -> code -> planes, one thread per run of 32 halves (four 16-byte loads).
 // MODE 0: code = (int)(h * half(scale[0])) (fp16 multiply, truncation, no clamp);
 // MODE 1: code = clamp(rint(float(h) * (1 / scale[row])), -2^(bits-1), 2^(bits-1) - 1).
 template <int BITS, int MODE>
@@ -84,61 +83,45 @@ __global__ void __launch_bounds__(kPackThreads) quantize_pack_half_kernel(const 
                                                                           const float *__restrict__ scale,
                                                                           uint32_t *__restrict__ planes, long L, int kw_per_row)
 {
-    const int lane = threadIdx.x & 31;
-    const long warp = (long)blockIdx.x * (kPackThreads / 32) + (threadIdx.x >> 5);
-    const long w0 = warp * 32;
-    if (w0 >= L)
+    const long idx = (long)blockIdx.x * kPackThreads + threadIdx.x;
+    if (idx >= L)
         return;
-    const int nwords = (int)min((long)32, L - w0); // always even: K/32 is a multiple of 4
-    uint32_t keep[BITS];
+    const uint4 *src = reinterpret_cast<const uint4 *>(in + idx * 32);
+    uint4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        v[i] = __ldg(src + i);
+    const __half hscale = (MODE == 0) ? __float2half(__ldg(scale)) : __half();
+    const float inv = (MODE == 1) ? __fdiv_rn(1.0f, __ldg(scale + idx / kw_per_row)) : 0.f;
+    const int qmin = -(1 << (BITS - 1)), qmax = (1 << (BITS - 1)) - 1;
+    uint32_t r[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w[4] = { v[i].x, v[i].y, v[i].z, v[i].w };
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const __half h = __ushort_as_half((unsigned short)(w[e >> 1] >> ((e & 1) * 16)));
+            int q;
+            if (MODE == 0) {
+                q = __half2int_rz(__hmul(h, hscale));
+            } else {
+                q = __float2int_rn(__fmul_rn(__half2float(h), inv));
+                q = max(qmin, min(qmax, q));
+            }
+            put_code(r, 8 * i + e, (uint32_t)q);
+        }
+    }
+    uint32_t p[BITS];
+    bytes_to_planes<BITS>(r, p);
 #pragma unroll
     for (int b = 0; b < BITS; ++b)
-        keep[b] = 0;
-    const __half hscale = (MODE == 0) ? __float2half(__ldg(scale)) : __half();
-    const int qmin = -(1 << (BITS - 1)), qmax = (1 << (BITS - 1)) - 1;
-    const __half2 *src = reinterpret_cast<const __half2 *>(in + w0 * 32);
-    for (int c = 0; c < nwords; c += 2) {
-        const uint32_t raw = __ldg(reinterpret_cast<const unsigned int *>(src) + (long)c * 16 + lane);
-        const uint32_t ra = __shfl_sync(0xffffffffu, raw, lane >> 1);
-        const uint32_t rb = __shfl_sync(0xffffffffu, raw, 16 + (lane >> 1));
-        const uint16_t ha = (lane & 1) ? (uint16_t)(ra >> 16) : (uint16_t)(ra & 0xffffu);
-        const uint16_t hb = (lane & 1) ? (uint16_t)(rb >> 16) : (uint16_t)(rb & 0xffffu);
-        int code[2];
-        const uint16_t hv[2] = { ha, hb };
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const __half h = __ushort_as_half(hv[u]);
-            if (MODE == 0) {
-                code[u] = __half2int_rz(__hmul(h, hscale));
-            } else {
-                const long row = (w0 + c + u) / kw_per_row;
-                const float inv = __fdiv_rn(1.0f, __ldg(scale + row));
-                int q = __float2int_rn(__fmul_rn(__half2float(h), inv));
-                code[u] = max(qmin, min(qmax, q));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-#pragma unroll
-            for (int b = 0; b < BITS; ++b) {
-                uint32_t word = __brev(__ballot_sync(0xffffffffu, (code[u] >> b) & 1));
-                if (lane == c + u)
-                    keep[b] = word;
-            }
-        }
-    }
-    if (lane < nwords) {
-#pragma unroll
-        for (int b = 0; b < BITS; ++b)
-            planes[(long)b * L + w0 + lane] = keep[b];
-    }
+        planes[(long)b * L + idx] = p[b];
 }
 
 template <int BITS>
 static cudaError_t launch_pack_int32(const int32_t *in, uint32_t *planes, long L, cudaStream_t stream)
 {
-    const long warps = (L + 31) / 32;
-    const unsigned blocks = (unsigned)((warps + kPackThreads / 32 - 1) / (kPackThreads / 32));
+    const unsigned blocks = (unsigned)((L + kPackThreads - 1) / kPackThreads);
     pack_int32_kernel<BITS><<<blocks, kPackThreads, 0, stream>>>(in, planes, L);
     return cudaGetLastError();
 }
@@ -147,8 +130,7 @@ template <int BITS>
 static cudaError_t launch_quant_half(const __half *in, const float *scale, uint32_t *planes, long L, int kw, int mode,
                                      cudaStream_t stream)
 {
-    const long warps = (L + 31) / 32;
-    const unsigned blocks = (unsigned)((warps + kPackThreads / 32 - 1) / (kPackThreads / 32));
+    const unsigned blocks = (unsigned)((L + kPackThreads - 1) / kPackThreads);
     if (mode == 0)
         quantize_pack_half_kernel<BITS, 0><<<blocks, kPackThreads, 0, stream>>>(in, scale, planes, L, kw);
     else

@@ -328,6 +328,74 @@ def prefill_leg(torch, abq, reps=10):
             "peak_source": "2 x MEASURED_PEAKS.json bf16_tflops" if peak else None, "cases": rows}
 
 
+def _time_calls(torch, fn, reps=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def routes_leg(torch, abq):
+    """The two formulations side by side on one decode and one prefill shape (int32 output, so that the numbers are the
+    contraction alone): route A = 1-bit mma.sync AND+POPC over the stacked planes as the reference does it, against the
+    int8 routes that the planner picks."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(11)
+    B = abq.binding
+    rows = []
+    for (q, p, M, N, K, fast) in [(2, 8, 1, 4096, 4096, abq.ROUTE_I8_MMA), (2, 8, 16, 4096, 4096, abq.ROUTE_I8_MMA),
+                                  (4, 4, 512, 4096, 4096, abq.ROUTE_I8_UMMA)]:
+        def planes_of(r, bits):
+            codes = torch.randint(0, 1 << bits, (r, K), dtype=torch.int32, device="cuda", generator=gen)
+            out = torch.empty((bits, r, K // 32), dtype=torch.int32, device="cuda")
+            abq.pack_int32(codes, out, r, K, bits)
+            return out
+        xp, wp = planes_of(M, p), planes_of(N, q)
+        out = torch.empty((M, N), dtype=torch.int32, device="cuda")
+        res = {}
+        for name, route in (("b1_mma", abq.ROUTE_B1_MMA), ("int8", fast)):
+            work = torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, p, q, route)), dtype=torch.uint8, device="cuda")
+            st = abq.gemm_init(B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=False, w_signed=False, route=route, workspace=work))
+            res[name] = _time_calls(torch, lambda: abq.gemm_exec(st), reps=5 if name == "b1_mma" else 20)
+        rows.append({"wxay": f"W{q}A{p}", "M": M, "N": N, "K": K, "us_route_a_b1_mma": round(res["b1_mma"], 1),
+                     "us_int8_route": round(res["int8"], 1), "int8_route": "I8_MMA" if fast == abq.ROUTE_I8_MMA else "I8_UMMA",
+                     "ratio": round(res["b1_mma"] / res["int8"], 1)})
+    return rows
+
+
+def pack_leg(torch, abq):
+    """The pack kernels against the HBM roofline: bytes read + planes written per launch over the launch time, on inputs
+    larger than L2 (a prefill batch of activations, a weight matrix)."""
+    peak, _ = measured_peaks()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    rows = []
+    M, K = 16384, 8192  # 268 MB of fp16 activations, 537 MB of int32 codes
+    x16 = (torch.randn((M, K), device="cuda", generator=gen) * 3).to(torch.float16)
+    scale = torch.full((1,), 8.0, dtype=torch.float32, device="cuda")
+    for bits in (8, 4):
+        planes = torch.empty((bits, M, K // 32), dtype=torch.int32, device="cuda")
+        us = _time_calls(torch, lambda: abq.quantize_pack_half(x16, scale, planes, M, K, bits, 0))
+        nbytes = 2 * M * K + bits * M * K // 8
+        rows.append({"kernel": f"quantize_pack_half_kernel<{bits}>", "rows": M, "K": K, "us": round(us, 1), "GBps": round(nbytes / us / 1e3, 1),
+                     "frac_of_hbm": round(nbytes / us / 1e3 / peak, 3)})
+    del x16
+    codes = torch.randint(0, 16, (M, K), dtype=torch.int32, device="cuda", generator=gen)
+    for bits in (4, 2):
+        planes = torch.empty((bits, M, K // 32), dtype=torch.int32, device="cuda")
+        us = _time_calls(torch, lambda: abq.pack_int32(codes, planes, M, K, bits))
+        nbytes = 4 * M * K + bits * M * K // 8
+        rows.append({"kernel": f"pack_int32_kernel<{bits}>", "rows": M, "K": K, "us": round(us, 1), "GBps": round(nbytes / us / 1e3, 1),
+                     "frac_of_hbm": round(nbytes / us / 1e3 / peak, 3)})
+    return rows
+
+
 def cpu_baseline_sample(kind_pref: str, budget_s: float = 12.0):
     """The reference's CPU loop (`compute_ref`) on a bounded sample of the sweep: its W2A8, M=16, N=4096,
     K=4096 GEMM, repeated until about `budget_s` seconds of host time are spent; all host cores."""
@@ -534,6 +602,8 @@ def main():
         line["config"]["workload"] = f"single GEMM --shape {args.shape} (profiling aid, not the sweep)"
     if rank == 0 and world == 1 and not args.no_prefill and not args.shape and not args.only:
         line["prefill"] = prefill_leg(torch, abq)
+        line["routes"] = routes_leg(torch, abq)
+        line["pack"] = pack_leg(torch, abq)
     if args.detail and rank == 0:
         line["detail"] = per_config_detail(torch, abq, gemms)
     if rank == 0:
