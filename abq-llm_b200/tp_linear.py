@@ -1,0 +1,176 @@
+"""Tensor-parallel quantized linear layers of a LLaMA decoder block (host side).
+
+Mirrors how the reference's FasterTransformer fork shards the four linear layers of a block
+(LlamaDecoderLayerWeight.cc:378-400; TensorParallelGptContextAttentionLayer.cc:50-53,
+TensorParallelSiluFfnLayer.cc:53-57):
+
+* QKV, gate, up: **column parallel** -- every rank owns a slice of the output features (rows of every weight plane),
+  no communication;
+* O, down: **row parallel** -- every rank owns a slice of the input features (word columns of every weight plane),
+  produces a full ``[M, hidden]`` fp16 partial, and the partials are summed by an all-reduce.
+
+Bit-planes shard cleanly both ways; slices along K are whole 128-feature units (the pack / MMA granularity), dealt as
+evenly as possible (11008 = 86 units -> 22/22/21/21 for four ranks).  Activations are quantised with a static scale
+(the reference's quantiser, mode 0), so ranks need not agree on a per-token scale for row-parallel inputs; partial
+sums are reduced after dequantisation, in fp16, as FasterTransformer does.
+
+The arithmetic is injected (``backend``): the product backend is :class:`AbqBackend` (this library, CUDA only);
+tests drive the sharding logic with a numpy stand-in over ``gloo`` ranks.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence, Tuple
+
+
+def unit_ranges(total: int, parts: int, unit: int = 128) -> List[Tuple[int, int]]:
+    """[begin, end) of every part when ``total`` features are dealt in whole ``unit``-feature pieces, the first
+    ``total/unit % parts`` parts getting one piece more."""
+    if total % unit:
+        raise ValueError(f"{total} is not a multiple of {unit}")
+    units = total // unit
+    base, extra = divmod(units, parts)
+    out, at = [], 0
+    for r in range(parts):
+        n = (base + (1 if r < extra else 0)) * unit
+        out.append((at, at + n))
+        at += n
+    return out
+
+
+@dataclass
+class LinearSpec:
+    name: str
+    out_features: int
+    in_features: int
+    parallel: str  # "column" (split out_features) or "row" (split in_features, all-reduce after)
+
+
+def llama_block_specs(hidden: int, ffn: int) -> List[LinearSpec]:
+    """The four quantized GEMMs of a block as FasterTransformer runs them: fused QKV, O, fused gate+up, down."""
+    return [LinearSpec("qkv", 3 * hidden, hidden, "column"), LinearSpec("o", hidden, hidden, "row"),
+            LinearSpec("gate_up", 2 * ffn, hidden, "column"), LinearSpec("down", hidden, ffn, "row")]
+
+
+def shard_of(spec: LinearSpec, rank: int, world: int, unit: int = 128) -> Tuple[slice, slice]:
+    """(rows, columns) of the full [out_features][in_features] code matrix that ``rank`` owns."""
+    if spec.parallel == "column":
+        # fused layers (qkv, gate_up) are split per fused part so that every rank holds matching slices of each
+        parts = 3 if spec.name == "qkv" else (2 if spec.name == "gate_up" else 1)
+        per = spec.out_features // parts
+        b, e = unit_ranges(per, world, unit)[rank]  # the same ranges as the K split of the row-parallel layer that follows
+        rows = [i for p in range(parts) for i in range(p * per + b, p * per + e)]
+        return rows, slice(0, spec.in_features)
+    b, e = unit_ranges(spec.in_features, world, unit)[rank]
+    return slice(0, spec.out_features), slice(b, e)
+
+
+class TensorParallelBlockLinears:
+    """The linear layers of one decoder block on one rank.
+
+    ``backend.make_linear(codes, scale, zero, w_bits, group)`` returns an object with ``__call__(x_half) -> fp16``;
+    ``backend.all_reduce(t)`` sums over ranks in place; ``backend.glue`` supplies the elementwise stand-ins between the
+    GEMMs (attention itself is outside this path: the first third of the QKV output stands in for its result).
+    """
+
+    def __init__(self, backend, hidden: int, ffn: int, rank: int, world: int, weights: Sequence, w_bits: int, group: int = 0):
+        self.backend, self.hidden, self.ffn, self.rank, self.world = backend, hidden, ffn, rank, world
+        self.specs = llama_block_specs(hidden, ffn)
+        self.layers = {}
+        for spec, (codes, scale, zero) in zip(self.specs, weights):
+            rows, cols = shard_of(spec, rank, world)
+            c = codes[rows][:, cols]
+            if group:  # per-group parameters follow their K groups
+                gsl = slice(cols.start // group, cols.stop // group)
+                s, z = scale[rows][:, gsl], (None if zero is None else zero[rows][:, gsl])
+            else:      # per-channel parameters follow the rows (replicated for row-parallel layers)
+                s, z = scale[rows], (None if zero is None else zero[rows])
+            self.layers[spec.name] = backend.make_linear(c, s, z, w_bits, group)
+
+    def forward(self, x):
+        """x: fp16 [M][hidden], replicated on every rank.  Returns fp16 [M][hidden], replicated."""
+        be = self.backend
+        hl = self.layers["qkv"].out_features // 3
+        qkv = self.layers["qkv"](x)                          # [M][3 * hidden / world]
+        attn = be.glue_attention(qkv, hl)                    # [M][hidden / world]: this rank's heads
+        o = self.layers["o"](attn)                           # partial [M][hidden]
+        be.all_reduce(o)
+        h = be.glue_residual(x, o)
+        gu = self.layers["gate_up"](h)                       # [M][2 * ffn_local]
+        act = be.glue_swiglu(gu, self.layers["gate_up"].out_features // 2)
+        d = self.layers["down"](act)                         # partial [M][hidden]
+        be.all_reduce(d)
+        return be.glue_residual(h, d)
+
+
+class AbqLinear:
+    """One sharded quantized linear layer on the GPU: static-scale activation quantise+pack, then the GEMM with its
+    fused dequantisation (per-channel or per-group scale and zero point, per-token activation scale)."""
+
+    def __init__(self, abq, torch, codes, scale, zero, w_bits: int, group: int, x_bits: int = 8, x_scale: float = 16.0,
+                 max_tokens: int = 64):
+        self.abq, self.torch = abq, torch
+        self.out_features, self.in_features = codes.shape
+        N, K = codes.shape
+        self.w_bits, self.x_bits, self.group = w_bits, x_bits, group
+        self.planes = torch.empty((w_bits, N, K // 32), dtype=torch.int32, device="cuda")
+        abq.pack_int32(codes.to(torch.int32).contiguous(), self.planes, N, K, w_bits)
+        self.scale = scale.to(torch.float16).contiguous()
+        self.zero = None if zero is None else zero.to(torch.uint8).contiguous()
+        self.q_scale = torch.full((1,), x_scale, dtype=torch.float32, device="cuda")
+        self.max_tokens = max_tokens
+        self.x_planes = torch.empty((x_bits, max_tokens, K // 32), dtype=torch.int32, device="cuda")
+        self.inv = torch.full((max_tokens,), 1.0 / x_scale, dtype=torch.float32, device="cuda")
+        self.work = torch.empty(max(256, abq.gemm_workspace_bytes(max_tokens, N, K, x_bits, w_bits)), dtype=torch.uint8, device="cuda")
+        self.plans = {}
+
+    def _plan(self, M):
+        """Plan and output buffer per token count, made on first use (outside stream capture: planning may touch the
+        workspace) and reused afterwards, so that a captured graph replays launches only."""
+        key = M
+        if key not in self.plans:
+            B = self.abq.binding
+            out = self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda")
+            x_view = self.x_planes.view(-1)[: self.x_bits * M * (self.in_features // 32)]
+            p = B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out, x_bits=self.x_bits, w_bits=self.w_bits,
+                              x_signed=True, w_signed=False, out_dtype=self.abq.OUT_FP16,
+                              scale_mode=self.abq.SCALE_GROUP if self.group else self.abq.SCALE_CHANNEL, group_size=self.group,
+                              w_scale=self.scale, w_zero=self.zero, x_scale=self.inv, flags=self.abq.FLAG_PDL, workspace=self.work)
+            self.plans[key] = (self.abq.gemm_init(p), x_view, out)
+        return self.plans[key]
+
+    def __call__(self, x):
+        M = x.shape[0]
+        if M > self.max_tokens:
+            raise ValueError(f"{M} tokens, planned for at most {self.max_tokens}")
+        st, x_view, out = self._plan(M)
+        self.abq.quantize_pack_half(x.contiguous(), self.q_scale, x_view, M, self.in_features, self.x_bits, 0)
+        self.abq.gemm_exec(st)
+        return out
+
+
+class AbqBackend:
+    """Product backend: this library for the GEMMs, torch.distributed (NCCL) for the all-reduce, torch elementwise
+    kernels for the glue between the GEMMs."""
+
+    def __init__(self, abq, torch, dist=None, x_bits: int = 8, x_scale: float = 16.0, max_tokens: int = 64):
+        if not torch.cuda.is_available():
+            raise RuntimeError("AbqBackend needs a CUDA device: there is no CPU path")
+        self.abq, self.torch, self.dist = abq, torch, dist
+        self.x_bits, self.x_scale, self.max_tokens = x_bits, x_scale, max_tokens
+
+    def make_linear(self, codes, scale, zero, w_bits, group):
+        return AbqLinear(self.abq, self.torch, codes, scale, zero, w_bits, group, self.x_bits, self.x_scale, self.max_tokens)
+
+    def all_reduce(self, t):
+        if self.dist is not None and self.dist.get_world_size() > 1:
+            self.dist.all_reduce(t)
+
+    def glue_attention(self, qkv, hl):
+        return qkv[:, :hl].contiguous()
+
+    def glue_residual(self, a, b):
+        return a + b
+
+    def glue_swiglu(self, gu, fl):
+        return self.torch.nn.functional.silu(gu[:, :fl]) * gu[:, fl:]

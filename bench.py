@@ -490,6 +490,87 @@ def reference_gpu_kernels():
     return rows
 
 
+def run_tp_decode(args, rank, world, local):
+    """`--workload tp_decode`: one decode step through the quantized linear layers of LLaMA-7B (32 blocks: fused QKV, O,
+    fused gate+up, down; W4A4, per-channel scale + zero point, static activation scale), tensor parallel over the
+    ranks: column-parallel QKV / gate+up, row-parallel O / down with an NCCL all-reduce after each.  Attention, norms,
+    embedding and lm_head are outside the path (elementwise torch stand-ins keep the data flowing).  Strong scaling:
+    the model is fixed, every rank holds 1/N of every weight."""
+    import torch
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    abq = load_package()
+    spec = importlib.util.spec_from_file_location("abq_llm_b200.tp_linear", ROOT / "abq-llm_b200" / "tp_linear.py")
+    tp = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = tp
+    spec.loader.exec_module(tp)
+    hidden, ffn, layers, q, p = 4096, 11008, args.layers, 4, 4
+    gen = torch.Generator(device="cuda")
+    backend = tp.AbqBackend(abq, torch, dist, x_bits=p, x_scale=2.0, max_tokens=32)
+    blocks = []
+    for layer in range(layers):
+        gen.manual_seed(1000 + layer)  # the same full weights on every rank; each keeps its shard
+        weights = []
+        for sp in tp.llama_block_specs(hidden, ffn):
+            codes = torch.randint(0, 1 << q, (sp.out_features, sp.in_features), dtype=torch.int32, device="cuda", generator=gen)
+            scale = (torch.rand((sp.out_features,), device="cuda", generator=gen) * 0.002 + 0.0005).to(torch.float16)
+            zero = torch.randint(0, 1 << q, (sp.out_features,), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8)
+            weights.append((codes, scale, zero))
+        blocks.append(tp.TensorParallelBlockLinears(backend, hidden, ffn, rank, world, weights, q, 0))
+        del weights
+    results = []
+    for M in (1, 8, 32):
+        gen.manual_seed(7)
+        x = (torch.randn((M, hidden), device="cuda", generator=gen)).to(torch.float16)
+
+        def step():
+            h = x
+            for b in blocks:
+                h = b.forward(h)
+            return h
+        for _ in range(2):
+            step()  # plans and buffers are made here
+        torch.cuda.synchronize()
+        if rank == 0:
+            print(f"tp_decode: batch {M} warmed up", file=sys.stderr, flush=True)
+        graph = None
+        # one GPU: the whole step as one CUDA graph.  Several ranks: eager launches (a first attempt to capture the NCCL
+        # all-reduce inside the graph did not finish on this stack, so collectives are never captured here)
+        if not args.no_graph and world == 1:
+            try:
+                side = torch.cuda.Stream()
+                with torch.cuda.stream(side):
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        step()
+                torch.cuda.synchronize()
+            except Exception as e:  # a collective that cannot be captured: time the eager step instead
+                graph = None
+                if rank == 0:
+                    print(f"graph capture failed ({type(e).__name__}): timing eager launches", file=sys.stderr)
+        fn = (lambda i: graph.replay()) if graph is not None else (lambda i: step())
+        ms, _ = timed(torch, dist, fn, max(3, args.steps // 10), 3)
+        n = max(3, args.steps // 10)
+        results.append({"batch": M, "ms_per_step": ms / n, "tokens_per_s": M * n / (ms * 1e-3), "cuda_graph": graph is not None})
+    if rank == 0:
+        wbytes = layers * sum(sp.out_features * sp.in_features for sp in tp.llama_block_specs(hidden, ffn)) * q // 8
+        best = results[0]
+        line = {"metric": "llama7b_w4a4_linear_stack_decode_tokens_per_s", "value": best["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+                "steps": max(3, args.steps // 10), "warmup": 3, "ms_per_step": best["ms_per_step"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                "config": {"workload": f"LLaMA-7B linear layers only, {layers} blocks, W4A4 per-channel, tensor parallel {world}, batch 1 "
+                                       "(value); batches 8 and 32 in `batches`", "weight_bytes_all_ranks": wbytes},
+                "batches": results,
+                "hbm_bound_tokens_per_s_batch1": world * measured_peaks()[0] * 1e9 / wbytes}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_reference(args, rank, world):
     """`--impl reference`: the reference's own CPU implementation of the path on the host cores."""
     if rank != 0:
@@ -527,6 +608,9 @@ def main():
     ap.add_argument("--only", default="", help="profiling aid: restrict the sweep to GEMMs 'q:M:N:K[,q:M:N:K...]' (0 = any)")
     ap.add_argument("--shape", default="", help="profiling aid: replace the sweep by the single GEMM 'q:M:N:K' (any size the route takes)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the short prefill-shape (tcgen05 route) leg")
+    ap.add_argument("--workload", default="decode_sweep", choices=["decode_sweep", "tp_decode"],
+                    help="decode_sweep (default, the headline metric) or tp_decode: tensor-parallel LLaMA-7B linear stack")
+    ap.add_argument("--layers", type=int, default=32, help="tp_decode: decoder blocks")
     ap.add_argument("--no-graph", action="store_true", help="profiling aid: launch kernel by kernel instead of one CUDA graph per pass")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling aid: skip the host-side reference timing")
     args = ap.parse_args()
@@ -537,6 +621,9 @@ def main():
         run_reference(args, rank, world)
         return
     args.warmup = max(3, args.warmup)
+    if args.workload == "tp_decode":
+        run_tp_decode(args, rank, world, local)
+        return
 
     import torch
     if not torch.cuda.is_available():
