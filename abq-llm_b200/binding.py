@@ -12,6 +12,7 @@ OUT_INT32, OUT_FP16 = 0, 1
 SCALE_NONE, SCALE_TENSOR_COMPAT, SCALE_CHANNEL, SCALE_GROUP = 0, 1, 2, 3
 FLAG_PDL = 1
 FLAG_WEIGHTS_PREPARED = 2
+FLAG_X_HALF = 4
 
 _PKG = Path(__file__).resolve().parent
 
@@ -35,6 +36,7 @@ class GemmParams(ctypes.Structure):
         ("route", ctypes.c_int), ("flags", ctypes.c_int),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("status_word", ctypes.c_void_p),
+        ("x_quant_scale", ctypes.c_void_p),
     ]
 
 
@@ -129,7 +131,7 @@ def gemm_workspace_bytes(M: int, N: int, K: int, x_bits: int, w_bits: int, route
 
 def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dtype=OUT_INT32, scale_mode=SCALE_NONE,
                 group_size=0, C=None, w_scale=None, w_zero=None, x_scale=None, route=ROUTE_AUTO, flags=0, workspace=None,
-                status_word=None) -> GemmParams:
+                status_word=None, x_quant_scale=None) -> GemmParams:
     p = GemmParams()
     p.M, p.N, p.K = M, N, K
     p.X, p.W, p.C, p.D = _ptr(X), _ptr(W), _ptr(C), _ptr(D)
@@ -141,6 +143,7 @@ def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dty
     p.workspace = _ptr(workspace)
     p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     p.status_word = _ptr(status_word)
+    p.x_quant_scale = _ptr(x_quant_scale)
     return p
 
 

@@ -16,6 +16,8 @@ cudaError_t quantize_pack_half(const __half *in, const float *scale, uint32_t *p
 
 // ---- xprep.cu
 cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream);
+// fp16 activations -> int8 codes [rows][K] (static scale, truncation: the FasterTransformer wrapper's quantiser)
+cudaError_t quantize_codes(const void *in_half, const float *scale, void *out, int rows, int K, int bits, cudaStream_t stream);
 // both operands of a GEMM (same K) in one launch
 cudaError_t unpack_pair_i8(const uint32_t *planes_a, void *out_a, int rows_a, int bits_a, int signed_a, const uint32_t *planes_b, void *out_b,
                            int rows_b, int bits_b, int signed_b, int K, cudaStream_t stream);

@@ -105,6 +105,12 @@ static abq_status validate(const abq_gemm_params &p)
     }
     if ((reinterpret_cast<uintptr_t>(p.X) | reinterpret_cast<uintptr_t>(p.W)) & 15)
         return ABQ_ERR_INVALID_ARG;
+    if (p.flags & ABQ_FLAG_X_HALF) {
+        if (!p.x_quant_scale || !p.x_signed)
+            return ABQ_ERR_INVALID_ARG;
+        if (p.route == ABQ_ROUTE_B1_MMA)
+            return ABQ_ERR_UNSUPPORTED; // the 1-bit route multiplies planes
+    }
     return ABQ_OK;
 }
 

@@ -50,6 +50,7 @@ struct DecodeArgs {
     int ring;              // TMA stages per warp
     const uint32_t *X;     // activation planes [x_bits][rows][K/32], first row of this launch
     size_t x_plane_words;  // words between two planes (all rows of the operand, not only the M of this launch)
+    const float *x_qscale; // not null: X is fp16 [rows][K], quantised here with this static scale (see build_records_half)
     int x_bits, x_signed;
     int *counters;         // one per tile (slices > 1), zero before the launch, left zero after it
     int *partials;         // [slice][tile][token][16 rows] int32 or fp32 bit patterns (slices > 1)
@@ -142,6 +143,57 @@ __device__ __forceinline__ void build_records(const DecodeArgs &a, uint8_t *rec_
     }
 }
 
+// The same records straight from fp16 activations: code = (int)(half(x) * half(scale)), truncated, the low x_bits bits
+// kept and sign-extended -- what quantize_pack_half (mode 0) followed by build_records gives, without the planes.
+template <int NW>
+__device__ __forceinline__ void build_records_half(const DecodeArgs &a, uint8_t *rec_base, int g_first, int n_groups, int MT, int rec_bytes)
+{
+    const int words = n_groups * 4;
+    const int items = MT * 8 * words;
+    const __half *xh = reinterpret_cast<const __half *>(a.X);
+    const __half hscale = __float2half(__ldg(a.x_qscale));
+    const uint32_t keep = 0x01010101u * ((1u << a.x_bits) - 1u);
+    for (int idx = threadIdx.x; idx < items; idx += NW * 32) {
+        const int m = idx / words, kwl = idx - m * words;
+        uint32_t r[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            r[s] = 0;
+        int sum = 0;
+        if (m < a.M) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(xh + (size_t)m * a.K + (size_t)(g_first * 4 + kwl) * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = __ldg(src + i);
+                const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const __half h = __ushort_as_half((unsigned short)(w[e >> 1] >> ((e & 1) * 16)));
+                    const uint32_t code = (uint32_t)__half2int_rz(__hmul(h, hscale)) & 0xffu;
+                    const int pos = 31 - (8 * i + e); // byte y of r[s] holds element 31 - 8y - s of the run
+                    r[pos & 7] |= code << (8 * (pos >> 3));
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                r[s] &= keep;
+                if (a.x_bits < 8)
+                    r[s] = sign_extend_bytes(r[s], a.x_bits);
+                sum = __dp4a((int)r[s], 0x01010101, sum);
+            }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int G = kwl >> 2, t = kwl & 3, mt = m >> 3, g = m & 7;
+        uint8_t *rec = rec_base + (size_t)G * rec_bytes;
+        uint4 *dst = reinterpret_cast<uint4 *>(rec + ((mt * 2) * 32 + g * 4 + t) * 16);
+        dst[0] = make_uint4(r[0], r[1], r[2], r[3]);
+        dst[32] = make_uint4(r[4], r[5], r[6], r[7]);
+        if (t == 0)
+            reinterpret_cast<int *>(rec + 1024 * MT)[m] = sum;
+    }
+}
+
 template <int Q, int MT, bool XU8, bool GROUPED, bool GPS1, int NW>
 __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const DecodeArgs a)
 {
@@ -209,6 +261,9 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
 
     // ---- activations: everything below may depend on the kernel launched just before
     pdl_wait_prior_grid();
+    if (a.x_qscale)
+        build_records_half<NW>(a, rec_base, g_slice, n_groups, MT, kRec);
+    else
     switch (a.x_bits) {
     case 1: build_records<1, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
     case 2: build_records<2, NW>(a, rec_base, g_slice, n_groups, MT, kRec); break;
@@ -743,6 +798,7 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.ring = st->tile[1];
     a.X = reinterpret_cast<const uint32_t *>(p.X);
     a.x_plane_words = (size_t)p.M * (p.K / 32);
+    a.x_qscale = (p.flags & ABQ_FLAG_X_HALF) ? p.x_quant_scale : nullptr;
     a.x_bits = p.x_bits;
     a.x_signed = p.x_signed;
     a.counters = nullptr;
@@ -770,7 +826,8 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     const size_t out_row_bytes = (size_t)p.N * (p.out_dtype == ABQ_OUT_INT32 ? 4 : 2);
     for (int m0 = 0; m0 < p.M; m0 += 16) {
         a.M = p.M - m0 < 16 ? p.M - m0 : 16;
-        a.X = reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
+        a.X = (p.flags & ABQ_FLAG_X_HALF) ? reinterpret_cast<const uint32_t *>(reinterpret_cast<const __half *>(p.X) + (size_t)m0 * p.K)
+                                          : reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
         a.D = reinterpret_cast<uint8_t *>(p.D) + (size_t)m0 * out_row_bytes;
         a.x_scale = p.x_scale ? p.x_scale + m0 : nullptr;
         cudaError_t e;

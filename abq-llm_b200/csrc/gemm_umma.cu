@@ -483,7 +483,13 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
     umma_layout(p.M, p.N, p.K, &off_w, &off_sum, &total);
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
     cudaError_t e;
-    if (p.flags & ABQ_FLAG_WEIGHTS_PREPARED) // the weight codes are in place: expand the activations only
+    if (p.flags & ABQ_FLAG_X_HALF) { // fp16 activations: quantise straight to codes; weights as usual
+        e = cudaSuccess;
+        if (!(p.flags & ABQ_FLAG_WEIGHTS_PREPARED))
+            e = unpack_i8(reinterpret_cast<const uint32_t *>(p.W), ws + off_w, p.N, p.K, p.w_bits, p.w_signed, stream);
+        if (e == cudaSuccess)
+            e = quantize_codes(p.X, p.x_quant_scale, ws, p.M, p.K, p.x_bits, stream);
+    } else if (p.flags & ABQ_FLAG_WEIGHTS_PREPARED) // the weight codes are in place: expand the activations only
         e = unpack_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.K, p.x_bits, p.x_signed, stream);
     else
         e = unpack_pair_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.x_bits, p.x_signed, reinterpret_cast<const uint32_t *>(p.W),

@@ -6,6 +6,8 @@
 //
 // The reference has no counterpart: it feeds the planes themselves to 1-bit tensor-core MMAs
 // (engine/mma_any/aq_bmma_kernel.h:227-251), an instruction class that sm_100a only emulates.
+#include <cuda_fp16.h>
+
 #include "abq_common.cuh"
 #include "abq_kernels.h"
 
@@ -115,6 +117,48 @@ cudaError_t unpack_pair_i8(const uint32_t *planes_a, void *out_a, int rows_a, in
     const unsigned blocks_a = (unsigned)((La + per - 1) / per), blocks_b = (unsigned)((Lb + per - 1) / per);
     unpack_pair_kernel<<<blocks_a + blocks_b, 256, 0, stream>>>(planes_a, reinterpret_cast<uint32_t *>(out_a), La, bits_a, signed_a, blocks_a,
                                                                 planes_b, reinterpret_cast<uint32_t *>(out_b), Lb, bits_b, signed_b);
+    return cudaGetLastError();
+}
+
+// fp16 activations -> int8 codes [rows][K], the static-scale quantiser of the FasterTransformer wrapper
+// (abq_gemm_wrapper.cu:29-54): code = (int)(half(x) * half(scale[0])), truncated, the low `bits` bits kept and
+// sign-extended.  16 values per thread: two 16-byte loads, one 16-byte store.
+__global__ void __launch_bounds__(256) quantize_codes_kernel(const __half *__restrict__ in, const float *__restrict__ scale,
+                                                             uint4 *__restrict__ out, long n16, int bits)
+{
+    pdl_launch_dependents();
+    const long idx = (long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= n16)
+        return;
+    const __half hscale = __float2half(__ldg(scale));
+    const uint32_t keep = 0x01010101u * ((1u << bits) - 1u);
+    const uint4 *src = reinterpret_cast<const uint4 *>(in) + idx * 2;
+    uint32_t o[4] = { 0, 0, 0, 0 };
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint4 v = __ldg(src + i);
+        const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const __half h = __ushort_as_half((unsigned short)(w[e >> 1] >> ((e & 1) * 16)));
+            const uint32_t code = (uint32_t)__half2int_rz(__hmul(h, hscale)) & 0xffu;
+            o[2 * i + (e >> 2)] |= code << (8 * (e & 3));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        o[k] &= keep;
+        if (bits < 8)
+            o[k] = sign_extend_bytes(o[k], bits);
+    }
+    out[idx] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+cudaError_t quantize_codes(const void *in_half, const float *scale, void *out, int rows, int K, int bits, cudaStream_t stream)
+{
+    const long n16 = (long)rows * K / 16;
+    quantize_codes_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const __half *>(in_half), scale,
+                                                                             reinterpret_cast<uint4 *>(out), n16, bits);
     return cudaGetLastError();
 }
 

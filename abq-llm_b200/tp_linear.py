@@ -90,22 +90,25 @@ class TensorParallelBlockLinears:
     def forward(self, x):
         """x: fp16 [M][hidden], replicated on every rank.  Returns fp16 [M][hidden], replicated."""
         be = self.backend
+        M = x.shape[0]
+        # where a layer exposes the buffer its plan reads, the producing elementwise step writes straight into it
+        buf = lambda name: self.layers[name].input(M) if hasattr(self.layers[name], "input") else None
         hl = self.layers["qkv"].out_features // 3
         qkv = self.layers["qkv"](x)                          # [M][3 * hidden / world]
-        attn = be.glue_attention(qkv, hl)                    # [M][hidden / world]: this rank's heads
+        attn = be.glue_attention(qkv, hl, buf("o"))          # [M][hidden / world]: this rank's heads
         o = self.layers["o"](attn)                           # partial [M][hidden]
         be.all_reduce(o)
-        h = be.glue_residual(x, o)
+        h = be.glue_residual(x, o, buf("gate_up"))
         gu = self.layers["gate_up"](h)                       # [M][2 * ffn_local]
-        act = be.glue_swiglu(gu, self.layers["gate_up"].out_features // 2)
+        act = be.glue_swiglu(gu, self.layers["gate_up"].out_features // 2, buf("down"))
         d = self.layers["down"](act)                         # partial [M][hidden]
         be.all_reduce(d)
-        return be.glue_residual(h, d)
+        return be.glue_residual(h, d, None)
 
 
 class AbqLinear:
-    """One sharded quantized linear layer on the GPU: static-scale activation quantise+pack, then the GEMM with its
-    fused dequantisation (per-channel or per-group scale and zero point, per-token activation scale)."""
+    """One sharded quantized linear layer on the GPU: one GEMM call that quantises the fp16 activations with a static
+    scale (ABQ_FLAG_X_HALF) and writes fp16 through its fused dequantisation (per-channel or per-group scale and zero point, per-token activation scale)."""
 
     def __init__(self, abq, torch, codes, scale, zero, w_bits: int, group: int, x_bits: int = 8, x_scale: float = 16.0,
                  max_tokens: int = 64):
@@ -119,7 +122,6 @@ class AbqLinear:
         self.zero = None if zero is None else zero.to(torch.uint8).contiguous()
         self.q_scale = torch.full((1,), x_scale, dtype=torch.float32, device="cuda")
         self.max_tokens = max_tokens
-        self.x_planes = torch.empty((x_bits, max_tokens, K // 32), dtype=torch.int32, device="cuda")
         self.inv = torch.full((max_tokens,), 1.0 / x_scale, dtype=torch.float32, device="cuda")
         self.work = torch.empty(max(256, abq.gemm_workspace_bytes(max_tokens, N, K, x_bits, w_bits)), dtype=torch.uint8, device="cuda")
         self.plans = {}
@@ -131,20 +133,26 @@ class AbqLinear:
         if key not in self.plans:
             B = self.abq.binding
             out = self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda")
-            x_view = self.x_planes.view(-1)[: self.x_bits * M * (self.in_features // 32)]
+            x_view = self.torch.empty((M, self.in_features), dtype=self.torch.float16, device="cuda")  # the GEMM reads fp16 here
             p = B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out, x_bits=self.x_bits, w_bits=self.w_bits,
                               x_signed=True, w_signed=False, out_dtype=self.abq.OUT_FP16,
                               scale_mode=self.abq.SCALE_GROUP if self.group else self.abq.SCALE_CHANNEL, group_size=self.group,
-                              w_scale=self.scale, w_zero=self.zero, x_scale=self.inv, flags=self.abq.FLAG_PDL, workspace=self.work)
+                              w_scale=self.scale, w_zero=self.zero, x_scale=self.inv, flags=self.abq.FLAG_PDL | self.abq.FLAG_X_HALF, x_quant_scale=self.q_scale,
+                              workspace=self.work)
             self.plans[key] = (self.abq.gemm_init(p), x_view, out)
         return self.plans[key]
+
+    def input(self, M):
+        """The fp16 buffer [M][in_features] this layer's plan reads: producers write straight into it."""
+        return self._plan(M)[1]
 
     def __call__(self, x):
         M = x.shape[0]
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens, planned for at most {self.max_tokens}")
         st, x_view, out = self._plan(M)
-        self.abq.quantize_pack_half(x.contiguous(), self.q_scale, x_view, M, self.in_features, self.x_bits, 0)
+        if x.data_ptr() != x_view.data_ptr():
+            x_view.copy_(x)  # callers that cannot write into input(M) pay one copy; the GEMM call quantises x_view itself
         self.abq.gemm_exec(st)
         return out
 
@@ -166,11 +174,14 @@ class AbqBackend:
         if self.dist is not None and self.dist.get_world_size() > 1:
             self.dist.all_reduce(t)
 
-    def glue_attention(self, qkv, hl):
-        return qkv[:, :hl].contiguous()
+    def glue_attention(self, qkv, hl, out=None):
+        if out is None:
+            return qkv[:, :hl].contiguous()
+        out.copy_(qkv[:, :hl])
+        return out
 
-    def glue_residual(self, a, b):
-        return a + b
+    def glue_residual(self, a, b, out=None):
+        return self.torch.add(a, b, out=out)
 
-    def glue_swiglu(self, gu, fl):
-        return self.torch.nn.functional.silu(gu[:, :fl]) * gu[:, fl:]
+    def glue_swiglu(self, gu, fl, out=None):
+        return self.torch.mul(self.torch.nn.functional.silu(gu[:, :fl]), gu[:, fl:], out=out)

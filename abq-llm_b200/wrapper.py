@@ -53,12 +53,17 @@ class ABQGEMMWrapper:
         if abq_gemm_ws_bytes < need:
             raise B.AbqError(3, f"workspace of {abq_gemm_ws_bytes} bytes, {need} needed")
         ws = abq_gemm_workspace
-        plane_bytes = (self.x_bits_ * M * (K // 32) * 4 + 255) & ~255
         base = ws.data_ptr()
-        B.quantize_pack_half(A, scale, base, M, K, self.x_bits_, 0, stream)
+        # signed configurations: the GEMM call quantises the fp16 activations itself (same codes as pack, one launch less)
+        fused = self.signed_
+        plane_bytes = 0 if fused else (self.x_bits_ * M * (K // 32) * 4 + 255) & ~255
+        if not fused:
+            B.quantize_pack_half(A, scale, base, M, K, self.x_bits_, 0, stream)
         p = B.GemmParams()
         p.M, p.N, p.K = M, N, K
-        p.X, p.W, p.C, p.D = base, B._ptr(B_planes), B._ptr(scale_out), B._ptr(D)
+        p.X, p.W, p.C, p.D = (B._ptr(A) if fused else base), B._ptr(B_planes), B._ptr(scale_out), B._ptr(D)
+        p.flags = B.FLAG_X_HALF if fused else 0
+        p.x_quant_scale = B._ptr(scale)
         p.bias = int(bool(bias))
         p.x_bits, p.w_bits = self.x_bits_, self.w_bits_
         p.x_signed = p.w_signed = int(self.signed_)

@@ -72,7 +72,12 @@ enum {
     /* Route I8_UMMA only: the int8 expansion of W already sits in this plan's workspace (abq_gemm_prepare_weights
      * put it there and nothing has overwritten it since): abq_gemm_exec expands the activations only.  For weights
      * that stay the same from call to call, with a workspace of their own. */
-    ABQ_FLAG_WEIGHTS_PREPARED = 2
+    ABQ_FLAG_WEIGHTS_PREPARED = 2,
+    /* X points to fp16 activations [M][K] instead of planes; the call quantises them itself exactly as the
+     * FasterTransformer wrapper's pack does (abq_gemm_wrapper.cu:29-54): code = (int)(half(x) * half(x_quant_scale[0])),
+     * truncated, unclamped, the low x_bits bits kept (x_signed must be 1).  Saves the pack launch and the round trip
+     * through planes; the result is bit-identical to abq_quantize_pack_half (mode 0) followed by the GEMM. */
+    ABQ_FLAG_X_HALF = 4
 };
 
 /*
@@ -82,7 +87,7 @@ enum {
  */
 typedef struct abq_gemm_params {
     int M, N, K;
-    const void *X;  /* uint32 planes [x_bits][M][K/32] */
+    const void *X;  /* uint32 planes [x_bits][M][K/32] (fp16 [M][K] with ABQ_FLAG_X_HALF) */
     const void *W;  /* uint32 planes [w_bits][N][K/32] */
     const void *C;  /* ABQ_SCALE_TENSOR_COMPAT: one fp16 scale; otherwise unused (reference: `half *C`) */
     void *D;        /* int32 [M][N] or fp16 [M][N], row-major */
@@ -101,6 +106,7 @@ typedef struct abq_gemm_params {
     void *workspace;        /* >= abq_gemm_workspace_bytes(), 256-byte aligned */
     size_t workspace_bytes;
     int *status_word;       /* optional device int, set non-zero by a kernel whose bounded wait expired */
+    const float *x_quant_scale; /* ABQ_FLAG_X_HALF: device float, the static activation scale */
 } abq_gemm_params;
 
 /*

@@ -238,12 +238,18 @@ public:
             std::printf("[ABQ][Error] workspace of %zu bytes cannot hold the activation planes\n", abq_gemm_ws_bytes);
             return;
         }
-        pack(A, scale, reinterpret_cast<int *>(abq_gemm_workspace), M, K, x_bits_, stream);
+        // signed configurations: the GEMM call quantises the fp16 activations itself (same codes as pack, one launch
+        // less, no planes); unsigned ones go through the planes as the reference does
+        const bool fused = signed_;
+        if (!fused)
+            pack(A, scale, reinterpret_cast<int *>(abq_gemm_workspace), M, K, x_bits_, stream);
         abq_gemm_params p = {};
         p.M = M;
         p.N = N;
         p.K = K;
-        p.X = abq_gemm_workspace;
+        p.X = fused ? static_cast<const void *>(A) : static_cast<const void *>(abq_gemm_workspace);
+        p.flags = fused ? ABQ_FLAG_X_HALF : 0;
+        p.x_quant_scale = scale;
         p.W = B;
         p.C = scale_out;
         p.D = D;
@@ -255,9 +261,10 @@ public:
         p.scale_mode = ABQ_SCALE_TENSOR_COMPAT;
         const size_t need = abq_gemm_workspace_bytes(M, N, K, x_bits_, w_bits_, ABQ_ROUTE_AUTO);
         abq_status s;
-        if (abq_gemm_ws_bytes >= plane_bytes + need) { // a caller that sized the workspace with room for the scratch
-            p.workspace = abq_gemm_workspace + plane_bytes;
-            p.workspace_bytes = abq_gemm_ws_bytes - plane_bytes;
+        const size_t used = fused ? 0 : plane_bytes; // the fused call leaves the whole workspace to the GEMM
+        if (abq_gemm_ws_bytes >= used + need) { // a caller that sized the workspace with room for the scratch
+            p.workspace = abq_gemm_workspace + used;
+            p.workspace_bytes = abq_gemm_ws_bytes - used;
             s = abq_gemm(&p, stream);
         } else { // the reference's layers size it for the planes only
             s = abq_gemm_static_scratch(&p, stream);

@@ -51,13 +51,13 @@ class NumpyBackend:
             tt = torch.from_numpy(t)
             self.dist.all_reduce(tt)
 
-    def glue_attention(self, qkv, hl):
+    def glue_attention(self, qkv, hl, out=None):
         return np.ascontiguousarray(qkv[:, :hl])
 
-    def glue_residual(self, a, b):
+    def glue_residual(self, a, b, out=None):
         return (a + b).astype(np.float16)
 
-    def glue_swiglu(self, gu, fl):
+    def glue_swiglu(self, gu, fl, out=None):
         g = gu[:, :fl].astype(np.float32)
         return (g / (1 + np.exp(-g)) * gu[:, fl:].astype(np.float32)).astype(np.float16)
 
