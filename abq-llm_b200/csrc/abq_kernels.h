@@ -15,12 +15,15 @@ cudaError_t quantize_pack_half(const __half *in, const float *scale, uint32_t *p
                                cudaStream_t stream);
 
 // ---- xprep.cu
-cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream);
+// zero != NULL: the codes written are code - zero[row][k / zero_group] (the caller guarantees that this fits int8)
+cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream,
+                      const uint8_t *zero = nullptr, int zero_group = 0);
 // fp16 activations -> int8 codes [rows][K] (static scale, truncation: the FasterTransformer wrapper's quantiser)
 cudaError_t quantize_codes(const void *in_half, const float *scale, void *out, int rows, int K, int bits, cudaStream_t stream);
 // both operands of a GEMM (same K) in one launch
 cudaError_t unpack_pair_i8(const uint32_t *planes_a, void *out_a, int rows_a, int bits_a, int signed_a, const uint32_t *planes_b, void *out_b,
-                           int rows_b, int bits_b, int signed_b, int K, cudaStream_t stream);
+                           int rows_b, int bits_b, int signed_b, int K, cudaStream_t stream, const uint8_t *zero_b = nullptr,
+                           int zero_group = 0);
 // Bytes of one decode-route activation record (one per 128 input features): MT token tiles of 8.
 __host__ __device__ constexpr int decode_record_bytes(int MT) { return 1024 * MT + 64; }
 

@@ -163,8 +163,14 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
         return s;
     int route = params->route;
     if (route == ABQ_ROUTE_AUTO)
-        // per-group scales need the accumulator per group: only the mma.sync route folds them (16 rows per launch)
-        route = params->M <= 16 || params->scale_mode == ABQ_SCALE_GROUP ? ABQ_ROUTE_I8_MMA : ABQ_ROUTE_I8_UMMA;
+        route = params->M <= 16 ? ABQ_ROUTE_I8_MMA : ABQ_ROUTE_I8_UMMA;
+    if (params->route == ABQ_ROUTE_AUTO && route == ABQ_ROUTE_I8_UMMA && params->scale_mode == ABQ_SCALE_GROUP) {
+        // per-group scales: the tensor-core route drains its accumulator per group where it can (whole K blocks per group,
+        // zero points foldable into int8 codes); otherwise the mma.sync route, 16 rows per launch
+        s = umma_plan(state);
+        if (s == ABQ_ERR_UNSUPPORTED)
+            route = ABQ_ROUTE_I8_MMA;
+    }
     switch (route) {
     case ABQ_ROUTE_B1_MMA: s = b1_plan(state); break;
     case ABQ_ROUTE_I8_MMA: s = decode_plan(state, clear_counters); break;

@@ -37,7 +37,9 @@ struct UmmaArgs {
     const __half *w_scale;
     const uint8_t *w_zero;
     const float *x_scale;
-    const int *xsum; // per-token code sums (only with zero points)
+    const int *xsum; // per-token code sums (only with per-channel zero points)
+    int kb_per_group;  // ABQ_SCALE_GROUP: 128-byte K blocks per scale group
+    int scale_groups;  // ABQ_SCALE_GROUP: scale groups per weight row
     int out_dtype, scale_mode;
     uint32_t idesc;
     int *status;
@@ -152,6 +154,20 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs &a, const int (&v)[32
                 dst[j] = __ushort_as_half((unsigned short)(h[j >> 1] >> ((j & 1) * 16)));
     }
 }
+
+// the same without the wait: several loads in flight, then one tmem_ld_wait()
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, int (&v)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+                   "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                   "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                   "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 template <int BN>
 __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -324,6 +340,217 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// ABQ_SCALE_GROUP on the tensor-core route: every scale group (kb_per_group K blocks) is multiplied into a fresh TMEM
+// accumulator, exactly, and the epilogue warps drain it while the next group is multiplied into the other one:
+//     facc[n] += scale[n][g] * acc_g[n]                                              (fp32, one row per thread)
+// The zero points are not seen here: the weight codes in the scratch are w - zero[n][g] (signed int8, exact for widths
+// up to 7 bits; see unpack_i8), so acc_g already is sum x * (w - z).  BN = 128 columns (128 fp32 partial sums per
+// thread); the scales of the tile, all groups, are staged once per tile in shared memory as fp32 [group][column].
+// MAGIC: |acc_g| < 2^22 (signed 8-bit activations, one K block per group): int -> float by the 1.5 * 2^23 trick, two
+// pipelined operations instead of a conversion instruction.  Same roles, barriers and bounded waits as umma_kernel.
+constexpr int kGroupBN = 128;
+constexpr int kGroupThreads = 320; // TMA warp, MMA warp, eight epilogue warps: two per TMEM lane quarter, 64 columns each
+
+template <bool MAGIC>
+__global__ void __launch_bounds__(kGroupThreads, 1) umma_group_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                     const __grid_constant__ CUtensorMap tmap_b, const UmmaArgs a)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int BN = kGroupBN;
+    constexpr int kABytes = kUmmaBM * kUmmaBK, kBBytes = BN * kUmmaBK, kStageBytes = kABytes + kBBytes;
+    constexpr int kAccs = 4;              // accumulators in flight: the hand-over MMA -> epilogue -> MMA takes longer than two groups
+    constexpr int kTmemCols = kAccs * BN; // all 512 columns
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int G = a.scale_groups;
+    float *s_scale = reinterpret_cast<float *>(smem + (size_t)a.stages * kStageBytes); // [G][BN]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_scale + (size_t)G * BN);
+    uint64_t *full = bars, *empty = bars + 8, *acc_full = bars + 16, *acc_empty = bars + 20, *par_ready = bars + 24, *par_free = bars + 25;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 26);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = a.K / kUmmaBK;
+    const int m_tiles = (a.M + kUmmaBM - 1) / kUmmaBM;
+    const int total_tiles = m_tiles * ((a.N + BN - 1) / BN);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < kAccs; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);
+        }
+        mbar_init(par_ready, 256); // the tile's scales are staged
+        mbar_init(par_free, 256);  // ... and no longer read (the next tile may overwrite them)
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait_prior_grid();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int kc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * kUmmaBM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++kc) {
+                    const int s = kc % a.stages;
+                    if (kc >= a.stages && !mbar_wait_bounded(&empty[s], ((kc / a.stages) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sa = smem + (size_t)s * kStageBytes, *sb = sa + kABytes;
+                    mbar_arrive_expect_tx(&full[s], kStageBytes);
+                    tma_load_2d(sa, &tmap_a, kb * kUmmaBK, m0, &full[s]);
+                    tma_load_2d(sb, &tmap_b, kb * kUmmaBK, n0, &full[s]);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int kc = 0, gc = 0; // K blocks and scale groups issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                for (int g = 0; g < G && ok; ++g, ++gc) {
+                    const int b = gc % kAccs;
+                    if (gc >= kAccs) { // the epilogue has drained this accumulator's previous group
+                        ok = mbar_wait_bounded(&acc_empty[b], ((gc / kAccs) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE);
+                        if (!ok)
+                            break;
+                        tmem_fence_after();
+                    }
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
+                    for (int kg = 0; kg < a.kb_per_group; ++kg, ++kc) {
+                        const int s = kc % a.stages;
+                        ok = mbar_wait_bounded(&full[s], (kc / a.stages) & 1, a.status, STATUS_TIMEOUT_TMA);
+                        if (!ok)
+                            break;
+                        tmem_fence_after();
+                        const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
+                        const uint64_t da = make_smem_desc_sw128(sa), db = make_smem_desc_sw128(sb);
+#pragma unroll
+                        for (int k = 0; k < kUmmaBK / 32; ++k) // the first MMA of a group starts a fresh sum
+                            umma_i8(tmem_d, da + (uint64_t)(k * 32 >> 4), db + (uint64_t)(k * 32 >> 4), a.idesc, (kg | k) != 0);
+                        umma_commit(&empty[s]);
+                    }
+                    if (ok)
+                        umma_commit(&acc_full[b]);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quarter = warp & 3;          // the TMEM lanes a warp may read: 32 * (warp id % 4)
+        const int half = (warp - 2) >> 2;      // which 64 of the tile's 128 columns
+        const int et = threadIdx.x - 64;       // 0..255
+        constexpr int HN = BN / 2;
+        int gc = 0, it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            const int m0 = (tile % m_tiles) * kUmmaBM, n0 = (tile / m_tiles) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            // ---- stage the scales of weight row n0 + et, all groups, as [group][column]
+            if (it > 0) {
+                ok = mbar_wait_bounded(par_free, (it - 1) & 1, a.status, STATUS_TIMEOUT_PIPE);
+                if (!ok)
+                    break;
+            }
+            {
+                const int col = et & (BN - 1), n = n0 + col;
+                const __half *src = a.w_scale + (size_t)(n < a.N ? n : 0) * G;
+                for (int g = et >> 7; g < G; g += 2) // two threads per weight row, alternate groups
+                    s_scale[(size_t)g * BN + col] = n < a.N ? __half2float(src[g]) : 0.f;
+            }
+            mbar_arrive(par_ready);
+            ok = mbar_wait_bounded(par_ready, it & 1, a.status, STATUS_TIMEOUT_PIPE);
+            if (!ok)
+                break;
+            float xs = 1.f;
+            if (row < a.M && a.x_scale)
+                xs = a.x_scale[row];
+            float facc[HN];
+#pragma unroll
+            for (int c = 0; c < HN; ++c)
+                facc[c] = 0.f;
+            for (int g = 0; g < G; ++g, ++gc) {
+                const int b = gc % kAccs;
+                ok = mbar_wait_bounded(&acc_full[b], (gc / kAccs) & 1, a.status, STATUS_TIMEOUT_MMA);
+                if (!ok)
+                    break;
+                tmem_fence_after();
+                const float *sg = s_scale + (size_t)g * BN + half * HN;
+                int v[2][32]; // both loads in flight before the first is used
+                tmem_ld32_nowait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * HN), v[0]);
+                tmem_ld32_nowait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * HN + 32), v[1]);
+                tmem_ld_wait();
+                // the accumulator sits in registers: hand its TMEM buffer back before the arithmetic
+                tmem_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&acc_empty[b]);
+#pragma unroll
+                for (int c = 0; c < HN; c += 32) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 sc = *reinterpret_cast<const float4 *>(sg + c + j); // the same address in every lane
+                        const float s4[4] = { sc.x, sc.y, sc.z, sc.w };
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int vi = v[c >> 5][j + e];
+                            const float fv = MAGIC ? __int_as_float(vi + 0x4b400000) - 12582912.0f : (float)vi;
+                            facc[c + j + e] = fmaf(s4[e], fv, facc[c + j + e]);
+                        }
+                    }
+                }
+            }
+            mbar_arrive(par_free); // this thread reads the staged parameters no more
+            if (!ok)
+                break;
+            if (row < a.M) {
+                const int nb = n0 + half * HN;
+                __half *dst = reinterpret_cast<__half *>(a.D) + (size_t)row * a.N + nb;
+                const bool vec = nb + HN <= a.N && (a.N & 7) == 0;
+#pragma unroll
+                for (int c = 0; c < HN; c += 8) {
+                    uint32_t h[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __half2 t = __floats2half2_rn(facc[c + 2 * e] * xs, facc[c + 2 * e + 1] * xs);
+                        h[e] = *reinterpret_cast<const uint32_t *>(&t);
+                    }
+                    if (vec) {
+                        *reinterpret_cast<uint4 *>(dst + c) = make_uint4(h[0], h[1], h[2], h[3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (nb + c + e < a.N)
+                                dst[c + e] = __ushort_as_half((unsigned short)(h[e >> 1] >> ((e & 1) * 16)));
+                    }
+                }
+            }
+        }
+    }
+
+    tmem_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tmem_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
 // per-token sum of the int8 / uint8 activation codes (needed only with weight zero points)
 __global__ void __launch_bounds__(256) rowsum_kernel(const uint8_t *__restrict__ x, int *__restrict__ out, int M, int K, int is_signed)
 {
@@ -377,8 +604,18 @@ size_t umma_workspace_bytes(int M, int N, int K)
 abq_status umma_plan(abq_gemm_state *st)
 {
     const abq_gemm_params &p = st->p;
-    if (p.scale_mode == ABQ_SCALE_GROUP)
-        return ABQ_ERR_UNSUPPORTED; // per-group scales need the accumulator drained per group: decode route only so far
+    const bool grouped = p.scale_mode == ABQ_SCALE_GROUP;
+    const int scale_groups = grouped ? p.K / p.group_size : 0;
+    if (grouped) {
+        // drained per scale group (umma_group_kernel): groups of whole K blocks; zero points are folded into the int8
+        // weight codes, which needs w - z to fit: unsigned weights of at most 7 bits
+        if (p.group_size % kUmmaBK != 0 || p.out_dtype != ABQ_OUT_FP16)
+            return ABQ_ERR_UNSUPPORTED;
+        if (p.w_zero && (p.w_signed || p.w_bits > 7))
+            return ABQ_ERR_UNSUPPORTED;
+        if ((size_t)scale_groups * kGroupBN * 4 + 3 * (size_t)(kUmmaBM + kGroupBN) * kUmmaBK > 216 * 1024)
+            return ABQ_ERR_UNSUPPORTED; // the tile's scales would not fit beside three stages
+    }
     size_t off_w, off_sum, total;
     umma_layout(p.M, p.N, p.K, &off_w, &off_sum, &total);
     if (!p.workspace || p.workspace_bytes < total)
@@ -409,8 +646,11 @@ abq_status umma_plan(abq_gemm_state *st)
     BN = env_int("ABQ_UMMA_BN", BN);
     if (BN != 64 && BN != 128 && BN != 256)
         return ABQ_ERR_INVALID_ARG;
+    if (grouped)
+        BN = kGroupBN;
     const int stage_bytes = (kUmmaBM + BN) * kUmmaBK;
-    int stages = (216 * 1024) / stage_bytes;
+    const size_t param_bytes = grouped ? (size_t)scale_groups * kGroupBN * 4 : (size_t)4 * BN * 4;
+    int stages = (int)((216 * 1024 - param_bytes) / stage_bytes);
     stages = stages > 8 ? 8 : stages;
     const int k_blocks = p.K / kUmmaBK;
     stages = stages > k_blocks ? k_blocks : stages;
@@ -429,25 +669,25 @@ abq_status umma_plan(abq_gemm_state *st)
     st->grid[0] = (unsigned)(tiles < sms ? tiles : sms); // persistent: a CTA per SM, tiles dealt round-robin
     st->grid[1] = 1;
     st->grid[2] = 1;
-    st->block[0] = kUmmaThreads;
+    st->block[0] = grouped ? kGroupThreads : kUmmaThreads;
     st->block[1] = st->block[2] = 1;
     st->cluster = 1;
-    st->shared_mem_size = 1024 + (size_t)stages * stage_bytes + (size_t)4 * BN * 4 + 256;
+    st->shared_mem_size = 1024 + (size_t)stages * stage_bytes + param_bytes + 256;
     st->tile[0] = BN;
     st->tile[1] = stages;
+    st->tile[2] = grouped ? 1 : 0;
     return ABQ_OK;
 }
 
-template <int BN>
-static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
+template <typename Kernel>
+static cudaError_t launch_kernel(Kernel kern, size_t *configured, const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
 {
-    auto kern = umma_kernel<BN>;
-    static thread_local size_t configured = 0;
-    if (st->shared_mem_size > configured) {
+    const int threads = st->block[0];
+    if (st->shared_mem_size > *configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->shared_mem_size);
         if (e != cudaSuccess)
             return e;
-        configured = st->shared_mem_size;
+        *configured = st->shared_mem_size;
     }
     CUtensorMap ta, tb;
     memcpy(&ta, st->tmap[0], sizeof(ta));
@@ -456,7 +696,7 @@ static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cud
     // kernel; every thread passes griddepcontrol.wait before it touches what that kernel (or the token sums) wrote
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(st->grid[0], 1, 1);
-    cfg.blockDim = dim3(kUmmaThreads);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = st->shared_mem_size;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -467,13 +707,30 @@ static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cud
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, args);
 }
 
+template <bool MAGIC>
+static cudaError_t launch_group(const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
+{
+    static thread_local size_t configured = 0;
+    return launch_kernel(umma_group_kernel<MAGIC>, &configured, st, args, stream);
+}
+
+template <int BN>
+static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
+{
+    static thread_local size_t configured = 0;
+    return launch_kernel(umma_kernel<BN>, &configured, st, args, stream);
+}
+
+// zero points that the weight expansion subtracts (ABQ_SCALE_GROUP on this route), else none
+static const uint8_t *folded_zero(const abq_gemm_params &p) { return p.scale_mode == ABQ_SCALE_GROUP ? p.w_zero : nullptr; }
+
 cudaError_t umma_prepare_weights(const abq_gemm_state *st, cudaStream_t stream)
 {
     const abq_gemm_params &p = st->p;
     size_t off_w, off_sum, total;
     umma_layout(p.M, p.N, p.K, &off_w, &off_sum, &total);
     return unpack_i8(reinterpret_cast<const uint32_t *>(p.W), reinterpret_cast<uint8_t *>(p.workspace) + off_w, p.N, p.K, p.w_bits, p.w_signed,
-                     stream);
+                     stream, folded_zero(p), p.group_size);
 }
 
 cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
@@ -486,14 +743,15 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
     if (p.flags & ABQ_FLAG_X_HALF) { // fp16 activations: quantise straight to codes; weights as usual
         e = cudaSuccess;
         if (!(p.flags & ABQ_FLAG_WEIGHTS_PREPARED))
-            e = unpack_i8(reinterpret_cast<const uint32_t *>(p.W), ws + off_w, p.N, p.K, p.w_bits, p.w_signed, stream);
+            e = unpack_i8(reinterpret_cast<const uint32_t *>(p.W), ws + off_w, p.N, p.K, p.w_bits, p.w_signed, stream, folded_zero(p),
+                          p.group_size);
         if (e == cudaSuccess)
             e = quantize_codes(p.X, p.x_quant_scale, ws, p.M, p.K, p.x_bits, stream);
     } else if (p.flags & ABQ_FLAG_WEIGHTS_PREPARED) // the weight codes are in place: expand the activations only
         e = unpack_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.K, p.x_bits, p.x_signed, stream);
     else
         e = unpack_pair_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.x_bits, p.x_signed, reinterpret_cast<const uint32_t *>(p.W),
-                           ws + off_w, p.N, p.w_bits, p.w_signed, p.K, stream);
+                           ws + off_w, p.N, p.w_bits, p.w_signed, p.K, stream, folded_zero(p), p.group_size);
     if (e != cudaSuccess)
         return e;
     UmmaArgs a;
@@ -519,9 +777,17 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
     const int BN = st->tile[0];
     // instruction descriptor, kind::i8: D format S32 (2) at bit 4, A / B format (0 = U8, 1 = S8) at bits 7 / 10,
     // both operands K-major (bits 15, 16 clear), N >> 3 at bit 17, M >> 4 at bit 24
-    a.idesc = (2u << 4) | ((p.x_signed ? 1u : 0u) << 7) | ((p.w_signed ? 1u : 0u) << 10) | ((uint32_t)(BN >> 3) << 17) |
+    const bool b_signed = p.w_signed || folded_zero(p) != nullptr; // w - zero is a signed code
+    a.idesc = (2u << 4) | ((p.x_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(BN >> 3) << 17) |
               ((uint32_t)(kUmmaBM >> 4) << 24);
     a.status = p.status_word;
+    a.kb_per_group = p.scale_mode == ABQ_SCALE_GROUP ? p.group_size / kUmmaBK : 0;
+    a.scale_groups = p.scale_mode == ABQ_SCALE_GROUP ? p.K / p.group_size : 0;
+    if (st->tile[2]) {
+        // |acc of a group| < 2^22 with signed activations (|x| <= 128), |w - z| <= 255 and one K block per group
+        const bool magic = p.x_signed && a.kb_per_group == 1;
+        return magic ? launch_group<true>(st, a, stream) : launch_group<false>(st, a, stream);
+    }
     switch (BN) {
     case 64: return launch_bn<64>(st, a, stream);
     case 128: return launch_bn<128>(st, a, stream);

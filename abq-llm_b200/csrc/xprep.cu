@@ -29,8 +29,16 @@ __device__ __forceinline__ void transpose4(uint32_t a, uint32_t b, uint32_t c, u
 // sectors (each lane alone would write its 32 bytes as two half sectors).
 constexpr int kUnpackRuns = 4; // runs per thread, 256 threads apart: all their plane loads are in flight before the first is used
 
+// Optional zero points: `zero` [rows][zgroups] bytes, one per run of `zwords` plane words of a row of `kw` words; the
+// codes written are then code - zero (two's complement bytes; the caller guarantees that the difference fits int8).
+struct ZeroTable {
+    const uint8_t *zero;
+    int kw, zwords, zgroups;
+};
+
 template <int BITS>
-__device__ __forceinline__ void unpack_run(const uint32_t *__restrict__ planes, uint32_t *__restrict__ out, long L, long idx0, int is_signed)
+__device__ __forceinline__ void unpack_run(const uint32_t *__restrict__ planes, uint32_t *__restrict__ out, long L, long idx0, int is_signed,
+                                           const ZeroTable zt = ZeroTable{ nullptr, 0, 0, 0 })
 {
     uint32_t p[kUnpackRuns][BITS];
     bool live[kUnpackRuns];
@@ -57,7 +65,13 @@ __device__ __forceinline__ void unpack_run(const uint32_t *__restrict__ planes, 
         uint32_t hi[4], lo[4];
         transpose4(r[3], r[2], r[1], r[0], hi);
         transpose4(r[7], r[6], r[5], r[4], lo);
-        const uint4 q0 = make_uint4(lo[3], hi[3], lo[2], hi[2]), q1 = make_uint4(lo[1], hi[1], lo[0], hi[0]);
+        uint4 q0 = make_uint4(lo[3], hi[3], lo[2], hi[2]), q1 = make_uint4(lo[1], hi[1], lo[0], hi[0]);
+        if (zt.zero && live[u]) { // the 32 codes of a run share their scale group
+            const long row = idx / zt.kw;
+            const uint32_t zz = 0x01010101u * zt.zero[row * zt.zgroups + (int)(idx - row * zt.kw) / zt.zwords];
+            q0 = make_uint4(__vsub4(q0.x, zz), __vsub4(q0.y, zz), __vsub4(q0.z, zz), __vsub4(q0.w, zz));
+            q1 = make_uint4(__vsub4(q1.x, zz), __vsub4(q1.y, zz), __vsub4(q1.z, zz), __vsub4(q1.w, zz));
+        }
         const bool odd = threadIdx.x & 1;
         const uint4 give = odd ? q0 : q1; // the even lane hands over its second half, the odd lane its first half
         uint4 got;
@@ -73,50 +87,52 @@ __device__ __forceinline__ void unpack_run(const uint32_t *__restrict__ planes, 
     }
 }
 
-__device__ __forceinline__ void unpack_any(const uint32_t *planes, uint32_t *out, long L, long idx, int bits, int is_signed)
+__device__ __forceinline__ void unpack_any(const uint32_t *planes, uint32_t *out, long L, long idx, int bits, int is_signed,
+                                           const ZeroTable zt = ZeroTable{ nullptr, 0, 0, 0 })
 {
     switch (bits) { // uniform per block
-    case 1: unpack_run<1>(planes, out, L, idx, is_signed); break;
-    case 2: unpack_run<2>(planes, out, L, idx, is_signed); break;
-    case 3: unpack_run<3>(planes, out, L, idx, is_signed); break;
-    case 4: unpack_run<4>(planes, out, L, idx, is_signed); break;
-    case 5: unpack_run<5>(planes, out, L, idx, is_signed); break;
-    case 6: unpack_run<6>(planes, out, L, idx, is_signed); break;
-    case 7: unpack_run<7>(planes, out, L, idx, is_signed); break;
-    default: unpack_run<8>(planes, out, L, idx, is_signed); break;
+    case 1: unpack_run<1>(planes, out, L, idx, is_signed, zt); break;
+    case 2: unpack_run<2>(planes, out, L, idx, is_signed, zt); break;
+    case 3: unpack_run<3>(planes, out, L, idx, is_signed, zt); break;
+    case 4: unpack_run<4>(planes, out, L, idx, is_signed, zt); break;
+    case 5: unpack_run<5>(planes, out, L, idx, is_signed, zt); break;
+    case 6: unpack_run<6>(planes, out, L, idx, is_signed, zt); break;
+    case 7: unpack_run<7>(planes, out, L, idx, is_signed, zt); break;
+    default: unpack_run<8>(planes, out, L, idx, is_signed, zt); break;
     }
 }
 
 template <int BITS>
 __global__ void __launch_bounds__(256) unpack_i8_kernel(const uint32_t *__restrict__ planes, uint32_t *__restrict__ out, long L,
-                                                        int is_signed)
+                                                        int is_signed, const ZeroTable zt)
 {
     pdl_launch_dependents(); // a GEMM kernel launched programmatically behind this one may start its set-up
-    unpack_run<BITS>(planes, out, L, (long)blockIdx.x * (256 * kUnpackRuns) + threadIdx.x, is_signed);
+    unpack_run<BITS>(planes, out, L, (long)blockIdx.x * (256 * kUnpackRuns) + threadIdx.x, is_signed, zt);
 }
 
 // Both operands of a GEMM in one launch: blocks [0, blocks_a) expand operand a, the rest operand b.  Lets the
 // dependent GEMM kernel start its set-up early (programmatic launch) and saves a launch per GEMM.
 __global__ void __launch_bounds__(256) unpack_pair_kernel(const uint32_t *__restrict__ pa, uint32_t *__restrict__ oa, long La, int bits_a,
                                                           int signed_a, unsigned blocks_a, const uint32_t *__restrict__ pb,
-                                                          uint32_t *__restrict__ ob, long Lb, int bits_b, int signed_b)
+                                                          uint32_t *__restrict__ ob, long Lb, int bits_b, int signed_b, const ZeroTable zt_b)
 {
     pdl_launch_dependents();
     if (blockIdx.x < blocks_a) {
         unpack_any(pa, oa, La, (long)blockIdx.x * (256 * kUnpackRuns) + threadIdx.x, bits_a, signed_a);
     } else {
-        unpack_any(pb, ob, Lb, (long)(blockIdx.x - blocks_a) * (256 * kUnpackRuns) + threadIdx.x, bits_b, signed_b);
+        unpack_any(pb, ob, Lb, (long)(blockIdx.x - blocks_a) * (256 * kUnpackRuns) + threadIdx.x, bits_b, signed_b, zt_b);
     }
 }
 
 cudaError_t unpack_pair_i8(const uint32_t *planes_a, void *out_a, int rows_a, int bits_a, int signed_a, const uint32_t *planes_b, void *out_b,
-                           int rows_b, int bits_b, int signed_b, int K, cudaStream_t stream)
+                           int rows_b, int bits_b, int signed_b, int K, cudaStream_t stream, const uint8_t *zero_b, int zero_group)
 {
+    const ZeroTable zt = { zero_b, K / 32, zero_b ? zero_group / 32 : 1, zero_b ? K / zero_group : 1 };
     const long La = (long)rows_a * (K / 32), Lb = (long)rows_b * (K / 32);
     const long per = 256 * kUnpackRuns;
     const unsigned blocks_a = (unsigned)((La + per - 1) / per), blocks_b = (unsigned)((Lb + per - 1) / per);
     unpack_pair_kernel<<<blocks_a + blocks_b, 256, 0, stream>>>(planes_a, reinterpret_cast<uint32_t *>(out_a), La, bits_a, signed_a, blocks_a,
-                                                                planes_b, reinterpret_cast<uint32_t *>(out_b), Lb, bits_b, signed_b);
+                                                                planes_b, reinterpret_cast<uint32_t *>(out_b), Lb, bits_b, signed_b, zt);
     return cudaGetLastError();
 }
 
@@ -162,11 +178,13 @@ cudaError_t quantize_codes(const void *in_half, const float *scale, void *out, i
     return cudaGetLastError();
 }
 
-cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream)
+cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream, const uint8_t *zero,
+                      int zero_group)
 {
+    const ZeroTable zt = { zero, K / 32, zero ? zero_group / 32 : 1, zero ? K / zero_group : 1 };
     const long L = (long)rows * (K / 32);
     const unsigned blocks = (unsigned)((L + 256 * kUnpackRuns - 1) / (256 * kUnpackRuns));
-#define CALL(B) (unpack_i8_kernel<B><<<blocks, 256, 0, stream>>>(planes, reinterpret_cast<uint32_t *>(out), L, is_signed), cudaGetLastError())
+#define CALL(B) (unpack_i8_kernel<B><<<blocks, 256, 0, stream>>>(planes, reinterpret_cast<uint32_t *>(out), L, is_signed, zt), cudaGetLastError())
     switch (bits) {
     case 1: return CALL(1);
     case 2: return CALL(2);

@@ -266,12 +266,13 @@ def per_config_detail(torch, abq, gemms, reps=20):
     return rows
 
 
-PREFILL_CASES = [(4, 4, 4096, 4096, 4096), (4, 4, 4096, 11008, 4096), (2, 8, 4096, 12288, 4096), (8, 8, 4096, 4096, 11008),
-                 (4, 4, 2048, 4096, 4096), (4, 4, 512, 12288, 4096)]  # (w bits, x bits, M, N, K)
+PREFILL_CASES = [(4, 4, 4096, 4096, 4096, 0), (4, 4, 4096, 11008, 4096, 0), (2, 8, 4096, 12288, 4096, 0), (8, 8, 4096, 4096, 11008, 0),
+                 (4, 4, 2048, 4096, 4096, 0), (4, 4, 512, 12288, 4096, 0),
+                 (4, 8, 4096, 4096, 4096, 128), (2, 8, 2048, 11008, 4096, 128)]  # (w bits, x bits, M, N, K, scale group: 0 = per channel)
 
 
 def prefill_leg(torch, abq, reps=10):
-    """Prefill shapes (M >= 512) on the tcgen05 kind::i8 route, per-channel fp16 scale, fp16 output: device time of the
+    """Prefill shapes (M >= 512) on the tcgen05 kind::i8 route, per-channel or per-group fp16 scale, fp16 output: device time of the
     whole call (plane -> int8 expansion of both operands, the GEMM with its fused epilogue) per case, effective
     TOPS = 2*M*N*K / t, and the fraction of twice the measured dense bf16 rate (the int8 rate of the same pipe)."""
     peak = None
@@ -282,18 +283,21 @@ def prefill_leg(torch, abq, reps=10):
     gen.manual_seed(7)
     B = abq.binding
     rows = []
-    for (q, p, M, N, K) in PREFILL_CASES:
+    for (q, p, M, N, K, group) in PREFILL_CASES:
         def planes_of(rows_, bits):
             codes = torch.randint(0, 1 << bits, (rows_, K), dtype=torch.int32, device="cuda", generator=gen)
             out = torch.empty((bits, rows_, K // 32), dtype=torch.int32, device="cuda")
             abq.pack_int32(codes, out, rows_, K, bits)
             return out
         xp, wp = planes_of(M, p), planes_of(N, q)
-        wsc = (torch.rand((N,), device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16)
+        shape = (N, K // group) if group else (N,)
+        wsc = (torch.rand(shape, device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16)
+        wz = torch.randint(0, 1 << q, shape, dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8) if group else None
         out = torch.empty((M, N), dtype=torch.float16, device="cuda")
         work = torch.empty(abq.gemm_workspace_bytes(M, N, K, p, q), dtype=torch.uint8, device="cuda")
-        prm = B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=False, w_signed=False, out_dtype=abq.OUT_FP16,
-                            scale_mode=abq.SCALE_CHANNEL, w_scale=wsc, workspace=work)
+        prm = B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=bool(group), w_signed=False, out_dtype=abq.OUT_FP16,
+                            scale_mode=abq.SCALE_GROUP if group else abq.SCALE_CHANNEL, group_size=group, w_scale=wsc, w_zero=wz,
+                            workspace=work)
         st = abq.gemm_init(prm)
         for _ in range(3):
             abq.gemm_exec(st)
@@ -320,7 +324,8 @@ def prefill_leg(torch, abq, reps=10):
         torch.cuda.synchronize()
         us2 = e0.elapsed_time(e1) * 1e3 / reps
         tops2 = 2.0 * M * N * K / us2 / 1e6
-        rows.append({"wxay": f"W{q}A{p}", "M": M, "N": N, "K": K, "us": round(us, 2), "TOPS": round(tops, 1),
+        rows.append({"wxay": f"W{q}A{p}", "scales": f"g{group} + zero" if group else "channel", "M": M, "N": N, "K": K, "us": round(us, 2),
+                     "TOPS": round(tops, 1),
                      "frac_of_int8_peak": round(tops / peak, 3) if peak else None, "us_weights_prepared": round(us2, 2),
                      "TOPS_weights_prepared": round(tops2, 1), "frac_weights_prepared": round(tops2 / peak, 3) if peak else None})
         del xp, wp, out, work

@@ -63,7 +63,7 @@ def test_per_group(abq, oracle, cuda, M, N, K, q, group, w_signed):
     wz = rng.integers(0, 1 << q, size=(N, G)).astype(np.uint8)
     got, st = run_gemm(abq, planes_dev(oracle, x, 8), planes_dev(oracle, w, q), M, N, K, x_bits=8, w_bits=q, x_signed=True,
                        w_signed=w_signed, out_fp16=True, scale_mode=abq.SCALE_GROUP, group_size=group, w_scale=dev(ws), w_zero=dev(wz),
-                       route=abq.ROUTE_I8_MMA if M <= 16 else abq.ROUTE_AUTO)  # taller: 16 rows per launch, chosen automatically
+                       route=abq.ROUTE_I8_MMA)  # taller than 16 rows: one launch per 16 rows
     assert st.route == abq.ROUTE_I8_MMA
     ref = oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), None, group)
     check_close(got, ref)

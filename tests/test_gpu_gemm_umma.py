@@ -144,3 +144,37 @@ def test_prepared_weights_give_the_same_result(abq, oracle, cuda):
         abq.gemm_exec(st)
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy(), oracle.gemm_values_blas(x, w)), f"call {i}"
+
+
+GROUP_CASES = [
+    # M, N, K, x_bits, x_signed, w_bits, w_signed, group, with_zero, expected route
+    (40, 320, 1024, 8, True, 4, False, 128, True, "umma"),
+    (300, 1000, 1152, 8, True, 2, False, 128, True, "umma"),
+    (512, 4096, 4096, 8, True, 3, False, 128, True, "umma"),
+    (130, 200, 2048, 8, True, 7, False, 256, True, "umma"),
+    (200, 520, 1536, 4, False, 4, False, 128, False, "umma"),     # unsigned activations: conversion instruction path
+    (64, 256, 1024, 8, True, 4, True, 128, False, "umma"),        # signed weights, no zero points
+    (2048, 2048, 512, 8, True, 4, False, 128, True, "umma"),      # several tiles per CTA
+    (100, 512, 4096, 8, True, 8, False, 128, True, "mma"),        # w - z does not fit int8: 16 rows per launch instead
+    (33, 96, 1280, 8, True, 3, False, 640, True, "umma"),
+]
+
+
+@pytest.mark.parametrize("case", GROUP_CASES, ids=lambda c: "M{}N{}K{}a{}w{}g{}{}".format(c[0], c[1], c[2], c[3], c[5], c[7], "z" if c[8] else ""))
+def test_per_group_scales_on_the_tensor_core_route(abq, oracle, cuda, case):
+    """ABQ_SCALE_GROUP at prefill shapes: the accumulator is drained per scale group, zero points are folded into the
+    int8 weight codes.  Against the oracle's float64 dequantised product."""
+    M, N, K, p, xs, q, wsg, group, with_zero, want_route = case
+    rng = np.random.default_rng(M + N + K + q)
+    x = rand_codes(rng, M, K, p, xs)
+    w = rand_codes(rng, N, K, q, wsg)
+    G = K // group
+    scale = rng.uniform(0.001, 0.02, size=(N, G)).astype(np.float16)
+    zero = rng.integers(0, 1 << q, size=(N, G)).astype(np.uint8) if with_zero else None
+    tok = rng.uniform(0.5, 2.0, size=M).astype(np.float32)
+    got, st = run_gemm(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=xs, w_signed=wsg,
+                       out_fp16=True, scale_mode=abq.SCALE_GROUP, group_size=group, w_scale=dev(scale), w_zero=None if zero is None else dev(zero),
+                       x_scale=dev(tok))
+    assert st.route == (abq.ROUTE_I8_UMMA if want_route == "umma" else abq.ROUTE_I8_MMA)
+    ref = oracle.dequant_gemm(x, w, scale, None if zero is None else zero.astype(np.int32), tok, group)
+    check_close(got, ref)
