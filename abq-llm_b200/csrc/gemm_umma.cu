@@ -721,8 +721,18 @@ static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cud
     return launch_kernel(umma_kernel<BN>, &configured, st, args, stream);
 }
 
-// zero points that the weight expansion subtracts (ABQ_SCALE_GROUP on this route), else none
-static const uint8_t *folded_zero(const abq_gemm_params &p) { return p.scale_mode == ABQ_SCALE_GROUP ? p.w_zero : nullptr; }
+// Zero points that the weight expansion subtracts (the codes multiplied are then w - zero, signed): always with per-group
+// scales on this route (the plan has checked that the difference fits int8), with per-channel scales where it fits
+// (unsigned weights of at most 7 bits); otherwise the epilogue subtracts zero * sum(x).
+static const uint8_t *folded_zero(const abq_gemm_params &p)
+{
+    if (p.scale_mode == ABQ_SCALE_GROUP)
+        return p.w_zero;
+    if (p.scale_mode == ABQ_SCALE_CHANNEL && p.out_dtype == ABQ_OUT_FP16 && !p.w_signed && p.w_bits <= 7)
+        return p.w_zero;
+    return nullptr;
+}
+static int folded_group(const abq_gemm_params &p) { return p.scale_mode == ABQ_SCALE_GROUP ? p.group_size : p.K; }
 
 cudaError_t umma_prepare_weights(const abq_gemm_state *st, cudaStream_t stream)
 {
@@ -730,7 +740,7 @@ cudaError_t umma_prepare_weights(const abq_gemm_state *st, cudaStream_t stream)
     size_t off_w, off_sum, total;
     umma_layout(p.M, p.N, p.K, &off_w, &off_sum, &total);
     return unpack_i8(reinterpret_cast<const uint32_t *>(p.W), reinterpret_cast<uint8_t *>(p.workspace) + off_w, p.N, p.K, p.w_bits, p.w_signed,
-                     stream, folded_zero(p), p.group_size);
+                     stream, folded_zero(p), folded_group(p));
 }
 
 cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
@@ -744,19 +754,19 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
         e = cudaSuccess;
         if (!(p.flags & ABQ_FLAG_WEIGHTS_PREPARED))
             e = unpack_i8(reinterpret_cast<const uint32_t *>(p.W), ws + off_w, p.N, p.K, p.w_bits, p.w_signed, stream, folded_zero(p),
-                          p.group_size);
+                          folded_group(p));
         if (e == cudaSuccess)
             e = quantize_codes(p.X, p.x_quant_scale, ws, p.M, p.K, p.x_bits, stream);
     } else if (p.flags & ABQ_FLAG_WEIGHTS_PREPARED) // the weight codes are in place: expand the activations only
         e = unpack_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.K, p.x_bits, p.x_signed, stream);
     else
         e = unpack_pair_i8(reinterpret_cast<const uint32_t *>(p.X), ws, p.M, p.x_bits, p.x_signed, reinterpret_cast<const uint32_t *>(p.W),
-                           ws + off_w, p.N, p.w_bits, p.w_signed, p.K, stream, folded_zero(p), p.group_size);
+                           ws + off_w, p.N, p.w_bits, p.w_signed, p.K, stream, folded_zero(p), folded_group(p));
     if (e != cudaSuccess)
         return e;
     UmmaArgs a;
     a.xsum = nullptr;
-    if (p.scale_mode == ABQ_SCALE_CHANNEL && p.w_zero) {
+    if (p.scale_mode == ABQ_SCALE_CHANNEL && p.w_zero && !folded_zero(p)) {
         rowsum_kernel<<<(p.M + 7) / 8, 256, 0, stream>>>(ws, reinterpret_cast<int *>(ws + off_sum), p.M, p.K, p.x_signed);
         e = cudaGetLastError();
         if (e != cudaSuccess)
@@ -770,7 +780,7 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.D = p.D;
     a.C = reinterpret_cast<const __half *>(p.C);
     a.w_scale = reinterpret_cast<const __half *>(p.w_scale);
-    a.w_zero = p.w_zero;
+    a.w_zero = folded_zero(p) ? nullptr : p.w_zero;
     a.x_scale = p.x_scale;
     a.out_dtype = p.out_dtype;
     a.scale_mode = p.scale_mode;
