@@ -162,8 +162,13 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
     if (s != ABQ_OK)
         return s;
     int route = params->route;
-    if (route == ABQ_ROUTE_AUTO)
-        route = params->M <= 16 ? ABQ_ROUTE_I8_MMA : ABQ_ROUTE_I8_UMMA;
+    if (route == ABQ_ROUTE_AUTO) {
+        // up to 16 rows: one launch of the mma.sync route.  17..32 rows: two such launches still beat the tensor-core
+        // route, whose weight expansion alone costs more (measured on 12288x4096 and 4096x11008), unless the weight
+        // codes are already expanded.  Above: tcgen05.
+        const int small = (params->flags & ABQ_FLAG_WEIGHTS_PREPARED) ? 16 : 32;
+        route = params->M <= small ? ABQ_ROUTE_I8_MMA : ABQ_ROUTE_I8_UMMA;
+    }
     if (params->route == ABQ_ROUTE_AUTO && route == ABQ_ROUTE_I8_UMMA && params->scale_mode == ABQ_SCALE_GROUP) {
         // per-group scales: the tensor-core route drains its accumulator per group where it can (whole K blocks per group,
         // zero points foldable into int8 codes); otherwise the mma.sync route, 16 rows per launch

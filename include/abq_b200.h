@@ -61,7 +61,7 @@ typedef enum abq_scale_mode {
 } abq_scale_mode;
 
 typedef enum abq_route {
-    ABQ_ROUTE_AUTO = 0,     /* M <= 16: I8_MMA; otherwise I8_UMMA (per-group scales it cannot fold: I8_MMA) */
+    ABQ_ROUTE_AUTO = 0,     /* M <= 32 (16 with prepared weights): I8_MMA; otherwise I8_UMMA (per-group scales it cannot fold: I8_MMA) */
     ABQ_ROUTE_B1_MMA = 1,   /* legacy mma.sync b1 AND+POPC over stacked planes (route A) */
     ABQ_ROUTE_I8_MMA = 2,   /* planes recombined in registers, mma.sync s8/u8, TMA-fed, split-K (decode); M > 16 runs 16 rows per launch */
     ABQ_ROUTE_I8_UMMA = 3   /* planes recombined to int8 tiles, tcgen05.mma kind::i8 in TMEM (route B) */
