@@ -1,4 +1,4 @@
-// Prefill-shape GEMM (M > 16), route ABQ_ROUTE_I8_UMMA ("route B").
+// Prefill-shape GEMM (more than 32 rows by default), route ABQ_ROUTE_I8_UMMA ("route B").
 //
 // tcgen05 has no 1-bit MMA kind, but integer arithmetic is exact and associative, so the shift-accumulate
 // over plane pairs (engine/mma_any/aq_bmma_kernel.h:537-565) can be folded into the operands: the p (q) planes
@@ -17,6 +17,7 @@
 //               dequantisation, 16-byte stores; then the accumulator goes back to the MMA warp
 // Every wait is bounded (abq_common.cuh); on expiry the status word is set, the roles leave their loops, the
 // CTA still meets at the final barrier and TMEM is released.
+// Per-group scales: umma_group_kernel below (accumulator drained per scale group).
 #include <cuda.h>
 #include <cstring>
 
