@@ -350,6 +350,22 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_cons
 // thread); the scales of the tile, all groups, are staged once per tile in shared memory as fp32 [group][column].
 // MAGIC: |acc_g| < 2^22 (signed 8-bit activations, one K block per group): int -> float by the 1.5 * 2^23 trick, two
 // pipelined operations instead of a conversion instruction.  Same roles, barriers and bounded waits as umma_kernel.
+// facc[C .. C + 31] += scale[C .. C + 31] * float(v[0 .. 31]); the scales are the same for every lane (shared-memory broadcast)
+template <bool MAGIC, int C>
+__device__ __forceinline__ void scale_add(const int (&v)[32], const float *scales, float (&facc)[64])
+{
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const float4 sc = *reinterpret_cast<const float4 *>(scales + C + j);
+        const float s4[4] = { sc.x, sc.y, sc.z, sc.w };
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float fv = MAGIC ? __int_as_float(v[j + e] + 0x4b400000) - 12582912.0f : (float)v[j + e];
+            facc[C + j + e] = fmaf(s4[e], fv, facc[C + j + e]);
+        }
+    }
+}
+
 constexpr int kGroupBN = 128;
 constexpr int kGroupThreads = 320; // TMA warp, MMA warp, eight epilogue warps: two per TMEM lane quarter, 64 columns each
 
@@ -485,36 +501,40 @@ __global__ void __launch_bounds__(kGroupThreads, 1) umma_group_kernel(const __gr
 #pragma unroll
             for (int c = 0; c < HN; ++c)
                 facc[c] = 0.f;
-            for (int g = 0; g < G; ++g, ++gc) {
+            // Pipelined over 32-column chunks: while chunk i is scaled and added, the tcgen05.ld of chunk i + 1 (the second
+            // half of this group, or the first half of the next group) is already in flight; an accumulator goes back
+            // to the MMA warp as soon as its second half sits in registers.
+            int va[32], vb[32];
+            const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * HN);
+            {
                 const int b = gc % kAccs;
                 ok = mbar_wait_bounded(&acc_full[b], (gc / kAccs) & 1, a.status, STATUS_TIMEOUT_MMA);
                 if (!ok)
                     break;
                 tmem_fence_after();
+                tmem_ld32_nowait(tlane + (uint32_t)(b * BN), va);
+            }
+            for (int g = 0; g < G; ++g) {
+                const int b = gc % kAccs;
                 const float *sg = s_scale + (size_t)g * BN + half * HN;
-                int v[2][32]; // both loads in flight before the first is used
-                tmem_ld32_nowait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * HN), v[0]);
-                tmem_ld32_nowait(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + half * HN + 32), v[1]);
-                tmem_ld_wait();
-                // the accumulator sits in registers: hand its TMEM buffer back before the arithmetic
+                tmem_ld_wait();                                         // first half of group g is in va
+                tmem_ld32_nowait(tlane + (uint32_t)(b * BN + 32), vb);  // second half on its way
+                scale_add<MAGIC, 0>(va, sg, facc);
+                tmem_ld_wait();                                         // second half in vb: the accumulator is free
                 tmem_fence_before();
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&acc_empty[b]);
-#pragma unroll
-                for (int c = 0; c < HN; c += 32) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 sc = *reinterpret_cast<const float4 *>(sg + c + j); // the same address in every lane
-                        const float s4[4] = { sc.x, sc.y, sc.z, sc.w };
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int vi = v[c >> 5][j + e];
-                            const float fv = MAGIC ? __int_as_float(vi + 0x4b400000) - 12582912.0f : (float)vi;
-                            facc[c + j + e] = fmaf(s4[e], fv, facc[c + j + e]);
-                        }
-                    }
+                ++gc;
+                if (g + 1 < G) {
+                    const int nb = gc % kAccs;
+                    ok = mbar_wait_bounded(&acc_full[nb], (gc / kAccs) & 1, a.status, STATUS_TIMEOUT_MMA);
+                    if (!ok)
+                        break;
+                    tmem_fence_after();
+                    tmem_ld32_nowait(tlane + (uint32_t)(nb * BN), va);  // first half of group g + 1 on its way
                 }
+                scale_add<MAGIC, 32>(vb, sg, facc);
             }
             mbar_arrive(par_free); // this thread reads the staged parameters no more
             if (!ok)
