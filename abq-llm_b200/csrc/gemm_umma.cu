@@ -350,6 +350,234 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_cons
 // thread); the scales of the tile, all groups, are staged once per tile in shared memory as fp32 [group][column].
 // MAGIC: |acc_g| < 2^22 (signed 8-bit activations, one K block per group): int -> float by the 1.5 * 2^23 trick, two
 // pipelined operations instead of a conversion instruction.  Same roles, barriers and bounded waits as umma_kernel.
+// cta_group::2 forms: issued by one thread of the even CTA of a pair
+__device__ __forceinline__ void umma2_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(tmem_d),
+                 "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair
+__device__ __forceinline__ void umma2_commit(uint64_t *bar)
+{
+    const unsigned short both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+                 "h"(both)
+                 : "memory");
+}
+// TMA tile load into this CTA's shared memory whose bytes are reported to a barrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const void *tmap, int c0, int c1, uint32_t leader_bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(tmap), "r"(leader_bar), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same GEMM on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile.  Each CTA loads
+// its 128 rows of A and its 128 rows (half the columns) of B, so a K block costs a CTA 32 KB instead of 48 KB for the
+// same arithmetic (the single-CTA kernel is bound by the L2 -> shared-memory feed), and six stages fit.  The even CTA
+// of the pair (the leader) issues the MMAs for both: every 256 x 256 x 32 instruction reads A and B from both CTAs'
+// shared memory and accumulates into both CTAs' TMEM (128 rows x 256 columns each).  Both CTAs' TMA loads report to the
+// leader's `full` barrier; tcgen05.commit multicasts to both CTAs' `empty` / `acc_full` barriers; both CTAs' epilogue
+// warps report to the leader's `acc_empty`.  No TMA load uses cluster multicast.
+constexpr int kPairBN = 256;
+
+__global__ void __launch_bounds__(kUmmaThreads, 1) umma2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                                                const UmmaArgs a)
+{
+    constexpr int BN = kPairBN;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int kABytes = kUmmaBM * kUmmaBK, kBBytes = (BN / 2) * kUmmaBK, kStageBytes = kABytes + kBBytes; // per CTA
+    constexpr int kTmemCols = 2 * BN; // two accumulators: the epilogue drains one while the next tile fills the other
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float *s_scale = reinterpret_cast<float *>(smem + (size_t)a.stages * kStageBytes); // [2][BN] channel scales of a tile
+    int *s_zero = reinterpret_cast<int *>(s_scale + 2 * BN);                            // [2][BN] channel zero points
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_zero + 2 * BN);
+    uint64_t *full = bars, *empty = bars + 8, *acc_full = bars + 16, *acc_empty = bars + 18, *par_ready = bars + 20;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 22);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = a.K / kUmmaBK;
+    const int m_tiles = (a.M + 2 * kUmmaBM - 1) / (2 * kUmmaBM); // 256-row tiles
+    const int total_tiles = m_tiles * ((a.N + BN - 1) / BN);
+    const uint32_t rank = cluster_ctarank();                       // 0: leader
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);    // one arrival per epilogue warp of both CTAs (only the leader's is used)
+            mbar_init(&par_ready[b], 128);  // every epilogue thread has staged its channel parameters
+        }
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) { // TMEM allocation is a warp-wide operation; the same warp frees it at the end
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tmem_fence_before();
+    __syncthreads();
+    cluster_sync_all(); // the peer's barriers are initialised before anything is signalled across
+    tmem_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait_prior_grid(); // operand codes and token sums come from the kernels launched just before
+
+    // Persistent CTA: tiles blockIdx.x, blockIdx.x + gridDim.x, ...; consecutive tiles share the weight (N) tile, so
+    // the CTAs running at one time read few distinct weight tiles and all of the activations out of L2.
+    if (warp == 0) {
+        if (lane == 0) {
+            int kc = 0; // k-blocks requested so far, over all tiles
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+                const int m0 = (tile % m_tiles) * 2 * kUmmaBM + (int)rank * kUmmaBM, n0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < k_blocks; ++kb, ++kc) {
+                    const int s = kc % a.stages;
+                    if (kc >= a.stages && !mbar_wait_bounded(&empty[s], ((kc / a.stages) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *sa = smem + (size_t)s * kStageBytes, *sb = sa + kABytes;
+                    if (rank == 0)
+                        mbar_arrive_expect_tx(&full[s], 2 * kStageBytes); // both CTAs' bytes land on the leader's barrier
+                    const uint32_t leader_full = map_to_cta(smem_u32(&full[s]), 0);
+                    tma_load_2d_pair(sa, &tmap_a, kb * kUmmaBK, m0, leader_full);
+                    tma_load_2d_pair(sb, &tmap_b, kb * kUmmaBK, n0, leader_full);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) { // the leader issues for the pair
+            int kc = 0, it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += pairs, ++it) {
+                const int b = it & 1;
+                if (it >= 2) { // the epilogue has drained this accumulator's previous tile
+                    ok = mbar_wait_bounded(&acc_empty[b], ((it >> 1) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE);
+                    if (!ok)
+                        break;
+                    tmem_fence_after();
+                }
+                const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++kc) {
+                    const int s = kc % a.stages;
+                    ok = mbar_wait_bounded(&full[s], (kc / a.stages) & 1, a.status, STATUS_TIMEOUT_TMA);
+                    if (!ok)
+                        break;
+                    tmem_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
+                    const uint64_t da = make_smem_desc_sw128(sa), db = make_smem_desc_sw128(sb);
+#pragma unroll
+                    for (int k = 0; k < kUmmaBK / 32; ++k) // 32 bytes of K per instruction: advance the start address inside the atom
+                        umma2_i8(tmem_d, da + (uint64_t)(k * 32 >> 4), db + (uint64_t)(k * 32 >> 4), a.idesc, (kb | k) != 0);
+                    umma2_commit(&empty[s]); // arrives, in both CTAs, when the MMAs above have finished reading this stage
+                }
+                if (ok)
+                    umma2_commit(&acc_full[b]); // arrives, in both CTAs, when all MMAs of the tile have written the accumulators
+            }
+        }
+        __syncwarp();
+    } else {
+        // epilogue warps 2..5: a warp may only touch the TMEM lane quarter (warp id % 4)
+        const int quarter = warp & 3;
+        const int et = threadIdx.x - 64; // 0..127 among the epilogue threads
+        const bool channel = a.out_dtype != ABQ_OUT_INT32 && a.scale_mode != ABQ_SCALE_TENSOR_COMPAT;
+        const bool has_zero = channel && a.scale_mode == ABQ_SCALE_CHANNEL && a.w_zero != nullptr;
+        const __half cscale = a.scale_mode == ABQ_SCALE_TENSOR_COMPAT && a.out_dtype != ABQ_OUT_INT32 ? ld_half(a.C) : __half();
+        int it = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs, ++it) {
+            const int b = it & 1;
+            const int m0 = (tile % m_tiles) * 2 * kUmmaBM + (int)rank * kUmmaBM, n0 = (tile / m_tiles) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            float *ts = s_scale + b * BN;
+            int *tz = s_zero + b * BN;
+            if (channel) { // stage the tile's channel parameters while its MMAs still run
+                for (int c = et; c < BN; c += 128) {
+                    const int n = n0 + c;
+                    float sv = 1.f;
+                    int zv = 0;
+                    if (n < a.N) {
+                        if (a.scale_mode == ABQ_SCALE_CHANNEL && a.w_scale)
+                            sv = __half2float(a.w_scale[n]);
+                        if (has_zero)
+                            zv = a.w_zero[n];
+                    }
+                    ts[c] = sv;
+                    tz[c] = zv;
+                }
+                // epilogue threads only, and bounded like every other wait; the other buffer (tile it - 1) stays untouched
+                mbar_arrive(&par_ready[b]);
+                ok = mbar_wait_bounded(&par_ready[b], (it >> 1) & 1, a.status, STATUS_TIMEOUT_PIPE);
+                if (!ok)
+                    break;
+            }
+            float xs = 1.f;
+            int xsum = 0;
+            if (row < a.M) {
+                if (a.x_scale)
+                    xs = a.x_scale[row];
+                if (a.xsum)
+                    xsum = a.xsum[row];
+            }
+            ok = mbar_wait_bounded(&acc_full[b], (it >> 1) & 1, a.status, STATUS_TIMEOUT_MMA);
+            if (!ok)
+                break;
+            tmem_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                int v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * BN + c), v);
+                if (row >= a.M)
+                    continue;
+                if (a.out_dtype == ABQ_OUT_INT32)
+                    store_chunk<0>(a, v, row, n0 + c, ts + c, tz + c, xs, xsum, cscale, has_zero);
+                else if (!channel)
+                    store_chunk<1>(a, v, row, n0 + c, ts + c, tz + c, xs, xsum, cscale, has_zero);
+                else
+                    store_chunk<2>(a, v, row, n0 + c, ts + c, tz + c, xs, xsum, cscale, has_zero);
+            }
+            tmem_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[b]), 0)); // this warp's quarter is free again: tell the leader
+        }
+    }
+
+    tmem_fence_before();
+    __syncthreads();
+    cluster_sync_all(); // neither CTA leaves while the other may still signal its barriers or read its shared memory
+    if (warp == 1) {
+        tmem_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// ABQ_SCALE_GROUP on the tensor-core route: every scale group (kb_per_group K blocks) is multiplied into a fresh TMEM
+// accumulator, exactly, and the epilogue warps drain it while the next group is multiplied into the other one:
+//     facc[n] += scale[n][g] * acc_g[n]                                              (fp32, one row per thread)
+// The zero points are not seen here: the weight codes in the scratch are w - zero[n][g] (signed int8, exact for widths
+// up to 7 bits; see unpack_i8), so acc_g already is sum x * (w - z).  BN = 128 columns (128 fp32 partial sums per
+// thread); the scales of the tile, all groups, are staged once per tile in shared memory as fp32 [group][column].
+// MAGIC: |acc_g| < 2^22 (signed 8-bit activations, one K block per group): int -> float by the 1.5 * 2^23 trick, two
+// pipelined operations instead of a conversion instruction.  Same roles, barriers and bounded waits as umma_kernel.
 // facc[C .. C + 31] += scale[C .. C + 31] * float(v[0 .. 31]); the scales are the same for every lane (shared-memory broadcast)
 template <bool MAGIC, int C>
 __device__ __forceinline__ void scale_add(const int (&v)[32], const float *scales, float (&facc)[64])
@@ -669,7 +897,11 @@ abq_status umma_plan(abq_gemm_state *st)
         return ABQ_ERR_INVALID_ARG;
     if (grouped)
         BN = kGroupBN;
-    const int stage_bytes = (kUmmaBM + BN) * kUmmaBK;
+    // CTA pairs (256 x 256 tiles, umma2_kernel): a third less operand traffic per SM and six stages.  Measured equal to the
+    // single-CTA kernel on the LLaMA shapes (that one already runs at the rate its rounds of tiles allow), so it is
+    // opt-in: ABQ_UMMA_PAIRS=1
+    const bool paired = !grouped && BN == 256 && p.M > kUmmaBM && env_int("ABQ_UMMA_PAIRS", 0) != 0;
+    const int stage_bytes = paired ? (kUmmaBM + kPairBN / 2) * kUmmaBK : (kUmmaBM + BN) * kUmmaBK;
     const size_t param_bytes = grouped ? (size_t)scale_groups * kGroupBN * 4 : (size_t)4 * BN * 4;
     int stages = (int)((216 * 1024 - param_bytes) / stage_bytes);
     stages = stages > 8 ? 8 : stages;
@@ -682,21 +914,26 @@ abq_status umma_plan(abq_gemm_state *st)
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
     const uint64_t dims_a[2] = { (uint64_t)p.K, (uint64_t)p.M }, dims_b[2] = { (uint64_t)p.K, (uint64_t)p.N };
     const uint64_t strides[1] = { (uint64_t)p.K };
-    const uint32_t box_a[2] = { (uint32_t)kUmmaBK, (uint32_t)kUmmaBM }, box_b[2] = { (uint32_t)kUmmaBK, (uint32_t)BN };
+    const uint32_t box_a[2] = { (uint32_t)kUmmaBK, (uint32_t)kUmmaBM }, box_b[2] = { (uint32_t)kUmmaBK, (uint32_t)(paired ? kPairBN / 2 : BN) };
     if (!encode_tmap(st->tmap[0], TMAP_U8, 2, ws, dims_a, strides, box_a, TMAP_SWIZZLE_128B) ||
         !encode_tmap(st->tmap[1], TMAP_U8, 2, ws + off_w, dims_b, strides, box_b, TMAP_SWIZZLE_128B))
         return ABQ_ERR_CUDA;
-    const long tiles = (long)m_tiles * ((p.N + BN - 1) / BN);
-    st->grid[0] = (unsigned)(tiles < sms ? tiles : sms); // persistent: a CTA per SM, tiles dealt round-robin
+    long tiles = (long)m_tiles * ((p.N + BN - 1) / BN);
+    if (paired) { // 256-row tiles, two CTAs each
+        tiles = (long)((p.M + 2 * kUmmaBM - 1) / (2 * kUmmaBM)) * ((p.N + kPairBN - 1) / kPairBN);
+        const long pairs = tiles < sms / 2 ? tiles : sms / 2;
+        st->grid[0] = (unsigned)(2 * pairs);
+    } else
+        st->grid[0] = (unsigned)(tiles < sms ? tiles : sms); // persistent: a CTA per SM, tiles dealt round-robin
     st->grid[1] = 1;
     st->grid[2] = 1;
     st->block[0] = grouped ? kGroupThreads : kUmmaThreads;
     st->block[1] = st->block[2] = 1;
-    st->cluster = 1;
+    st->cluster = paired ? 2 : 1;
     st->shared_mem_size = 1024 + (size_t)stages * stage_bytes + param_bytes + 256;
     st->tile[0] = BN;
     st->tile[1] = stages;
-    st->tile[2] = grouped ? 1 : 0;
+    st->tile[2] = grouped ? 1 : (paired ? 2 : 0);
     return ABQ_OK;
 }
 
@@ -720,11 +957,18 @@ static cudaError_t launch_kernel(Kernel kern, size_t *configured, const abq_gemm
     cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = st->shared_mem_size;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (st->cluster == 2) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, args);
 }
 
@@ -733,6 +977,12 @@ static cudaError_t launch_group(const abq_gemm_state *st, const UmmaArgs &args, 
 {
     static thread_local size_t configured = 0;
     return launch_kernel(umma_group_kernel<MAGIC>, &configured, st, args, stream);
+}
+
+static cudaError_t launch_pair(const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
+{
+    static thread_local size_t configured = 0;
+    return launch_kernel(umma2_kernel, &configured, st, args, stream);
 }
 
 template <int BN>
@@ -814,6 +1064,10 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.status = p.status_word;
     a.kb_per_group = p.scale_mode == ABQ_SCALE_GROUP ? p.group_size / kUmmaBK : 0;
     a.scale_groups = p.scale_mode == ABQ_SCALE_GROUP ? p.K / p.group_size : 0;
+    if (st->tile[2] == 2) { // CTA pairs: one instruction covers 256 rows
+        a.idesc = (a.idesc & ~(0x1fu << 24)) | ((uint32_t)(2 * kUmmaBM >> 4) << 24);
+        return launch_pair(st, a, stream);
+    }
     if (st->tile[2]) {
         // |acc of a group| < 2^22 with signed activations (|x| <= 128), |w - z| <= 255 and one K block per group
         const bool magic = p.x_signed && a.kb_per_group == 1;

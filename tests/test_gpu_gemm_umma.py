@@ -178,3 +178,24 @@ def test_per_group_scales_on_the_tensor_core_route(abq, oracle, cuda, case):
     assert st.route == (abq.ROUTE_I8_UMMA if want_route == "umma" else abq.ROUTE_I8_MMA)
     ref = oracle.dequant_gemm(x, w, scale, None if zero is None else zero.astype(np.int32), tok, group)
     check_close(got, ref)
+
+
+@pytest.mark.parametrize("case", [(130, 72, 640, 6, 7, False, True), (300, 520, 1152, 8, 4, True, False), (1000, 12000, 384, 8, 3, True, False),
+                                  (4096, 4096, 256, 4, 4, False, False)], ids=lambda c: "M{}N{}K{}a{}w{}".format(*c[:5]))
+def test_cta_pairs(abq, oracle, cuda, case, monkeypatch):
+    """The cta_group::2 kernel (opt-in): a pair of CTAs per 256 x 256 tile, ragged tiles in both directions, a second
+    CTA without rows, several tiles per pair.  int32 bit-exact, and the fp16 per-channel epilogue."""
+    monkeypatch.setenv("ABQ_UMMA_PAIRS", "1")
+    monkeypatch.setenv("ABQ_UMMA_BN", "256")   # small problems would otherwise get narrower, unpaired tiles
+    M, N, K, p, q, xs, ws = case
+    rng = np.random.default_rng(M * 3 + N)
+    x, w = rand_codes(rng, M, K, p, xs), rand_codes(rng, N, K, q, ws)
+    xp, wp = planes_dev(oracle, x, p), planes_dev(oracle, w, q)
+    got, st = run_gemm(abq, xp, wp, M, N, K, x_bits=p, w_bits=q, x_signed=xs, w_signed=ws, route=abq.ROUTE_I8_UMMA)
+    assert st.cluster == 2
+    want = oracle.gemm_values_blas(x, w)
+    assert np.array_equal(got, want)
+    scale = rng.uniform(0.001, 0.02, size=N).astype(np.float16)
+    got16, _ = run_gemm(abq, xp, wp, M, N, K, x_bits=p, w_bits=q, x_signed=xs, w_signed=ws, route=abq.ROUTE_I8_UMMA, out_fp16=True,
+                        scale_mode=abq.SCALE_CHANNEL, w_scale=dev(scale))
+    check_close(got16, want.astype(np.float64) * scale.astype(np.float64)[None, :])
