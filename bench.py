@@ -151,42 +151,52 @@ def build_workload(abq, torch, seed):
     torch.cuda.synchronize()
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     gemms = []
+    # e2e mode: the activation planes of a whole pass travel in ONE pinned host buffer -> one device buffer, the fp16
+    # results of a pass in one device buffer -> one pinned host buffer; every GEMM works on its views of the two
+    order = [(q, M, N, K) for q in WBITS for M in MS for (N, K) in SHAPES]
+    x_words = sum(XBITS * M * (K // 32) for (_, M, _, K) in order)
+    out_elems = sum(M * N for (_, M, N, _) in order)
+    e2e = {"x_host": torch.empty(x_words, dtype=torch.int32).pin_memory(), "x_dev": torch.empty(x_words, dtype=torch.int32, device="cuda"),
+           "out_dev": torch.empty(out_elems, dtype=torch.float16, device="cuda"), "out_host": torch.empty(out_elems, dtype=torch.float16).pin_memory()}
+    x_at = out_at = 0
     # one bit width after the other, as a model with one weight format runs them: consecutive GEMMs use the same kernel
-    for q in WBITS:
-        for M in MS:
-            for (N, K) in SHAPES:
-                ws_bytes = abq.gemm_workspace_bytes(M, N, K, XBITS, q)
-                for c in range(WEIGHT_COPIES):
-                    planes, wsc, wz = weights[(q, N, K)][c]
-                    out = torch.empty((M, N), dtype=torch.float16, device="cuda")
-                    out_host = torch.empty((M, N), dtype=torch.float16).pin_memory()
-                    work = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
-                    host_x, dev_x = acts[(M, K)]
-                    stage_x = torch.empty_like(dev_x)  # e2e: destination of the per-step host->device copy
-                    states = {}
-                    for name, xbuf in (("resident", dev_x), ("e2e", stage_x)):
-                        p = B.make_params(M, N, K, xbuf, planes, out, x_bits=XBITS, w_bits=q, x_signed=True, w_signed=False,
-                                          out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP, group_size=GROUP, w_scale=wsc, w_zero=wz,
-                                          flags=abq.FLAG_PDL if os.environ.get("ABQ_BENCH_PDL", "1") == "1" else 0, workspace=work,
-                                          status_word=status)
-                        states[name] = abq.gemm_init(p)
-                    gemms.append(dict(M=M, N=N, K=K, q=q, copy=c, states=states, out=out, out_host=out_host, host_x=host_x, stage_x=stage_x,
-                                      keep=(planes, wsc, wz, work, dev_x), bytes=algorithmic_bytes(M, N, K, XBITS, q), ops=2 * M * N * K))
+    for (q, M, N, K) in order:
+        ws_bytes = abq.gemm_workspace_bytes(M, N, K, XBITS, q)
+        host_x, dev_x = acts[(M, K)]
+        nx, no = XBITS * M * (K // 32), M * N
+        e2e["x_host"][x_at:x_at + nx].copy_(host_x.view(-1))
+        stage_x = e2e["x_dev"][x_at:x_at + nx].view(XBITS, M, K // 32)
+        out_e2e = e2e["out_dev"][out_at:out_at + no].view(M, N)
+        x_at, out_at = x_at + nx, out_at + no
+        for c in range(WEIGHT_COPIES):
+            planes, wsc, wz = weights[(q, N, K)][c]
+            out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+            work = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+            states = {}
+            for name, xbuf, obuf in (("resident", dev_x, out), ("e2e", stage_x, out_e2e)):
+                p = B.make_params(M, N, K, xbuf, planes, obuf, x_bits=XBITS, w_bits=q, x_signed=True, w_signed=False,
+                                  out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP, group_size=GROUP, w_scale=wsc, w_zero=wz,
+                                  flags=abq.FLAG_PDL if os.environ.get("ABQ_BENCH_PDL", "1") == "1" else 0, workspace=work,
+                                  status_word=status)
+                states[name] = abq.gemm_init(p)
+            gemms.append(dict(M=M, N=N, K=K, q=q, copy=c, states=states, out=out, host_x=host_x,
+                              keep=(planes, wsc, wz, work, dev_x), bytes=algorithmic_bytes(M, N, K, XBITS, q), ops=2 * M * N * K))
+    for g in gemms:
+        g["e2e"] = e2e
     return gemms, status
 
 
 def one_pass(abq, gemms, copy, mode):
     """One pass over the 36 GEMMs (weight copy `copy`).  mode 'resident': operands already in HBM;
-    mode 'e2e': activation planes come from pinned host memory and the result goes back to the host."""
-    for g in gemms:
-        if g["copy"] != copy:
-            continue
-        if mode == "e2e":
-            g["stage_x"].copy_(g["host_x"], non_blocking=True)
-            abq.gemm_exec(g["states"]["e2e"])
-            g["out_host"].copy_(g["out"], non_blocking=True)
-        else:
-            abq.gemm_exec(g["states"]["resident"])
+    mode 'e2e': the pass's activation planes come from pinned host memory in one copy and its results go back to
+    pinned host memory in one copy, both inside the pass."""
+    mine = [g for g in gemms if g["copy"] == copy]
+    if mode == "e2e" and mine:
+        mine[0]["e2e"]["x_dev"].copy_(mine[0]["e2e"]["x_host"], non_blocking=True)      # this pass's activation planes, host -> device
+    for g in mine:
+        abq.gemm_exec(g["states"]["e2e" if mode == "e2e" else "resident"])
+    if mode == "e2e" and mine:
+        mine[0]["e2e"]["out_host"].copy_(mine[0]["e2e"]["out_dev"], non_blocking=True)  # this pass's results, device -> host
 
 
 def capture_passes(torch, abq, gemms, mode):
@@ -687,6 +697,8 @@ def main():
     e2e = whole_job_rate(world, bytes_per_step, args.steps, ms_e2e) / 1e9
     h2d = sum(g["host_x"].numel() * 4 for g in gemms if g["copy"] == 0)
     d2h = sum(g["out"].numel() * 2 for g in gemms if g["copy"] == 0)
+    if args.only or args.shape:
+        h2d, d2h = gemms[0]["e2e"]["x_host"].numel() * 4, gemms[0]["e2e"]["out_host"].numel() * 2  # the buffers travel whole
     peak, peak_kind = measured_peaks()
     per_gpu = bytes_per_step * args.steps / (ms * 1e-3) / 1e9
     line = {
