@@ -14,6 +14,28 @@ cudaError_t pack_int4(const void *in, uint32_t *planes, int rows, int K, int bit
 cudaError_t quantize_pack_half(const __half *in, const float *scale, uint32_t *planes, int rows, int K, int bits, int mode,
                                cudaStream_t stream);
 
+// Largest dynamic shared-memory size already opted in for one kernel, per device (the attribute is per device and
+// function).  One instance per kernel instantiation and host thread: `static thread_local SmemOptIn done;`
+struct SmemOptIn {
+    static constexpr int kMaxDevices = 64;
+    size_t bytes[kMaxDevices] = {};
+    template <typename Kernel>
+    cudaError_t ensure(Kernel kern, size_t need)
+    {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess)
+            return e;
+        const bool tracked = dev >= 0 && dev < kMaxDevices;
+        if (tracked && need <= bytes[dev])
+            return cudaSuccess;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+        if (e == cudaSuccess && tracked)
+            bytes[dev] = need;
+        return e;
+    }
+};
+
 // ---- xprep.cu
 // zero != NULL: the codes written are code - zero[row][k / zero_group] (the caller guarantees that this fits int8)
 cudaError_t unpack_i8(const uint32_t *planes, void *out, int rows, int K, int bits, int is_signed, cudaStream_t stream,

@@ -691,12 +691,11 @@ static cudaError_t launch_variant(const abq_gemm_state *st, const DecodeArgs &ar
     const int grouped = args.scale_mode != ABQ_SCALE_GROUP ? 0 : (args.groups_per_scale == 1 ? 1 : 2);
     auto kern = grouped == 0 ? decode_kernel<Q, MT, XU8, false, true, NW>
                              : (grouped == 1 ? decode_kernel<Q, MT, XU8, true, true, NW> : decode_kernel<Q, MT, XU8, true, false, NW>);
-    static thread_local size_t configured[3] = { 0, 0, 0 }; // per instantiation and thread: largest size already opted in
-    if (st->shared_mem_size > configured[grouped]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->shared_mem_size);
+    static thread_local SmemOptIn opted[3]; // per instantiation, scale mode and host thread
+    {
+        cudaError_t e = opted[grouped].ensure(kern, st->shared_mem_size);
         if (e != cudaSuccess)
             return e;
-        configured[grouped] = st->shared_mem_size;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(st->grid[0], 1, 1);

@@ -938,14 +938,13 @@ abq_status umma_plan(abq_gemm_state *st)
 }
 
 template <typename Kernel>
-static cudaError_t launch_kernel(Kernel kern, size_t *configured, const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
+static cudaError_t launch_kernel(Kernel kern, SmemOptIn *opted, const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
 {
     const int threads = st->block[0];
-    if (st->shared_mem_size > *configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st->shared_mem_size);
+    {
+        cudaError_t e = opted->ensure(kern, st->shared_mem_size);
         if (e != cudaSuccess)
             return e;
-        *configured = st->shared_mem_size;
     }
     CUtensorMap ta, tb;
     memcpy(&ta, st->tmap[0], sizeof(ta));
@@ -975,21 +974,21 @@ static cudaError_t launch_kernel(Kernel kern, size_t *configured, const abq_gemm
 template <bool MAGIC>
 static cudaError_t launch_group(const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
 {
-    static thread_local size_t configured = 0;
-    return launch_kernel(umma_group_kernel<MAGIC>, &configured, st, args, stream);
+    static thread_local SmemOptIn opted;
+    return launch_kernel(umma_group_kernel<MAGIC>, &opted, st, args, stream);
 }
 
 static cudaError_t launch_pair(const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
 {
-    static thread_local size_t configured = 0;
-    return launch_kernel(umma2_kernel, &configured, st, args, stream);
+    static thread_local SmemOptIn opted;
+    return launch_kernel(umma2_kernel, &opted, st, args, stream);
 }
 
 template <int BN>
 static cudaError_t launch_bn(const abq_gemm_state *st, const UmmaArgs &args, cudaStream_t stream)
 {
-    static thread_local size_t configured = 0;
-    return launch_kernel(umma_kernel<BN>, &configured, st, args, stream);
+    static thread_local SmemOptIn opted;
+    return launch_kernel(umma_kernel<BN>, &opted, st, args, stream);
 }
 
 // Zero points that the weight expansion subtracts (the codes multiplied are then w - zero, signed): always with per-group
