@@ -1,0 +1,6 @@
+// decode_kernel for 1-bit weights (all token-tile, scale-mode and warp-count variants)
+#include "gemm_decode_kernel.cuh"
+
+namespace abq {
+ABQ_DECODE_WIDTH(1)
+} // namespace abq

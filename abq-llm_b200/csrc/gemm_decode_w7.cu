@@ -1,0 +1,6 @@
+// decode_kernel for 7-bit weights (all token-tile, scale-mode and warp-count variants)
+#include "gemm_decode_kernel.cuh"
+
+namespace abq {
+ABQ_DECODE_WIDTH(7)
+} // namespace abq
