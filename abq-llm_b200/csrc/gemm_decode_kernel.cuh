@@ -205,7 +205,9 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
     constexpr int kStageBytes = Q * 1024; // [plane][16 rows][64 B]
     constexpr int kRec = decode_record_bytes(MT);
     using X = Expand<Q>;
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment as an offset from the array itself: a pointer rebuilt from an integer would lose its address space
+    // and every access behind it would compile to a generic load
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *ring_base = smem;
     uint8_t *rec_base = ring_base + (size_t)NW * a.ring * kStageBytes;
     int *red = reinterpret_cast<int *>(rec_base + (size_t)a.stages_per_slice * 4 * kRec); // [warp][4 MT][32 lanes]

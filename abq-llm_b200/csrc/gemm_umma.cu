@@ -177,7 +177,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) umma_kernel(const __grid_cons
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int kABytes = kUmmaBM * kUmmaBK, kBBytes = BN * kUmmaBK, kStageBytes = kABytes + kBBytes;
     constexpr int kTmemCols = 2 * BN; // two accumulators: the epilogue drains one while the next tile fills the other
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment as an offset from the array itself: a pointer rebuilt from an integer would lose its address space
+    // and every access behind it would compile to a generic load
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     float *s_scale = reinterpret_cast<float *>(smem + (size_t)a.stages * kStageBytes); // [2][BN] channel scales of a tile
     int *s_zero = reinterpret_cast<int *>(s_scale + 2 * BN);                            // [2][BN] channel zero points
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_zero + 2 * BN);
@@ -399,7 +401,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) umma2_kernel(const __grid_con
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int kABytes = kUmmaBM * kUmmaBK, kBBytes = (BN / 2) * kUmmaBK, kStageBytes = kABytes + kBBytes; // per CTA
     constexpr int kTmemCols = 2 * BN; // two accumulators: the epilogue drains one while the next tile fills the other
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment as an offset from the array itself: a pointer rebuilt from an integer would lose its address space
+    // and every access behind it would compile to a generic load
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     float *s_scale = reinterpret_cast<float *>(smem + (size_t)a.stages * kStageBytes); // [2][BN] channel scales of a tile
     int *s_zero = reinterpret_cast<int *>(s_scale + 2 * BN);                            // [2][BN] channel zero points
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_zero + 2 * BN);
@@ -606,7 +610,9 @@ __global__ void __launch_bounds__(kGroupThreads, 1) umma_group_kernel(const __gr
     constexpr int kABytes = kUmmaBM * kUmmaBK, kBBytes = BN * kUmmaBK, kStageBytes = kABytes + kBBytes;
     constexpr int kAccs = 4;              // accumulators in flight: the hand-over MMA -> epilogue -> MMA takes longer than two groups
     constexpr int kTmemCols = kAccs * BN; // all 512 columns
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment as an offset from the array itself: a pointer rebuilt from an integer would lose its address space
+    // and every access behind it would compile to a generic load
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int G = a.scale_groups;
     float *s_scale = reinterpret_cast<float *>(smem + (size_t)a.stages * kStageBytes); // [G][BN]
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_scale + (size_t)G * BN);
