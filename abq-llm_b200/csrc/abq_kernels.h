@@ -49,7 +49,7 @@ cudaError_t unpack_pair_i8(const uint32_t *planes_a, void *out_a, int rows_a, in
 // Bytes of one decode-route activation record (one per 128 input features): MT token tiles of 8.
 __host__ __device__ constexpr int decode_record_bytes(int MT) { return 1024 * MT + 64; }
 
-// ---- gemm_decode.cu (route ABQ_ROUTE_I8_MMA, M <= 16)
+// ---- gemm_decode.cu (route ABQ_ROUTE_I8_MMA; taller problems run 16 rows per launch)
 constexpr int kDecodeMaxSlices = 8;  // largest split-K factor (the workspace reserves that many partial slots)
 // clear_counters: zero the split-K arrival counters now and wait for it (plans that are launched many times);
 // otherwise the caller queues decode_clear_counters() on its stream before the launch (one-shot calls)

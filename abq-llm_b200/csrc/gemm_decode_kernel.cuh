@@ -1,4 +1,4 @@
-// Decode-shape GEMM (M <= 16), route ABQ_ROUTE_I8_MMA: one kernel per GEMM.
+// Decode-shape GEMM (up to 16 rows per launch), route ABQ_ROUTE_I8_MMA: one kernel per GEMM.
 //
 // HBM-bound and, at LLaMA sizes, only a few microseconds long, so the kernel is built around two things:
 // every weight plane word is read exactly once, and nothing on the path from "activations are ready" to "output
