@@ -58,8 +58,17 @@ def test_validation_needs_no_device(abq):
     p.w_bits = 2
     p.out_dtype, p.scale_mode = 1, 3  # fp16 + group scales without a scale pointer
     assert init(ctypes.byref(p), ctypes.byref(st)) == 1
+    p.out_dtype, p.scale_mode = 0, 0
+    p.flags = abq.FLAG_X_HALF            # fp16 activations: need the quantiser scale and signed codes
+    assert init(ctypes.byref(p), ctypes.byref(st)) == 1
+    p.x_quant_scale, p.x_signed, p.route = 4096, 1, abq.ROUTE_B1_MMA
+    assert init(ctypes.byref(p), ctypes.byref(st)) == 2  # the 1-bit route multiplies planes
+    p.flags, p.route = 0, 0
+    p.M = 0
+    assert init(ctypes.byref(p), ctypes.byref(st)) == 1  # empty problem
     assert st.init_success == 0
     assert abq.lib().abq_gemm_exec(ctypes.byref(st), None) == 5  # not initialised
+    assert abq.lib().abq_gemm_prepare_weights(ctypes.byref(st), None) == 5
     assert abq.lib().abq_pack_int32(None, None, 1, 128, 4, None) == 1
 
 
