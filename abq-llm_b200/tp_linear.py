@@ -87,21 +87,33 @@ class TensorParallelBlockLinears:
                 s, z = scale[rows], (None if zero is None else zero[rows])
             self.layers[spec.name] = backend.make_linear(c, s, z, w_bits, group)
 
+    def _buf(self, name, M):
+        # where a layer exposes the buffer its plan reads, the producing elementwise step writes straight into it
+        return self.layers[name].input(M) if hasattr(self.layers[name], "input") else None
+
+    # The block in the three pieces that lie between its two all-reduces (a caller that replays CUDA graphs captures
+    # the pieces and launches the collectives between them):
+    def attention_part(self, x):
+        """x -> this rank's partial of the attention output projection (to be all-reduced)."""
+        be, M = self.backend, x.shape[0]
+        qkv = self.layers["qkv"](x)                                                        # [M][3 * hidden / world]
+        attn = be.glue_attention(qkv, self.layers["qkv"].out_features // 3, self._buf("o", M))  # this rank's heads
+        return self.layers["o"](attn)                                                      # partial [M][hidden]
+
+    def ffn_part(self, x, o):
+        """(x, all-reduced o) -> (h, this rank's partial of the down projection (to be all-reduced))."""
+        be, M = self.backend, x.shape[0]
+        h = be.glue_residual(x, o, self._buf("gate_up", M))
+        gu = self.layers["gate_up"](h)                                                     # [M][2 * ffn_local]
+        act = be.glue_swiglu(gu, self.layers["gate_up"].out_features // 2, self._buf("down", M))
+        return h, self.layers["down"](act)                                                 # partial [M][hidden]
+
     def forward(self, x):
         """x: fp16 [M][hidden], replicated on every rank.  Returns fp16 [M][hidden], replicated."""
         be = self.backend
-        M = x.shape[0]
-        # where a layer exposes the buffer its plan reads, the producing elementwise step writes straight into it
-        buf = lambda name: self.layers[name].input(M) if hasattr(self.layers[name], "input") else None
-        hl = self.layers["qkv"].out_features // 3
-        qkv = self.layers["qkv"](x)                          # [M][3 * hidden / world]
-        attn = be.glue_attention(qkv, hl, buf("o"))          # [M][hidden / world]: this rank's heads
-        o = self.layers["o"](attn)                           # partial [M][hidden]
+        o = self.attention_part(x)
         be.all_reduce(o)
-        h = be.glue_residual(x, o, buf("gate_up"))
-        gu = self.layers["gate_up"](h)                       # [M][2 * ffn_local]
-        act = be.glue_swiglu(gu, self.layers["gate_up"].out_features // 2, buf("down"))
-        d = self.layers["down"](act)                         # partial [M][hidden]
+        h, d = self.ffn_part(x, o)
         be.all_reduce(d)
         return be.glue_residual(h, d, None)
 

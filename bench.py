@@ -573,9 +573,11 @@ def run_tp_decode(args, rank, world, local):
         if rank == 0:
             print(f"tp_decode: batch {M} warmed up", file=sys.stderr, flush=True)
         graph = None
-        # one GPU: the whole step as one CUDA graph.  Several ranks: eager launches (a first attempt to capture the NCCL
-        # all-reduce inside the graph did not finish on this stack, so collectives are never captured here)
-        if not args.no_graph and world == 1:
+        pieces = None
+        # one GPU: the whole step as one CUDA graph.  Several ranks: the pieces between the all-reduces as CUDA graphs and
+        # the NCCL all-reduces launched between them (a capture that contained the collectives did not finish on this
+        # stack, so collectives are never captured here)
+        if not args.no_graph and world == 1 and not args.tp_pieces:
             try:
                 side = torch.cuda.Stream()
                 with torch.cuda.stream(side):
@@ -583,14 +585,42 @@ def run_tp_decode(args, rank, world, local):
                     with torch.cuda.graph(graph, stream=side):
                         step()
                 torch.cuda.synchronize()
-            except Exception as e:  # a collective that cannot be captured: time the eager step instead
+            except Exception as e:
                 graph = None
                 if rank == 0:
                     print(f"graph capture failed ({type(e).__name__}): timing eager launches", file=sys.stderr)
-        fn = (lambda i: graph.replay()) if graph is not None else (lambda i: step())
+        elif not args.no_graph:
+            side = torch.cuda.Stream()
+            pieces, pool = [], None
+            with torch.cuda.stream(side):
+                cur, pend = x, None
+                for b in blocks:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side, pool=pool):
+                        xin = cur if pend is None else backend.glue_residual(pend[0], pend[1], None)
+                        o = b.attention_part(xin)
+                    pool = pool or g.pool()
+                    pieces.append((g, o))
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side, pool=pool):
+                        h, d = b.ffn_part(xin, o)
+                    pieces.append((g, d))
+                    pend = (h, d)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side, pool=pool):
+                    y = backend.glue_residual(pend[0], pend[1], None)
+                pieces.append((g, None))
+            torch.cuda.synchronize()
+
+        def step_pieces():
+            for g, t in pieces:
+                g.replay()
+                if t is not None:
+                    backend.all_reduce(t)
+        fn = (lambda i: graph.replay()) if graph is not None else ((lambda i: step_pieces()) if pieces else (lambda i: step()))
         ms, _ = timed(torch, dist, fn, max(3, args.steps // 10), 3)
         n = max(3, args.steps // 10)
-        results.append({"batch": M, "ms_per_step": ms / n, "tokens_per_s": M * n / (ms * 1e-3), "cuda_graph": graph is not None})
+        results.append({"batch": M, "ms_per_step": ms / n, "tokens_per_s": M * n / (ms * 1e-3), "cuda_graph": "whole step" if graph is not None else ("between the all-reduces" if pieces else "no")})
     if rank == 0:
         wbytes = layers * sum(sp.out_features * sp.in_features for sp in tp.llama_block_specs(hidden, ffn)) * q // 8
         best = results[0]
@@ -646,6 +676,7 @@ def main():
     ap.add_argument("--workload", default="decode_sweep", choices=["decode_sweep", "tp_decode"],
                     help="decode_sweep (default, the headline metric) or tp_decode: tensor-parallel LLaMA-7B linear stack")
     ap.add_argument("--layers", type=int, default=32, help="tp_decode: decoder blocks")
+    ap.add_argument("--tp-pieces", action="store_true", help="tp_decode on one GPU: graphs between the all-reduce points, as several ranks run it")
     ap.add_argument("--no-graph", action="store_true", help="profiling aid: launch kernel by kernel instead of one CUDA graph per pass")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling aid: skip the host-side reference timing")
     args = ap.parse_args()
