@@ -161,6 +161,16 @@ def gemm_prepare_weights(state: GemmState, stream=None) -> None:
     _check(lib().abq_gemm_prepare_weights(ctypes.byref(state), _stream(stream)), "abq_gemm_prepare_weights")
 
 
+def peer_allreduce_half(bufs_dev: int, signals_dev: int, rank: int, world: int, signal_offset: int, out, n_halves: int, counter,
+                        status_word=None, stream=None) -> None:
+    """One-shot sum over the ranks' partial buffers (peer-mapped pointers, see abq_peer_allreduce_half)."""
+    f = lib().abq_peer_allreduce_half
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_long, ctypes.c_void_p,
+                  ctypes.c_void_p, ctypes.c_void_p]
+    _check(f(bufs_dev, signals_dev, rank, world, signal_offset, _ptr(out), n_halves, _ptr(counter), _ptr(status_word), _stream(stream)),
+           "abq_peer_allreduce_half")
+
+
 def gemm(params: GemmParams, stream=None) -> None:
     _check(lib().abq_gemm(ctypes.byref(params), _stream(stream)), "abq_gemm")
 

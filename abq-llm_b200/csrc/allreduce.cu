@@ -1,0 +1,99 @@
+// Sum of the fp16 partial results of the row-parallel GEMMs over the ranks of one node, read straight out of the peers'
+// memory (NVLink peer loads; no multimem, no library collective).  Replaces the ncclAllReduce that the reference's
+// FasterTransformer fork issues after the attention output and the FFN down projections
+// (TensorParallelGptContextAttentionLayer.cc:50-53, TensorParallelSiluFfnLayer.cc:53-57) for the small messages of a
+// decode step, where the latency of a collective call, not its bandwidth, is what costs.
+//
+// One-shot: every rank's partial lies in a buffer that all ranks have mapped (bufs[r] on every rank); a rank tells each
+// peer that its buffer is written (a flag in the peer's signal pad, release at system scope), waits for the peers'
+// flags in its own pad (acquire, bounded), then reads all buffers and adds them in rank order in fp32, so every rank
+// gets the same bits.  The flag value is a call counter kept on the device, so a CUDA graph can replay the launch.
+// A buffer may be written again only after another all-reduce of the same ranks has completed in between (each
+// all-reduce is a barrier), which holds when every layer owns its buffer.
+#include <cuda_fp16.h>
+
+#include "abq_common.cuh"
+#include "abq_kernels.h"
+
+namespace abq {
+
+constexpr int kAllreduceThreads = 1024;
+
+__global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const __half *const *bufs, uint32_t *const *signals, int rank,
+                                                                           int world, int signal_offset, __half *out, long n, uint32_t *counter, int *status)
+{
+    __shared__ uint32_t s_epoch;
+    if (threadIdx.x == 0)
+        s_epoch = *counter + 1;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
+        const int peer = threadIdx.x;
+        // everything earlier in the stream (the GEMM that wrote bufs[rank]) is complete: publish, then wait for the peer
+        __threadfence_system();
+        uint32_t *theirs = signals[peer] + signal_offset + rank; // my column of the peer's pad
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        const uint32_t *mine = signals[rank] + signal_offset + peer;
+        const unsigned long long t0 = globaltimer_ns();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if ((int)(v - epoch) >= 0)
+                break;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) { // the peer never arrived: record it and carry on (the sum is then void)
+                if (status)
+                    atomicOr(status, STATUS_TIMEOUT_PIPE);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    for (long i = (long)threadIdx.x * 8; i < n; i += (long)kAllreduceThreads * 8) { // 8 halves = 16 bytes
+        float acc[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
+        for (int r = 0; r < world; ++r) {
+            const uint4 v = __ldcv(reinterpret_cast<const uint4 *>(bufs[r] + i)); // no stale cached copy of a peer's line
+            const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]);
+                acc[2 * e] += f.x;
+                acc[2 * e + 1] += f.y;
+            }
+        }
+        uint4 o;
+        __half2 *oh = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            oh[e] = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
+        *reinterpret_cast<uint4 *>(out + i) = o;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        *counter = epoch;
+}
+
+cudaError_t peer_allreduce(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world, int signal_offset, void *out,
+                           long n_halves, uint32_t *counter, int *status, cudaStream_t stream)
+{
+    peer_allreduce_kernel<<<1, kAllreduceThreads, 0, stream>>>(reinterpret_cast<const __half *const *>(bufs_dev), signals_dev, rank, world,
+                                                               signal_offset, reinterpret_cast<__half *>(out), n_halves, counter, status);
+    return cudaGetLastError();
+}
+
+} // namespace abq
+
+extern "C" abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world,
+                                              int signal_offset, void *out, long n_halves, uint32_t *counter, int *status_word,
+                                              abq_stream_t stream)
+{
+    if (!bufs_dev || !signals_dev || !out || !counter || world < 1 || world > 32 || rank < 0 || rank >= world || n_halves <= 0 ||
+        n_halves % 8 != 0 || signal_offset < 0)
+        return ABQ_ERR_INVALID_ARG;
+    cudaError_t e = abq::peer_allreduce(bufs_dev, signals_dev, rank, world, signal_offset, out, n_halves, counter, status_word,
+                                        reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        abq::set_last_cuda_error(e);
+        return ABQ_ERR_CUDA;
+    }
+    return ABQ_OK;
+}

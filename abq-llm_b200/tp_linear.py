@@ -68,8 +68,8 @@ def shard_of(spec: LinearSpec, rank: int, world: int, unit: int = 128) -> Tuple[
 class TensorParallelBlockLinears:
     """The linear layers of one decoder block on one rank.
 
-    ``backend.make_linear(codes, scale, zero, w_bits, group)`` returns an object with ``__call__(x_half) -> fp16``;
-    ``backend.all_reduce(t)`` sums over ranks in place; ``backend.glue`` supplies the elementwise stand-ins between the
+    ``backend.make_linear(codes, scale, zero, w_bits, group, reduce_output=...)`` returns an object with
+    ``__call__(x_half) -> fp16``; ``backend.all_reduce(t)`` returns the sum over ranks (in ``t`` or in a tensor of its own); ``backend.glue`` supplies the elementwise stand-ins between the
     GEMMs (attention itself is outside this path: the first third of the QKV output stands in for its result).
     """
 
@@ -85,7 +85,7 @@ class TensorParallelBlockLinears:
                 s, z = scale[rows][:, gsl], (None if zero is None else zero[rows][:, gsl])
             else:      # per-channel parameters follow the rows (replicated for row-parallel layers)
                 s, z = scale[rows], (None if zero is None else zero[rows])
-            self.layers[spec.name] = backend.make_linear(c, s, z, w_bits, group)
+            self.layers[spec.name] = backend.make_linear(c, s, z, w_bits, group, reduce_output=spec.parallel == "row")
 
     def _buf(self, name, M):
         # where a layer exposes the buffer its plan reads, the producing elementwise step writes straight into it
@@ -111,11 +111,9 @@ class TensorParallelBlockLinears:
     def forward(self, x):
         """x: fp16 [M][hidden], replicated on every rank.  Returns fp16 [M][hidden], replicated."""
         be = self.backend
-        o = self.attention_part(x)
-        be.all_reduce(o)
+        o = be.all_reduce(self.attention_part(x))
         h, d = self.ffn_part(x, o)
-        be.all_reduce(d)
-        return be.glue_residual(h, d, None)
+        return be.glue_residual(h, be.all_reduce(d), None)
 
 
 class AbqLinear:
@@ -123,8 +121,9 @@ class AbqLinear:
     scale (ABQ_FLAG_X_HALF) and writes fp16 through its fused dequantisation (per-channel or per-group scale and zero point, per-token activation scale)."""
 
     def __init__(self, abq, torch, codes, scale, zero, w_bits: int, group: int, x_bits: int = 8, x_scale: float = 16.0,
-                 max_tokens: int = 64):
+                 max_tokens: int = 64, make_out=None):
         self.abq, self.torch = abq, torch
+        self.make_out = make_out  # row-parallel layers: output buffers that the other ranks can read
         self.out_features, self.in_features = codes.shape
         N, K = codes.shape
         self.w_bits, self.x_bits, self.group = w_bits, x_bits, group
@@ -144,7 +143,8 @@ class AbqLinear:
         key = M
         if key not in self.plans:
             B = self.abq.binding
-            out = self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda")
+            out = (self.make_out(M, self.out_features) if self.make_out else
+                   self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda"))
             x_view = self.torch.empty((M, self.in_features), dtype=self.torch.float16, device="cuda")  # the GEMM reads fp16 here
             p = B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out, x_bits=self.x_bits, w_bits=self.w_bits,
                               x_signed=True, w_signed=False, out_dtype=self.abq.OUT_FP16,
@@ -178,13 +178,38 @@ class AbqBackend:
             raise RuntimeError("AbqBackend needs a CUDA device: there is no CPU path")
         self.abq, self.torch, self.dist = abq, torch, dist
         self.x_bits, self.x_scale, self.max_tokens = x_bits, x_scale, max_tokens
+        import os
+        self.peer_reduce = dist is not None and dist.get_world_size() > 1 and os.environ.get("ABQ_TP_NCCL", "0") != "1"
+        self._reduced = {}
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
 
-    def make_linear(self, codes, scale, zero, w_bits, group):
-        return AbqLinear(self.abq, self.torch, codes, scale, zero, w_bits, group, self.x_bits, self.x_scale, self.max_tokens)
+    def make_linear(self, codes, scale, zero, w_bits, group, reduce_output=False):
+        make_out = self._peer_visible_output if (reduce_output and self.peer_reduce) else None
+        return AbqLinear(self.abq, self.torch, codes, scale, zero, w_bits, group, self.x_bits, self.x_scale, self.max_tokens, make_out)
+
+    # ---- all-reduce of the row-parallel partials.  Several ranks on one node: the partial buffers live in symmetric
+    # memory (every rank has every rank's buffer mapped) and the library's one-shot kernel adds them over NVLink peer
+    # loads -- one launch, capturable in a CUDA graph.  Otherwise (or with ABQ_TP_NCCL=1): torch.distributed.
+    def _peer_visible_output(self, M, N):
+        import torch.distributed._symmetric_memory as symm
+        t = symm.empty((M, N), dtype=self.torch.float16, device="cuda")
+        h = symm.rendezvous(t, self.dist.group.WORLD)
+        self._reduced[t.data_ptr()] = (h, t, self.torch.empty((M, N), dtype=self.torch.float16, device="cuda"),
+                                       self.torch.zeros(1, dtype=self.torch.int32, device="cuda"))
+        return t
 
     def all_reduce(self, t):
-        if self.dist is not None and self.dist.get_world_size() > 1:
+        if self.dist is None or self.dist.get_world_size() == 1:
+            return t
+        entry = self._reduced.get(t.data_ptr())
+        if entry is None:
             self.dist.all_reduce(t)
+            return t
+        h, _, out, counter = entry
+        # the upper half of the pad: the lower words belong to the symmetric-memory library's own barriers
+        self.abq.peer_allreduce_half(h.buffer_ptrs_dev, h.signal_pad_ptrs_dev, h.rank, h.world_size, h.signal_pad_size // 8, out, t.numel(),
+                                     counter, self.status)
+        return out
 
     def glue_attention(self, qkv, hl, out=None):
         if out is None:

@@ -574,10 +574,10 @@ def run_tp_decode(args, rank, world, local):
             print(f"tp_decode: batch {M} warmed up", file=sys.stderr, flush=True)
         graph = None
         pieces = None
-        # one GPU: the whole step as one CUDA graph.  Several ranks: the pieces between the all-reduces as CUDA graphs and
-        # the NCCL all-reduces launched between them (a capture that contained the collectives did not finish on this
-        # stack, so collectives are never captured here)
-        if not args.no_graph and world == 1 and not args.tp_pieces:
+        # The whole step as one CUDA graph: on one GPU, and on several ranks when the all-reduce is the library's own
+        # one-shot kernel over peer memory.  With NCCL all-reduces (ABQ_TP_NCCL=1): the pieces between them as graphs
+        # and the collectives launched in between (a capture that contained NCCL collectives did not finish on this stack)
+        if not args.no_graph and (world == 1 or backend.peer_reduce) and not args.tp_pieces:
             try:
                 side = torch.cuda.Stream()
                 with torch.cuda.stream(side):

@@ -179,6 +179,24 @@ ABQ_API abq_status abq_quantize_pack_half(const void *in_half, const float *scal
  */
 ABQ_API abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_stream_t stream);
 
+/*
+ * Sum of fp16 partial results over the ranks of one node, read out of the peers' memory (NVLink peer loads): what a
+ * row-parallel linear layer needs after its GEMM.  Replaces the ncclAllReduce of the reference's FasterTransformer fork
+ * (TensorParallelGptContextAttentionLayer.cc:50-53, TensorParallelSiluFfnLayer.cc:53-57) for decode-sized messages.
+ *   bufs_dev     device array of `world` pointers: every rank's partial buffer as mapped into THIS process (peer
+ *                mappings, e.g. torch symmetric memory `buffer_ptrs_dev`); bufs_dev[rank] is the local one, already
+ *                written by earlier work on `stream`
+ *   signals_dev  device array of `world` pointers to the ranks' signal pads; uint32 words signal_offset .. signal_offset +
+ *                world - 1 of every pad belong to this call site and are zero before first use
+ *   out          local result, n_halves fp16 values (n_halves % 8 == 0); must not alias a partial buffer
+ *   counter      device uint32, zero before first use: the call count (lets a CUDA graph replay the launch)
+ * Every rank adds in rank order in fp32: all ranks get the same bits.  A partial buffer may be written again only
+ * after another all-reduce of the same ranks has completed.  The wait for the peers is bounded (status_word).
+ */
+ABQ_API abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world,
+                                           int signal_offset, void *out, long n_halves, uint32_t *counter, int *status_word,
+                                           abq_stream_t stream);
+
 /* Bit-planes -> int8 codes, row-major [rows][K] (two's complement for signed; unsigned 8-bit codes are
  * stored as uint8).  Used by route B; exported because weight planes can be expanded once and cached. */
 ABQ_API abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, int K, int bits, int is_signed,

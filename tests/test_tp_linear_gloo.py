@@ -31,7 +31,7 @@ class NumpyBackend:
         from oracle import oracle as O
         self.O, self.group, self.dist, self.x_scale = O, group, dist_mod, x_scale
 
-    def make_linear(self, codes, scale, zero, w_bits, group):
+    def make_linear(self, codes, scale, zero, w_bits, group, reduce_output=False):
         be = self
 
         class L:
@@ -50,6 +50,7 @@ class NumpyBackend:
         if self.dist is not None:
             tt = torch.from_numpy(t)
             self.dist.all_reduce(tt)
+        return t
 
     def glue_attention(self, qkv, hl, out=None):
         return np.ascontiguousarray(qkv[:, :hl])

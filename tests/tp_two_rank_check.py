@@ -1,0 +1,56 @@
+"""Helper of test_gpu_tp_two_ranks.py, run under torch.distributed.run with two ranks (one GPU each): the block linears
+with the library's one-shot peer all-reduce against the same block with torch.distributed (NCCL) all-reduces."""
+import importlib.util
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from conftest import load_package
+    abq = load_package()
+    spec = importlib.util.spec_from_file_location("tp_linear_two_ranks", ROOT / "abq-llm_b200" / "tp_linear.py")
+    tp = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = tp
+    spec.loader.exec_module(tp)
+    hidden, ffn, q = 1024, 2816, 4
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    weights = []
+    for sp in tp.llama_block_specs(hidden, ffn):
+        codes = torch.randint(0, 1 << q, (sp.out_features, sp.in_features), dtype=torch.int32, device="cuda", generator=gen)
+        scale = (torch.rand((sp.out_features,), device="cuda", generator=gen) * 0.004 + 0.001).half()
+        zero = torch.randint(0, 1 << q, (sp.out_features,), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8)
+        weights.append((codes, scale, zero))
+    outs = {}
+    for mode in ("0", "1"):
+        os.environ["ABQ_TP_NCCL"] = mode
+        be = tp.AbqBackend(abq, torch, dist, x_bits=8, x_scale=8.0, max_tokens=32)
+        assert be.peer_reduce == (mode == "0")
+        block = tp.TensorParallelBlockLinears(be, hidden, ffn, rank, world, weights, q, 0)
+        for M in (1, 8, 32):
+            gen.manual_seed(M)
+            x = torch.randn((M, hidden), device="cuda", generator=gen).half()
+            for _ in range(3):   # repeated calls: the call counters of the peer all-reduce advance
+                y = block.forward(x)
+            torch.cuda.synchronize()
+            outs[(mode, M)] = y.clone()
+        assert int(be.status.item()) == 0
+    ok = all(torch.equal(outs[("0", M)], outs[("1", M)]) for M in (1, 8, 32))
+    print(f"rank {rank} PEER_EQUALS_NCCL {ok}", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
