@@ -8,6 +8,8 @@
 // peer that its buffer is written (a flag in the peer's signal pad, release at system scope), waits for the peers'
 // flags in its own pad (acquire, bounded), then reads all buffers and adds them in rank order in fp32, so every rank
 // gets the same bits.  The flag value is a call counter kept on the device, so a CUDA graph can replay the launch.
+// Several blocks share the message (remote loads are latency-bound: more of them in flight); block 0 flags the peers,
+// every block waits for the peers' flags, and the last block to finish advances the counter.
 // A buffer may be written again only after another all-reduce of the same ranks has completed in between (each
 // all-reduce is a barrier), which holds when every layer owns its buffer.
 #include <cuda_fp16.h>
@@ -22,17 +24,20 @@ constexpr int kAllreduceThreads = 1024;
 __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const __half *const *bufs, uint32_t *const *signals, int rank,
                                                                            int world, int signal_offset, __half *out, long n, uint32_t *counter, int *status)
 {
+    // counter[0]: calls completed; counter[1]: blocks of this call that have finished
     __shared__ uint32_t s_epoch;
     if (threadIdx.x == 0)
-        s_epoch = *counter + 1;
+        s_epoch = *reinterpret_cast<volatile uint32_t *>(counter) + 1; // (only the last block of a call writes it, after all have read it)
     __syncthreads();
     const uint32_t epoch = s_epoch;
     if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
         const int peer = threadIdx.x;
-        // everything earlier in the stream (the GEMM that wrote bufs[rank]) is complete: publish, then wait for the peer
-        __threadfence_system();
-        uint32_t *theirs = signals[peer] + signal_offset + rank; // my column of the peer's pad
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        if (blockIdx.x == 0) {
+            // everything earlier in the stream (the GEMM that wrote bufs[rank]) is complete: publish
+            __threadfence_system();
+            uint32_t *theirs = signals[peer] + signal_offset + rank; // my column of the peer's pad
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        }
         const uint32_t *mine = signals[rank] + signal_offset + peer;
         const unsigned long long t0 = globaltimer_ns();
         for (;;) {
@@ -48,7 +53,7 @@ __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const
         }
     }
     __syncthreads();
-    for (long i = (long)threadIdx.x * 8; i < n; i += (long)kAllreduceThreads * 8) { // 8 halves = 16 bytes
+    for (long i = ((long)blockIdx.x * kAllreduceThreads + threadIdx.x) * 8; i < n; i += (long)gridDim.x * kAllreduceThreads * 8) { // 16 bytes
         float acc[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
         for (int r = 0; r < world; ++r) {
             const uint4 v = __ldcv(reinterpret_cast<const uint4 *>(bufs[r] + i)); // no stale cached copy of a peer's line
@@ -68,14 +73,22 @@ __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const
         *reinterpret_cast<uint4 *>(out + i) = o;
     }
     __syncthreads();
-    if (threadIdx.x == 0)
-        *counter = epoch;
+    if (threadIdx.x == 0) {
+        const uint32_t done = atomicAdd(counter + 1, 1u);
+        if (done == gridDim.x - 1) { // every block of this call has read the counter and finished
+            counter[1] = 0;
+            __threadfence();
+            counter[0] = epoch;
+        }
+    }
 }
 
 cudaError_t peer_allreduce(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world, int signal_offset, void *out,
                            long n_halves, uint32_t *counter, int *status, cudaStream_t stream)
 {
-    peer_allreduce_kernel<<<1, kAllreduceThreads, 0, stream>>>(reinterpret_cast<const __half *const *>(bufs_dev), signals_dev, rank, world,
+    long blocks = (n_halves / 8 + kAllreduceThreads - 1) / kAllreduceThreads; // one 16-byte piece per thread where that needs <= 32 blocks
+    blocks = blocks < 1 ? 1 : (blocks > 32 ? 32 : blocks);
+    peer_allreduce_kernel<<<(unsigned)blocks, kAllreduceThreads, 0, stream>>>(reinterpret_cast<const __half *const *>(bufs_dev), signals_dev, rank, world,
                                                                signal_offset, reinterpret_cast<__half *>(out), n_halves, counter, status);
     return cudaGetLastError();
 }

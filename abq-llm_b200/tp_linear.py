@@ -195,7 +195,7 @@ class AbqBackend:
         t = symm.empty((M, N), dtype=self.torch.float16, device="cuda")
         h = symm.rendezvous(t, self.dist.group.WORLD)
         self._reduced[t.data_ptr()] = (h, t, self.torch.empty((M, N), dtype=self.torch.float16, device="cuda"),
-                                       self.torch.zeros(1, dtype=self.torch.int32, device="cuda"))
+                                       self.torch.zeros(2, dtype=self.torch.int32, device="cuda"))
         return t
 
     def all_reduce(self, t):

@@ -189,7 +189,8 @@ ABQ_API abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_str
  *   signals_dev  device array of `world` pointers to the ranks' signal pads; uint32 words signal_offset .. signal_offset +
  *                world - 1 of every pad belong to this call site and are zero before first use
  *   out          local result, n_halves fp16 values (n_halves % 8 == 0); must not alias a partial buffer
- *   counter      device uint32, zero before first use: the call count (lets a CUDA graph replay the launch)
+ *   counter      two device uint32, zero before first use: the call count (lets a CUDA graph replay the launch) and a
+ *                block ticket
  * Every rank adds in rank order in fp32: all ranks get the same bits.  A partial buffer may be written again only
  * after another all-reduce of the same ranks has completed.  The wait for the peers is bounded (status_word).
  */
