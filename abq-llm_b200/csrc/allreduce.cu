@@ -73,7 +73,9 @@ __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const
         *reinterpret_cast<uint4 *>(out + i) = o;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && gridDim.x == 1) {
+        counter[0] = epoch; // a lone block needs no ticket
+    } else if (threadIdx.x == 0) {
         const uint32_t done = atomicAdd(counter + 1, 1u);
         if (done == gridDim.x - 1) { // every block of this call has read the counter and finished
             counter[1] = 0;
