@@ -22,19 +22,34 @@ __device__ __forceinline__ void put_code(uint32_t (&r)[8], int j, uint32_t code)
     r[s] |= (code & 0xffu) << (8 * y);
 }
 
-// One thread per output word (= 32 codes).  `L` = rows * K / 32 words per plane.
+// One thread per output word (= 32 codes = 128 bytes of input).  `L` = rows * K / 32 words per plane.
+// A thread that fetched its own 128 bytes would make every load instruction of the warp touch 32 different lines (256
+// L1 wavefronts per 4 KB: the kernel then stops at about 4.5 TB/s of input whatever the DRAM does), so a warp fetches
+// its 4 KB with consecutive lanes on consecutive 16-byte chunks and hands them over through shared memory, chunk
+// position XOR run index so that both the stores and the per-run reads are free of bank conflicts.
 template <int BITS>
 __global__ void __launch_bounds__(kPackThreads) pack_int32_kernel(const int32_t *__restrict__ in, uint32_t *__restrict__ planes,
                                                                   long L)
 {
+    __shared__ int4 stage[kPackThreads * 8];
+    const int lane = threadIdx.x & 31;
     const long idx = (long)blockIdx.x * kPackThreads + threadIdx.x;
+    const long warp_run0 = idx - lane;
+    int4 *mine = stage + (threadIdx.x - lane) * 8; // this warp's 256 chunks
+    const int4 *src = reinterpret_cast<const int4 *>(in) + warp_run0 * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = i * 32 + lane, run = c >> 3, pos = c & 7;
+        if (warp_run0 + run < L)
+            mine[run * 8 + (pos ^ (run & 7))] = __ldg(src + c);
+    }
+    __syncwarp();
     if (idx >= L)
         return;
-    const int4 *src = reinterpret_cast<const int4 *>(in + idx * 32);
     int4 v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-        v[i] = __ldg(src + i);
+        v[i] = mine[lane * 8 + (i ^ (lane & 7))];
     uint32_t r[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
