@@ -102,7 +102,7 @@ extern "C" abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint3
                                               abq_stream_t stream)
 {
     if (!bufs_dev || !signals_dev || !out || !counter || world < 1 || world > 32 || rank < 0 || rank >= world || n_halves <= 0 ||
-        n_halves % 8 != 0 || signal_offset < 0)
+        n_halves % 8 != 0 || signal_offset < 0 || (reinterpret_cast<uintptr_t>(out) & 15))
         return ABQ_ERR_INVALID_ARG;
     cudaError_t e = abq::peer_allreduce(bufs_dev, signals_dev, rank, world, signal_offset, out, n_halves, counter, status_word,
                                         reinterpret_cast<cudaStream_t>(stream));

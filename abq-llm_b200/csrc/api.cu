@@ -103,7 +103,8 @@ static abq_status validate(const abq_gemm_params &p)
             return ABQ_ERR_INVALID_ARG;
         }
     }
-    if ((reinterpret_cast<uintptr_t>(p.X) | reinterpret_cast<uintptr_t>(p.W)) & 15)
+    // the kernels move operands and results in 16-byte pieces: a misaligned pointer would fault on the device
+    if ((reinterpret_cast<uintptr_t>(p.X) | reinterpret_cast<uintptr_t>(p.W) | reinterpret_cast<uintptr_t>(p.D)) & 15)
         return ABQ_ERR_INVALID_ARG;
     if (p.flags & ABQ_FLAG_X_HALF) {
         if (!p.x_quant_scale || !p.x_signed)
@@ -246,6 +247,8 @@ abq_status abq_gemm(const abq_gemm_params *params, abq_stream_t stream)
 static abq_status check_pack_args(const void *in, const void *planes, int rows, int K, int bits)
 {
     if (!in || !planes || rows <= 0 || K < 128 || K % 128 != 0 || bits < 1 || bits > 8)
+        return ABQ_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(planes)) & 15) // 16-byte vector loads and stores
         return ABQ_ERR_INVALID_ARG;
     return ABQ_OK;
 }

@@ -6,8 +6,9 @@
 // only (x_bits * tokens * K / 8 bytes, allocated by layer code that a drop-in kernel library does not own), and
 // inside a layer's forward pass a cudaMalloc is not an option either: it synchronises the device, breaks
 // stream-ordered execution, and is forbidden outright while the stream is being captured into a CUDA graph.
-// For them this file keeps one fixed scratch array in device memory, reserved when the library is loaded on a
-// GPU and held until the process exits, and this entry point runs the ordinary GEMM on top of it.  Nothing here
+// For them this file keeps one fixed scratch array in device memory and this entry point runs the ordinary GEMM on
+// top of it.  The array belongs to the library's device code: a GPU holds it from the moment the CUDA runtime loads
+// that code on it (with lazy module loading that is the first call below on that GPU) until the process exits.  Nothing here
 // (nor anything it calls) calls cudaMalloc, cudaFree or an allocating library routine.
 #include <cuda_runtime.h>
 
@@ -46,6 +47,10 @@ static cudaError_t static_scratch_address(void **out)
 extern "C" abq_status abq_gemm_static_scratch(const abq_gemm_params *params, abq_stream_t stream)
 {
     if (!params)
+        return ABQ_ERR_INVALID_ARG;
+    // "Prepared" weights are an expansion that an earlier call left in the plan's own workspace.  On the shared array
+    // the last call may have been any other GEMM, so whatever sits there is not this problem's weights: refuse.
+    if (params->flags & ABQ_FLAG_WEIGHTS_PREPARED)
         return ABQ_ERR_INVALID_ARG;
     const size_t need = abq_gemm_workspace_bytes(params->M, params->N, params->K, params->x_bits, params->w_bits, params->route);
     if (need > (size_t)ABQ_STATIC_SCRATCH_BYTES)

@@ -12,12 +12,14 @@
  * (engine/common/pack.cu:46-64, engine/mma_any/aq_bmma_kernel.h:121-127); weights arrive already
  * packed, activations are packed (or quantised and packed) per call.
  *
- * All pointers are device pointers unless stated otherwise.  Nothing is allocated by the library;
- * scratch memory is a caller-owned workspace.  All launches are asynchronous on the stream given.
+ * All pointers are device pointers unless stated otherwise.  No entry point allocates memory: scratch is a
+ * caller-owned workspace (abq_gemm_static_scratch alone uses a fixed array that is part of the library's device
+ * code instead).  All launches are asynchronous on the stream given.
  * Every entry point returns an abq_status; 0 is success.  There is no CPU fallback: if no usable
  * GPU kernel exists for a request the call fails with ABQ_ERR_UNSUPPORTED.
  *
- * Each declaration cites the reference interface it replaces (path inside the reference repo).
+ * Each declaration cites the reference interface it replaces (path inside the reference repo), or says that the
+ * reference has no counterpart.
  */
 #ifndef ABQ_B200_H
 #define ABQ_B200_H
@@ -206,9 +208,11 @@ ABQ_API abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, i
 /*
  * abq_gemm for callers that cannot supply scratch memory.  No counterpart in the reference.
  *
- * Same contract as abq_gemm, except that params->workspace / workspace_bytes are ignored: the scratch the chosen
- * route needs is taken from one array of ABQ_STATIC_SCRATCH_BYTES bytes that lives in device memory of every GPU
- * the library is loaded on, from load until the process exits.  The call allocates nothing (no cudaMalloc, no
+ * Same contract as abq_gemm, except that params->workspace / workspace_bytes are ignored and that
+ * ABQ_FLAG_WEIGHTS_PREPARED is refused (ABQ_ERR_INVALID_ARG: prepared weights live in a workspace of their own, and
+ * the shared array holds whatever the last call left).  The scratch the chosen route needs is taken from one array
+ * of ABQ_STATIC_SCRATCH_BYTES bytes in the library's device code: a GPU holds it from the moment the CUDA runtime
+ * loads that code on it (with lazy loading: the first call on that GPU) until the process exits.  The call allocates nothing (no cudaMalloc, no
  * cudaFree, no allocating library routine), which is what a caller needs that runs inside a stream-ordered forward
  * pass with a workspace it does not size itself (the FasterTransformer linear layers give the GEMM wrapper only
  * x_bits * tokens * K / 8 bytes) and must not synchronise the device.

@@ -72,6 +72,33 @@ def test_validation_needs_no_device(abq):
     assert abq.lib().abq_pack_int32(None, None, 1, 128, 4, None) == 1
 
 
+def test_misaligned_pointers_are_argument_errors(abq):
+    """Operands and results move in 16-byte pieces; a pointer that is not 16-byte aligned (a tensor view at an element
+    offset) must come back as a status, not as a fault on the device.  Nothing is launched here."""
+    from abq_llm_b200 import binding as B
+    L = abq.lib()
+    p, st = B.GemmParams(), B.GemmState()
+    p.M, p.N, p.K, p.x_bits, p.w_bits = 1, 64, 128, 8, 2
+    for bad in ("X", "W", "D"):
+        p.X = p.W = p.D = 4096
+        setattr(p, bad, 4096 + 4)
+        assert L.abq_gemm_init(ctypes.byref(p), ctypes.byref(st)) == 1, bad
+    assert L.abq_pack_int32(4096 + 4, 8192, 1, 128, 4, None) == 1
+    assert L.abq_pack_int32(4096, 8192 + 8, 1, 128, 4, None) == 1
+    assert L.abq_pack_int4(4096 + 2, 8192, 1, 128, 4, None) == 1
+    assert L.abq_quantize_pack_half(4096 + 2, 4096, 8192, 1, 128, 8, 0, None) == 1
+    assert L.abq_unpack_int8(4096, 8192 + 1, 1, 128, 8, 1, None) == 1
+
+
+def test_static_scratch_refuses_prepared_weights_without_a_device(abq):
+    from abq_llm_b200 import binding as B
+    p = B.GemmParams()
+    p.M, p.N, p.K, p.x_bits, p.w_bits = 64, 64, 128, 4, 4
+    p.X = p.W = p.D = 4096
+    p.flags = abq.FLAG_WEIGHTS_PREPARED
+    assert abq.lib().abq_gemm_static_scratch(ctypes.byref(p), None) == 1
+
+
 def test_workspace_sizes(abq):
     assert abq.gemm_workspace_bytes(1, 4096, 4096, 8, 2) % 256 == 0
     big = abq.gemm_workspace_bytes(4096, 4096, 4096, 8, 8)

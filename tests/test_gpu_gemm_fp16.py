@@ -70,18 +70,21 @@ def test_per_group(abq, oracle, cuda, M, N, K, q, group, w_signed):
 
 
 @pytest.mark.parametrize("N,K", [(4096, 4096), (12288, 4096), (11008, 4096), (4096, 11008)])
-@pytest.mark.parametrize("q,M", [(2, 1), (3, 4), (4, 16), (2, 16)])
-def test_full_size_sweep_shapes(abq, oracle, cuda, N, K, q, M):
-    """The benchmark's own GEMMs at full size (LLaMA-7B shapes, g128 scale + zero point, int8 activations ~N(0, 30)):
-    fp16 result against the oracle's float64 dequantised product, and the int32 accumulation bit for bit."""
-    rng = np.random.default_rng(N + K + q + M)
-    x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+@pytest.mark.parametrize("q", [2, 3, 4])
+def test_full_size_sweep_shapes(abq, oracle, cuda, N, K, q):
+    """All 36 GEMMs the benchmark times, at full size (LLaMA-7B shapes, W{2,3,4}A8, M in {1, 4, 16}, g128 scale + zero point, int8
+    activations ~N(0, 30)): fp16 result against the oracle's float64 dequantised product, and the int32 accumulation bit for
+    bit.  One weight matrix per (shape, width), the three token counts on it."""
+    rng = np.random.default_rng(N + K + q)
     w = rand_codes(rng, N, K, q, False)
     ws = rng.uniform(0.001, 0.02, size=(N, K // 128)).astype(np.float16)
     wz = rng.integers(0, 1 << q, size=(N, K // 128)).astype(np.uint8)
-    xp, wp = planes_dev(oracle, x, 8), planes_dev(oracle, w, q)
-    got, _ = run_gemm(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_fp16=True, scale_mode=abq.SCALE_GROUP,
-                      group_size=128, w_scale=dev(ws), w_zero=dev(wz), flags=abq.FLAG_PDL)
-    check_close(got, oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), None, 128))
-    acc, _ = run_gemm(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False)
-    assert np.array_equal(acc, oracle.gemm_values_blas(x, w))
+    wp, dws, dwz = planes_dev(oracle, w, q), dev(ws), dev(wz)
+    for M in (1, 4, 16):
+        x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+        xp = planes_dev(oracle, x, 8)
+        got, _ = run_gemm(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_fp16=True, scale_mode=abq.SCALE_GROUP,
+                          group_size=128, w_scale=dws, w_zero=dwz, flags=abq.FLAG_PDL)
+        check_close(got, oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), None, 128))
+        acc, _ = run_gemm(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False)
+        assert np.array_equal(acc, oracle.gemm_values_blas(x, w)), f"M={M}"

@@ -35,6 +35,29 @@ def test_int32(abq, oracle, cuda, case):
     assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} of {got.size} differ"
 
 
+# one full-size prefill case (M = 512, LLaMA-7B shapes) for every width pair of the prefill sweep that has none above
+WIDTH_CASES = [(512, 4096, 4096, 3, 3, True), (512, 4096, 4096, 5, 5, True), (512, 11008, 4096, 6, 6, False), (512, 4096, 11008, 7, 7, True),
+               (512, 12288, 4096, 4, 2, False), (2048, 4096, 4096, 6, 2, True), (512, 4096, 4096, 2, 2, False), (512, 4096, 4096, 8, 8, True)]
+
+
+@pytest.mark.parametrize("case", WIDTH_CASES, ids=lambda c: "M{}N{}K{}a{}w{}{}".format(*c[:5], "s" if c[5] else "u"))
+def test_int32_full_size_per_width(abq, oracle, cuda, case):
+    """WxAx for x = 2..8 plus W2A4 and W2A6 at prefill sizes: int32 bit for bit against the oracle's exact product, on the route the
+    planner picks by itself, and the per-channel fp16 epilogue on the same operands."""
+    M, N, K, p, q, signed = case
+    rng = np.random.default_rng(sum(case[:5]))
+    x, w = rand_codes(rng, M, K, p, signed), rand_codes(rng, N, K, q, signed)
+    xp, wp = planes_dev(oracle, x, p), planes_dev(oracle, w, q)
+    got, st = run_gemm(abq, xp, wp, M, N, K, x_bits=p, w_bits=q, x_signed=signed, w_signed=signed)
+    assert st.route == abq.ROUTE_I8_UMMA
+    want = oracle.gemm_values_blas(x, w)
+    assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} of {got.size} differ"
+    scale = rng.uniform(0.001, 0.02, size=N).astype(np.float16)
+    got16, _ = run_gemm(abq, xp, wp, M, N, K, x_bits=p, w_bits=q, x_signed=signed, w_signed=signed, out_fp16=True,
+                        scale_mode=abq.SCALE_CHANNEL, w_scale=dev(scale))
+    check_close(got16, want.astype(np.float64) * scale.astype(np.float64)[None, :])
+
+
 def test_literal_reference_loop_on_sampled_rows(abq, oracle, cuda):
     """W4A4 128 x 4096 x 4096: the literal plane/bit loop on a sample of rows, the GPU result on all of them."""
     M, N, K, p, q = 128, 4096, 4096, 4, 4

@@ -57,3 +57,35 @@ def test_static_scratch_rejects_oversized_problem(abq, cuda):
     with pytest.raises(abq.AbqError) as err:
         abq.gemm_static_scratch(p)
     assert err.value.status == 3  # ABQ_ERR_WORKSPACE, before anything is launched
+
+
+def test_static_scratch_decode_split_k_twice_in_a_row(abq, oracle, cuda):
+    """16 tokens with K = 11008: the decode route splits K over CTAs and keeps its arrival counters and partial sums at
+    the head of the scratch -- here the shared array, which the previous test left full of other data.  Two calls in a
+    row with different operands must both match the entry point with a caller-owned workspace and the oracle."""
+    M, N, K, p, q = 16, 1024, 11008, 8, 4
+    rng = np.random.default_rng(23)
+    for call in range(2):
+        x, w = rand_codes(rng, M, K, p, True), rand_codes(rng, N, K, q, False)
+        xp, wp = planes_dev(oracle, x, p), planes_dev(oracle, w, q)
+        ref_out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+        new_out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+        ws = torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, p, q)), dtype=torch.uint8, device="cuda")
+        from abq_llm_b200 import binding as B
+        kw = dict(x_bits=p, w_bits=q, x_signed=True, w_signed=False, route=abq.ROUTE_I8_MMA)
+        abq.gemm(B.make_params(M, N, K, xp, wp, ref_out, workspace=ws, **kw))
+        abq.gemm_static_scratch(B.make_params(M, N, K, xp, wp, new_out, **kw))
+        torch.cuda.synchronize()
+        assert torch.equal(ref_out, new_out)
+        assert np.array_equal(new_out.cpu().numpy(), oracle.gemm_values_blas(x, w))
+
+
+def test_static_scratch_refuses_prepared_weights(abq, cuda):
+    """Prepared weights are a copy that lives in the caller's own workspace; on the shared array the "copy" would be
+    whatever the last call left there, so the flag is an argument error and nothing is launched."""
+    from abq_llm_b200 import binding as B
+    one = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    p = B.make_params(64, 64, 128, one, one, one, x_bits=4, w_bits=4, x_signed=False, w_signed=False, flags=abq.FLAG_WEIGHTS_PREPARED)
+    with pytest.raises(abq.AbqError) as err:
+        abq.gemm_static_scratch(p)
+    assert err.value.status == 1  # ABQ_ERR_INVALID_ARG

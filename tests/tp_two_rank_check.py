@@ -48,6 +48,23 @@ def main():
         assert int(be.status.item()) == 0
     ok = all(torch.equal(outs[("0", M)], outs[("1", M)]) for M in (1, 8, 32))
     print(f"rank {rank} PEER_EQUALS_NCCL {ok}", flush=True)
+
+    # ... and against the unsharded block computed by the CPU oracle (one rank, numpy stand-in for the GEMMs): what the
+    # two ranks produce together is the model's result, not merely the same thing twice.  Tolerance of the one-GPU test:
+    # chained GEMMs with fp16 intermediates, where one rounding difference moves a quantised code.
+    import numpy as np
+    from test_tp_linear_gloo import NumpyBackend
+    host_w = [(c.cpu().numpy(), s.cpu().numpy(), z.cpu().numpy()) for c, s, z in weights]
+    whole = tp.TensorParallelBlockLinears(NumpyBackend(0, None, x_scale=8.0), hidden, ffn, 0, 1, host_w, q, 0)
+    close = True
+    for M in (1, 8, 32):
+        gen.manual_seed(M)
+        x = torch.randn((M, hidden), device="cuda", generator=gen).half()
+        ref = whole.forward(x.cpu().numpy()).astype(np.float64)
+        got = outs[("0", M)].cpu().numpy().astype(np.float64)
+        err = np.abs(got - ref)
+        close = close and bool(np.all(err <= 2.0 ** -6 * np.abs(ref) + 2.0 ** -7 * np.abs(ref).max()))
+    print(f"rank {rank} MATCHES_UNSHARDED_ORACLE {close}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
