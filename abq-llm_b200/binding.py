@@ -37,6 +37,7 @@ class GemmParams(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("status_word", ctypes.c_void_p),
         ("x_quant_scale", ctypes.c_void_p),
+        ("w_prepared", ctypes.c_void_p),
     ]
 
 
@@ -72,6 +73,8 @@ def lib() -> ctypes.CDLL:
         L.abq_last_cuda_error.restype = ctypes.c_int
         L.abq_gemm_workspace_bytes.restype = ctypes.c_size_t
         L.abq_gemm_workspace_bytes.argtypes = [ctypes.c_int] * 6
+        L.abq_gemm_prepared_weight_bytes.restype = ctypes.c_size_t
+        L.abq_gemm_prepared_weight_bytes.argtypes = [ctypes.POINTER(GemmParams)]
         L.abq_gemm_init.argtypes = [ctypes.POINTER(GemmParams), ctypes.POINTER(GemmState)]
         L.abq_gemm_exec.argtypes = [ctypes.POINTER(GemmState), ctypes.c_void_p]
         L.abq_gemm_prepare_weights.argtypes = [ctypes.POINTER(GemmState), ctypes.c_void_p]
@@ -131,7 +134,7 @@ def gemm_workspace_bytes(M: int, N: int, K: int, x_bits: int, w_bits: int, route
 
 def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dtype=OUT_INT32, scale_mode=SCALE_NONE,
                 group_size=0, C=None, w_scale=None, w_zero=None, x_scale=None, route=ROUTE_AUTO, flags=0, workspace=None,
-                status_word=None, x_quant_scale=None) -> GemmParams:
+                status_word=None, x_quant_scale=None, w_prepared=None) -> GemmParams:
     p = GemmParams()
     p.M, p.N, p.K = M, N, K
     p.X, p.W, p.C, p.D = _ptr(X), _ptr(W), _ptr(C), _ptr(D)
@@ -144,7 +147,13 @@ def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dty
     p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     p.status_word = _ptr(status_word)
     p.x_quant_scale = _ptr(x_quant_scale)
+    p.w_prepared = _ptr(w_prepared)
     return p
+
+
+def gemm_prepared_weight_bytes(params: GemmParams) -> int:
+    """Bytes of the re-ordered weight copy a decode-shape plan reads through ``w_prepared`` (0: no prepared form)."""
+    return int(lib().abq_gemm_prepared_weight_bytes(ctypes.byref(params)))
 
 
 def gemm_init(params: GemmParams) -> GemmState:

@@ -57,6 +57,16 @@ abq_status decode_plan(abq_gemm_state *st, bool clear_counters);
 cudaError_t decode_clear_counters(const abq_gemm_state *st, cudaStream_t stream);
 cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream);
 size_t decode_workspace_bytes(int M, int N, int K);
+// split-K scratch shared by both decode kernels: [tile counters][partial slots for kDecodeMaxSlices slices]
+void decode_workspace_layout(int M, int N, size_t *off_partials, size_t *total);
+
+// ---- gemm_stream.cu (route ABQ_ROUTE_I8_MMA over prepared weights, ABQ_FLAG_WEIGHTS_PREPARED + w_prepared)
+bool stream_supported(const abq_gemm_params &p);
+size_t stream_prepared_bytes(const abq_gemm_params &p);
+abq_status stream_plan(abq_gemm_state *st, bool clear_counters);
+bool stream_planned(const abq_gemm_state *st);
+cudaError_t stream_prepare_weights(const abq_gemm_state *st, cudaStream_t stream);
+cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream);
 
 // ---- gemm_b1.cu (route ABQ_ROUTE_B1_MMA)
 abq_status b1_plan(abq_gemm_state *st);

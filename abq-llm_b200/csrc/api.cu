@@ -153,6 +153,13 @@ size_t abq_gemm_workspace_bytes(int M, int N, int K, int x_bits, int w_bits, int
     return (need + 255) & ~(size_t)255;
 }
 
+size_t abq_gemm_prepared_weight_bytes(const abq_gemm_params *params)
+{
+    if (!params || params->N <= 0 || params->K < 128 || params->K % 128 != 0)
+        return 0;
+    return stream_prepared_bytes(*params);
+}
+
 static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state, bool clear_counters)
 {
     if (!params || !state)
@@ -218,9 +225,12 @@ abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_stream_t st
 {
     if (!state || !state->init_success)
         return ABQ_ERR_NOT_INITIALIZED;
-    if (state->route != ABQ_ROUTE_I8_UMMA)
+    if (state->route == ABQ_ROUTE_I8_MMA && !stream_planned(state))
         return ABQ_OK;
-    cudaError_t e = umma_prepare_weights(state, reinterpret_cast<cudaStream_t>(stream));
+    if (state->route != ABQ_ROUTE_I8_UMMA && state->route != ABQ_ROUTE_I8_MMA)
+        return ABQ_OK;
+    cudaError_t e = state->route == ABQ_ROUTE_I8_MMA ? stream_prepare_weights(state, reinterpret_cast<cudaStream_t>(stream))
+                                                     : umma_prepare_weights(state, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
         set_last_cuda_error(e);
         return ABQ_ERR_CUDA;

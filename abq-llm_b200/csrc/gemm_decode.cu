@@ -18,7 +18,7 @@ static int device_sms()
 }
 
 // Workspace (only used when K is split over CTAs): [tile counters][partial slots for kDecodeMaxSlices slices]
-static void workspace_layout(int M, int N, size_t *off_partials, size_t *total)
+void decode_workspace_layout(int M, int N, size_t *off_partials, size_t *total)
 {
     const int tiles = (N + 15) / 16;
     const int rows = M < 16 ? M : 16; // taller problems run as launches of 16 rows, one after the other
@@ -30,7 +30,7 @@ size_t decode_workspace_bytes(int M, int N, int K)
 {
     (void)K;
     size_t a, total;
-    workspace_layout(M, N, &a, &total);
+    decode_workspace_layout(M, N, &a, &total);
     return total;
 }
 
@@ -106,13 +106,16 @@ static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
     L->stages_per_split = (sps + best_split - 1) / best_split;
     L->ring = ring;
     L->smem = fixed + (size_t)sps * 4 * rec + (size_t)NW * ring * stage_bytes;
-    workspace_layout(p.M, p.N, &L->off_partials, &L->bytes);
+    decode_workspace_layout(p.M, p.N, &L->off_partials, &L->bytes);
     return L->smem <= 227 * 1024;
 }
 
 abq_status decode_plan(abq_gemm_state *st, bool clear_counters)
 {
     const abq_gemm_params &p = st->p;
+    // weights already re-laid-out for this route: the stream kernel (widths and modes it does not take read the planes)
+    if ((p.flags & ABQ_FLAG_WEIGHTS_PREPARED) && p.w_prepared && stream_supported(p))
+        return stream_plan(st, clear_counters);
     if (p.scale_mode == ABQ_SCALE_GROUP && (p.group_size % 128 != 0))
         return ABQ_ERR_UNSUPPORTED;
     DecodeLayout L;
@@ -158,10 +161,12 @@ cudaError_t decode_clear_counters(const abq_gemm_state *st, cudaStream_t stream)
 
 cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
 {
+    if (stream_planned(st))
+        return stream_launch(st, stream);
     const abq_gemm_params &p = st->p;
     const int MT = (p.M < 16 ? p.M : 16) <= 8 ? 1 : 2; // as planned: by the rows of a full launch
     size_t off_partials, total;
-    workspace_layout(p.M, p.N, &off_partials, &total);
+    decode_workspace_layout(p.M, p.N, &off_partials, &total);
     uint8_t *ws = reinterpret_cast<uint8_t *>(p.workspace);
     const int tiles = (p.N + 15) / 16;
     DecodeArgs a;

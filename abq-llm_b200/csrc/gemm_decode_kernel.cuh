@@ -36,6 +36,7 @@
 #include "abq_common.cuh"
 #include "abq_kernels.h"
 #include "expand.cuh"
+#include "xbytes.cuh"
 
 namespace abq {
 
@@ -69,33 +70,6 @@ struct DecodeArgs {
     int w_signed;
     int *status;
 };
-
-// Bit-planes of 32 activation codes -> eight registers of true byte values (byte y of r[s] = code at bit 8y + s).
-template <int P>
-__device__ __forceinline__ void x_bytes(const uint32_t (&p)[P], bool is_signed, uint32_t (&r)[8])
-{
-    if constexpr (P >= 5 || P == 1) {
-        Expand<P>::run(p, r); // these widths come out of the butterfly as plain byte values
-    } else {
-        uint32_t n[4];
-        if constexpr (P == 2)
-            nibble_fields(p[0], p[1], 0u, 0u, false, n);
-        else if constexpr (P == 3)
-            nibble_fields(p[0], p[1], p[2], 0u, false, n);
-        else
-            nibble_fields(p[0], p[1], p[2], p[3], true, n);
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-            r[s] = n[s] & 0x0f0f0f0fu;
-            r[4 + s] = (n[s] >> 4) & 0x0f0f0f0fu;
-        }
-    }
-    if (is_signed && P < 8) {
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-            r[s] = sign_extend_bytes(r[s], P);
-    }
-}
 
 // Expand the activation planes of groups [g_first, g_first + n_groups) into records in shared memory.  Record of a
 // 128-feature group: [token tile mt][step pair ip][lane = 4 g + t][16 bytes] B fragments, then 16 int32 code sums.

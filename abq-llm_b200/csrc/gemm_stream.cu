@@ -1,0 +1,231 @@
+// Decode route over prepared weights (stream layout, gemm_stream_kernel.cuh): planner, load-time re-layout and launch
+// entry.  The kernel is instantiated per weight width in gemm_stream_w2.cu .. gemm_stream_w8.cu.
+#include "gemm_stream_kernel.cuh"
+
+namespace abq {
+
+namespace {
+
+// What abq_gemm_init decided for this route, kept in the state's route-specific words (tmap[1]).
+struct StreamPlan {
+    int magic;
+    int nw, cu, ring, slices, units_per_slice, ctas_per_slice, MT, MP, grouped, unit_bytes, max_tiles_per_cta;
+};
+constexpr int kStreamMagic = 0x5354524d;
+
+int device_sms()
+{
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+        return v;
+    return 148;
+}
+
+bool width_supported(int q) { return q == 2 || q == 3 || q == 4 || q == 8; }
+
+int unit_bytes_of(const abq_gemm_params &p) { return p.w_bits * 256 + (p.scale_mode == ABQ_SCALE_GROUP ? 64 : 0); }
+
+} // namespace
+
+bool stream_supported(const abq_gemm_params &p)
+{
+    if (!width_supported(p.w_bits))
+        return false;
+    if (!p.x_signed && p.x_bits == 8)
+        return false; // unsigned 8-bit activations need the u8 x u8 MMA: the plane kernel has it
+    if (p.scale_mode == ABQ_SCALE_GROUP && p.group_size % 128 != 0)
+        return false;
+    return true;
+}
+
+size_t stream_prepared_bytes(const abq_gemm_params &p)
+{
+    if (!stream_supported(p))
+        return 0;
+    return (size_t)((p.N + 15) / 16) * (p.K / 128) * unit_bytes_of(p);
+}
+
+// Launch shape.  Preference: a CTA small enough for two to share an SM (so that the next GEMM's CTAs move in and fetch
+// their first weights while this one computes), K split over CTAs only when the activation records of the whole K
+// range do not fit, chunks of about 4 KB, as deep a ring as the shared memory left over allows.
+static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_bytes)
+{
+    const int rows = p.M < 16 ? p.M : 16;
+    const bool grouped = p.scale_mode == ABQ_SCALE_GROUP;
+    P->magic = kStreamMagic;
+    P->grouped = grouped;
+    P->MT = rows > 8 ? 2 : 1;
+    P->MP = P->MT == 2 || !grouped ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
+    const int GS = grouped && P->MT == 1 ? 8 / P->MP : 1;
+    const int MR = P->MT == 2 ? 16 : P->MP;
+    P->unit_bytes = unit_bytes_of(p);
+    const int units = p.K / 128;
+    const int tiles = (p.N + 15) / 16;
+    const int sms = device_sms();
+    const int force_full = env_int("ABQ_STREAM_FULL", 0);
+    const int force_slices = env_int("ABQ_STREAM_SLICES", 0);
+    for (int mode = force_full ? 1 : 0; mode < 2; ++mode) { // 0: two CTAs per SM, 1: one
+        const size_t budget = mode == 0 ? 112 * 1024 : 226 * 1024;
+        const int nw = env_int("ABQ_STREAM_WARPS", mode == 0 ? 8 : 16);
+        if (nw < 1 || nw > kStreamMaxWarps)
+            return false;
+        int cu = env_int("ABQ_STREAM_CU", 0);
+        if (cu <= 0) {
+            cu = (4608 / P->unit_bytes) / GS * GS;
+            cu = cu < GS ? GS : cu;
+            cu = cu > 8 ? 8 : cu;
+        }
+        if (cu % GS != 0)
+            return false;
+        for (int sl = force_slices > 0 ? force_slices : 1; sl <= kDecodeMaxSlices; ++sl) {
+            int ups = (units + sl - 1) / sl;
+            ups = (ups + cu - 1) / cu * cu;
+            const int slices = (units + ups - 1) / ups; // drop slices that would be empty
+            int cps = env_int("ABQ_STREAM_CTAS", sms) / slices;
+            cps = cps > tiles ? tiles : cps;
+            cps = cps < 1 ? 1 : cps;
+            const int max_T = (tiles + cps - 1) / cps;
+            const StreamSmem L0 = stream_smem_layout(nw, 0, cu, P->unit_bytes, ups, MR, max_T, P->MT);
+            if (L0.total < budget) {
+                int ring = (int)((budget - L0.total) / ((size_t)nw * cu * P->unit_bytes));
+                ring = ring > kStreamMaxRing ? kStreamMaxRing : ring;
+                const int forced = env_int("ABQ_STREAM_RING", 0);
+                if (forced > 0 && forced <= ring)
+                    ring = forced;
+                if (ring >= 2) {
+                    P->nw = nw;
+                    P->cu = cu;
+                    P->ring = ring;
+                    P->slices = slices;
+                    P->units_per_slice = ups;
+                    P->ctas_per_slice = cps;
+                    P->max_tiles_per_cta = max_T;
+                    *smem_bytes = stream_smem_layout(nw, ring, cu, P->unit_bytes, ups, MR, max_T, P->MT).total;
+                    return true;
+                }
+            }
+            if (force_slices > 0)
+                break;
+        }
+    }
+    return false;
+}
+
+abq_status stream_plan(abq_gemm_state *st, bool clear_counters)
+{
+    const abq_gemm_params &p = st->p;
+    if (!stream_supported(p) || !p.w_prepared)
+        return ABQ_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(p.w_prepared) & 15)
+        return ABQ_ERR_INVALID_ARG;
+    StreamPlan P;
+    size_t smem = 0;
+    if (!make_plan(p, &P, &smem))
+        return ABQ_ERR_UNSUPPORTED;
+    if (P.slices > 1) {
+        if (!p.workspace || p.workspace_bytes < decode_workspace_bytes(p.M, p.N, p.K))
+            return ABQ_ERR_WORKSPACE;
+        if (clear_counters) { // as the plane kernel: cleared once here, every launch leaves them zero
+            if (cudaMemsetAsync(p.workspace, 0, (size_t)((p.N + 15) / 16) * 4, cudaStreamPerThread) != cudaSuccess ||
+                cudaStreamSynchronize(cudaStreamPerThread) != cudaSuccess)
+                return ABQ_ERR_CUDA;
+        }
+    }
+    static_assert(sizeof(StreamPlan) <= sizeof(st->tmap[1]), "plan words");
+    std::memcpy(st->tmap[1], &P, sizeof(P));
+    st->grid[0] = P.slices * P.ctas_per_slice;
+    st->grid[1] = st->grid[2] = 1;
+    st->block[0] = P.nw * 32;
+    st->block[1] = st->block[2] = 1;
+    st->cluster = P.slices;
+    st->shared_mem_size = smem;
+    st->tile[0] = P.units_per_slice;
+    st->tile[1] = P.ring;
+    st->tile[2] = P.ctas_per_slice;
+    st->tile[3] = P.cu;
+    return ABQ_OK;
+}
+
+bool stream_planned(const abq_gemm_state *st)
+{
+    StreamPlan P;
+    std::memcpy(&P, st->tmap[1], sizeof(P));
+    return st->route == ABQ_ROUTE_I8_MMA && P.magic == kStreamMagic;
+}
+
+cudaError_t stream_prepare_weights(const abq_gemm_state *st, cudaStream_t stream)
+{
+    const abq_gemm_params &p = st->p;
+    const int grouped = p.scale_mode == ABQ_SCALE_GROUP;
+    const int gps = grouped ? p.group_size / 128 : 1, sg = grouped ? p.K / p.group_size : 1;
+    const uint32_t *planes = reinterpret_cast<const uint32_t *>(p.W);
+    const __half *ws = reinterpret_cast<const __half *>(p.w_scale);
+    uint8_t *out = reinterpret_cast<uint8_t *>(p.w_prepared);
+    switch (p.w_bits) {
+    case 2: return stream_prepare_w2(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
+    case 3: return stream_prepare_w3(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
+    case 4: return stream_prepare_w4(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
+    case 8: return stream_prepare_w8(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
+{
+    const abq_gemm_params &p = st->p;
+    StreamPlan P;
+    std::memcpy(&P, st->tmap[1], sizeof(P));
+    StreamArgs a;
+    a.N = p.N;
+    a.K = p.K;
+    a.tiles = (p.N + 15) / 16;
+    a.units = p.K / 128;
+    a.unit_bytes = P.unit_bytes;
+    a.slices = P.slices;
+    a.units_per_slice = P.units_per_slice;
+    a.ctas_per_slice = P.ctas_per_slice;
+    a.cu = P.cu;
+    a.ring = P.ring;
+    a.nw = P.nw;
+    a.Wp = reinterpret_cast<const uint8_t *>(p.w_prepared);
+    a.x_plane_words = (size_t)p.M * (p.K / 32);
+    a.x_qscale = (p.flags & ABQ_FLAG_X_HALF) ? p.x_quant_scale : nullptr;
+    a.x_bits = p.x_bits;
+    a.x_signed = p.x_signed;
+    a.counters = nullptr;
+    a.partials = nullptr;
+    if (P.slices > 1) {
+        size_t off_partials, total;
+        decode_workspace_layout(p.M, p.N, &off_partials, &total);
+        a.counters = reinterpret_cast<int *>(p.workspace);
+        a.partials = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(p.workspace) + off_partials);
+    }
+    a.w_scale = reinterpret_cast<const __half *>(p.w_scale);
+    a.w_zero = p.w_zero;
+    a.C = reinterpret_cast<const __half *>(p.C);
+    a.out_dtype = p.out_dtype;
+    a.scale_mode = p.scale_mode;
+    a.w_signed = p.w_signed;
+    a.status = p.status_word;
+    const size_t out_row_bytes = (size_t)p.N * (p.out_dtype == ABQ_OUT_INT32 ? 4 : 2);
+    for (int m0 = 0; m0 < p.M; m0 += 16) { // taller problems: 16 rows per launch, in stream order (they share the workspace)
+        a.M = p.M - m0 < 16 ? p.M - m0 : 16;
+        a.X = (p.flags & ABQ_FLAG_X_HALF) ? reinterpret_cast<const uint32_t *>(reinterpret_cast<const __half *>(p.X) + (size_t)m0 * p.K)
+                                          : reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
+        a.D = reinterpret_cast<uint8_t *>(p.D) + (size_t)m0 * out_row_bytes;
+        a.x_scale = p.x_scale ? p.x_scale + m0 : nullptr;
+        cudaError_t e;
+        switch (p.w_bits) {
+        case 2: e = stream_launch_w2(st, a, P.MT, P.MP, P.grouped != 0, stream); break;
+        case 3: e = stream_launch_w3(st, a, P.MT, P.MP, P.grouped != 0, stream); break;
+        case 4: e = stream_launch_w4(st, a, P.MT, P.MP, P.grouped != 0, stream); break;
+        case 8: e = stream_launch_w8(st, a, P.MT, P.MP, P.grouped != 0, stream); break;
+        default: e = cudaErrorInvalidValue;
+        }
+        if (e != cudaSuccess)
+            return e;
+    }
+    return cudaSuccess;
+}
+
+} // namespace abq

@@ -1,0 +1,797 @@
+// Decode-shape GEMM (up to 16 rows per launch) over weights in the library's own "stream" layout: the same bits as the
+// reference's bit-planes (engine/common/pack.cu:46-64), re-ordered once at load time (prepare_stream_kernel below) so
+// that the kernel that runs every step spends its instructions on arithmetic instead of on un-shuffling planes.
+//
+// Layout.  The weight matrix is cut into units of 16 output rows x 128 input features; a unit is Q * 256 bytes of codes
+// followed (when scales come per group) by 64 bytes of parameters, and the units of a 16-row tile follow one another
+// along K, tile after tile.  Inside a unit, lane l = 4 g + t of a warp owns rows g and g + 8 and the features
+// 32 t .. 32 t + 31; its codes sit where the lane reads them with 16-byte loads and are packed so that one AND (for
+// some fields of the 3-bit format a shift, AND, OR) per register yields the A fragments of mma.sync.m16n8k32 as byte
+// values times a power of two; fragments with different powers go to different accumulator sets, merged exactly when
+// the sets are folded.  The 64 parameter bytes are, per row, the fp32 bits of the group's fp16 scale with the zero
+// point (plus the offset of two's-complement codes) in the low mantissa bits, which an fp16 value leaves zero.
+//
+// Kernel.  A CTA owns a contiguous range of tiles, i.e. one contiguous byte range of the stream; its warps deal the
+// range among themselves in chunks of a few units and every warp pulls its chunks through a private ring with plain bulk
+// copies (cp.async.bulk, no tensor map), refilling a slot as soon as it is consumed.  Weight requests go out before the
+// wait on the previous kernel (programmatic dependent launch), and the kernel is shaped so that two CTAs fit on an SM:
+// while one GEMM computes, the next one's CTAs are already resident with their first chunks in shared memory.
+// The activations are expanded once per CTA into byte "records" (the B fragments) plus per-unit code sums.
+// With few tokens the eight columns of the MMA would mostly multiply padding; instead column c holds token c % MP of
+// unit (c / MP) of a block of GS = 8 / MP consecutive units (their B fragments are zero elsewhere), so the fold of the
+// integer accumulators into fp32 -- the expensive part of group-wise scales -- happens once per GS units.
+// Partial sums of the warps that share a tile meet in shared memory after one barrier and are added in warp order.
+//
+// Covers, for prepared weights, what the reference does with plane-stacked 1-bit MMAs and a shared-memory
+// shift-accumulate epilogue (engine/mma_any/aq_bmma_kernel.h:109-271, 485-580; fp16 scalar epilogue of the
+// FasterTransformer copy, fastertransformer/.../abqgemm/mma_any/aq_bmma_kernel.h:474-524).
+#pragma once
+#include <cuda.h>
+#include <cstring>
+
+#include "abq_common.cuh"
+#include "abq_kernels.h"
+#include "xbytes.cuh"
+
+namespace abq {
+
+constexpr int kStreamMaxWarps = 16;
+constexpr int kStreamMaxRing = 8;
+constexpr uint32_t kZeroMask = 0x1fffu; // low mantissa bits of the packed (scale, zero) word that hold the zero point
+
+struct StreamArgs {
+    int M, N, K;
+    int tiles;           // ceil(N / 16)
+    int units;           // K / 128: units per tile in the stream
+    int unit_bytes;      // Q * 256 (+ 64 with group parameters)
+    int slices;          // K split over CTAs (1 unless the records of all K do not fit in shared memory)
+    int units_per_slice; // multiple of cu
+    int ctas_per_slice;
+    int cu;              // units per chunk (multiple of GS)
+    int ring;            // chunks per warp ring
+    int nw;              // warps per CTA
+    const uint8_t *Wp;   // weights in stream layout
+    const uint32_t *X;   // activation planes [x_bits][rows][K/32], first row of this launch (fp16 [rows][K] with x_qscale)
+    size_t x_plane_words;
+    const float *x_qscale;
+    int x_bits, x_signed;
+    int *counters;  // slices > 1: one arrival counter per tile, zero before the launch, left zero after it
+    int *partials;  // slices > 1: [slice][tile][token][16 rows]
+    void *D;
+    const __half *w_scale; // per-channel mode only (group parameters travel in the stream)
+    const uint8_t *w_zero;
+    const float *x_scale;
+    const __half *C;
+    int out_dtype, scale_mode, w_signed;
+    int *status;
+};
+
+// ------------------------------------------------------------------------------------------ formats
+// StreamFormat<Q>: how the codes of one lane (rows g and g + 8, 32 features each) are packed, and how they come back.
+//   code(j, a, y): byte y of A register a (a0: row g low half, a1: row g + 8 low half, a2: row g high half, a3: row g + 8
+//   high half) of MMA step j of the unit = the row's code at feature 32 t + 31 - 8 y - (2 j + (a >> 1)).
+//   pack():   the codes of a lane as bytes c[row 0/1][s = 2 j + h] (byte y in bits 8y..8y+7) -> its kWords words
+//   expand(): shared memory -> R[j][a] = code bytes * 2^(kShift * set_of(j))
+template <int Q>
+struct StreamFormat;
+
+template <>
+struct StreamFormat<2> {
+    static constexpr int kWords = 4, kSets = 2, kShift = 2;
+    __host__ __device__ static constexpr int set_of(int j) { return j & 1; }
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            w[a] = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                w[a] |= c[a & 1][2 * j + (a >> 1)] << (2 * j);
+        }
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[4][4])
+    {
+        const uint4 v = *reinterpret_cast<const uint4 *>(unit + lane * 16);
+        const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const uint32_t hi = w[a] >> 4;
+            R[0][a] = w[a] & 0x03030303u;
+            R[1][a] = w[a] & 0x0c0c0c0cu;
+            R[2][a] = hi & 0x03030303u;
+            R[3][a] = hi & 0x0c0c0c0cu;
+        }
+    }
+};
+
+template <>
+struct StreamFormat<4> {
+    static constexpr int kWords = 8, kSets = 2, kShift = 4;
+    __host__ __device__ static constexpr int set_of(int j) { return j & 1; }
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+                w[jj * 4 + a] = c[a & 1][4 * jj + (a >> 1)] | (c[a & 1][4 * jj + 2 + (a >> 1)] << 4);
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[4][4])
+    {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(unit + jj * 512 + lane * 16);
+            const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                R[2 * jj][a] = w[a] & 0x0f0f0f0fu;
+                R[2 * jj + 1][a] = w[a] & 0xf0f0f0f0u;
+            }
+        }
+    }
+};
+
+// Three bits: eight codes of a byte lane in three bytes.  Slot s' of a row holds the code of step/half (j, h) with
+// slot_of(j, h) below; slots 0, 3, 6, 2 come out times 1, slots 1, 4, 7, 5 times 8.
+//   A = c0 | c1 << 3 | (c2 & 3) << 6;  B = c3 | c4 << 3 | (c5 & 3) << 6;  C = c6 | c7 << 3 | (c2 >> 2) << 6 | (c5 >> 2) << 7
+template <>
+struct StreamFormat<3> {
+    static constexpr int kWords = 6, kSets = 2, kShift = 3;
+    __host__ __device__ static constexpr int set_of(int j) { return j >> 1; }
+    __host__ __device__ static constexpr int slot_of(int j, int h)
+    {
+        return j == 0 ? (h ? 3 : 0) : j == 1 ? (h ? 2 : 6) : j == 2 ? (h ? 4 : 1) : (h ? 5 : 7);
+    }
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            uint32_t s[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    s[slot_of(j, h)] = c[r][2 * j + h];
+            const uint32_t A = s[0] | (s[1] << 3) | ((s[2] & 0x03030303u) << 6);
+            const uint32_t B = s[3] | (s[4] << 3) | ((s[5] & 0x03030303u) << 6);
+            const uint32_t C = s[6] | (s[7] << 3) | (((s[2] >> 2) & 0x01010101u) << 6) | (((s[5] >> 2) & 0x01010101u) << 7);
+            // words 0..3 are the lane's 16-byte piece, words 4, 5 its 8-byte piece
+            if (r == 0) {
+                w[0] = A;
+                w[1] = B;
+                w[2] = C;
+            } else {
+                w[3] = A;
+                w[4] = B;
+                w[5] = C;
+            }
+        }
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[4][4])
+    {
+        const uint4 v = *reinterpret_cast<const uint4 *>(unit + lane * 16);
+        const uint2 u = *reinterpret_cast<const uint2 *>(unit + 512 + lane * 8);
+        const uint32_t abc[2][3] = { { v.x, v.y, v.z }, { v.w, u.x, u.y } };
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t A = abc[r][0], B = abc[r][1], C = abc[r][2];
+            uint32_t s[8];
+            s[0] = A & 0x07070707u;
+            s[1] = A & 0x38383838u;
+            s[3] = B & 0x07070707u;
+            s[4] = B & 0x38383838u;
+            s[6] = C & 0x07070707u;
+            s[7] = C & 0x38383838u;
+            s[2] = ((A >> 6) & 0x03030303u) | ((C >> 4) & 0x04040404u);
+            s[5] = ((B >> 3) & 0x18181818u) | ((C >> 2) & 0x20202020u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                R[j][r] = s[slot_of(j, 0)];     // a0 (r = 0) / a1 (r = 1): low half
+                R[j][2 + r] = s[slot_of(j, 1)]; // a2 / a3: high half
+            }
+        }
+    }
+};
+
+template <>
+struct StreamFormat<8> {
+    static constexpr int kWords = 16, kSets = 1, kShift = 0;
+    __host__ __device__ static constexpr int set_of(int) { return 0; }
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+                w[j * 4 + a] = c[a & 1][2 * j + (a >> 1)];
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[4][4])
+    {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(unit + j * 512 + lane * 16);
+            R[j][0] = v.x;
+            R[j][1] = v.y;
+            R[j][2] = v.z;
+            R[j][3] = v.w;
+        }
+    }
+};
+
+// True when no earlier MMA step of a unit feeds the accumulator set of step j.
+template <typename F>
+__host__ __device__ constexpr bool stream_first_in_set(int j)
+{
+    for (int i = 0; i < j; ++i)
+        if (F::set_of(i) == F::set_of(j))
+            return false;
+    return true;
+}
+
+// Where lane `lane` finds word i of its kWords words inside a unit's code block (16-byte pieces first, lane-major).
+template <int Q>
+__host__ __device__ constexpr int stream_word_offset(int lane, int i)
+{
+    constexpr int kWords = StreamFormat<Q>::kWords;
+    constexpr int full = kWords / 4; // 16-byte pieces per lane
+    return i < full * 4 ? (i / 4) * 512 + lane * 16 + (i % 4) * 4 : full * 512 + lane * ((kWords % 4) * 4) + (i - full * 4) * 4;
+}
+
+// ------------------------------------------------------------------------------------------ load-time re-layout
+// planes [Q][N][K/32] (+ per-group fp16 scale / u8 zero point) -> stream layout.  One thread per (tile, unit, lane).
+template <int Q>
+__global__ void __launch_bounds__(256) prepare_stream_kernel(const uint32_t *__restrict__ planes, const __half *__restrict__ w_scale,
+                                                             const uint8_t *__restrict__ w_zero, uint8_t *__restrict__ out, int N, int K, int w_signed,
+                                                             int grouped, int groups_per_scale, int scale_groups)
+{
+    using F = StreamFormat<Q>;
+    const int units = K >> 7, KW = K >> 5;
+    const int tiles = (N + 15) >> 4;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)tiles * units * 32)
+        return;
+    const int lane = (int)(idx & 31);
+    const int u = (int)((idx >> 5) % units), r = (int)((idx >> 5) / units);
+    const int g = lane >> 2, t = lane & 3;
+    const int unit_bytes = Q * 256 + (grouped ? 64 : 0);
+    uint8_t *unit = out + ((size_t)r * units + u) * unit_bytes;
+    uint32_t c[2][8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = r * 16 + g + 8 * h;
+        uint32_t p[Q];
+#pragma unroll
+        for (int b = 0; b < Q; ++b)
+            p[b] = row < N ? planes[((size_t)b * N + row) * KW + u * 4 + t] : 0u;
+        planes_to_bytes<Q>(p, w_signed != 0 && row < N, c[h]); // two's complement -> offset codes: top plane flipped
+    }
+    uint32_t w[F::kWords];
+    F::pack(c, w);
+#pragma unroll
+    for (int i = 0; i < F::kWords; ++i)
+        *reinterpret_cast<uint32_t *>(unit + stream_word_offset<Q>(lane, i)) = w[i];
+    if (grouped && t == 0) {
+        const int zoff = w_signed ? (1 << (Q - 1)) : 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = r * 16 + g + 8 * h;
+            uint32_t pk = 0;
+            if (row < N) {
+                const size_t si = (size_t)row * scale_groups + u / groups_per_scale;
+                pk = __float_as_uint(__half2float(w_scale[si])) | (uint32_t)(zoff + (w_zero ? (int)w_zero[si] : 0));
+            }
+            *reinterpret_cast<uint32_t *>(unit + Q * 256 + (2 * g + h) * 4) = pk;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ activation records
+// Records of units [u_first, u_first + n_units) of this CTA's K range, zero-padded to n_pad units and MR token rows:
+// rec[(ul * MR + m) * 128 + t * 32 + {0, 16} ^ ((m & 1) << 4)] = the lane-t halves (registers 0..3 and 4..7 of x_bytes)
+// of token m, and sums[ul * MR + m] = the sum of its 128 codes.
+template <int P>
+__device__ __forceinline__ void stream_record_item(const StreamArgs &a, int m, int kw, uint32_t (&r)[8])
+{
+    uint32_t p[P];
+    const uint32_t *src = a.X + (size_t)m * (a.K >> 5) + kw;
+#pragma unroll
+    for (int b = 0; b < P; ++b)
+        p[b] = __ldg(src + b * a.x_plane_words);
+    x_bytes<P>(p, a.x_signed != 0, r);
+}
+
+__device__ __forceinline__ void stream_build_records(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR)
+{
+    const int words = n_pad * 4;
+    const int items = MR * words;
+    const __half hscale = a.x_qscale ? __float2half(__ldg(a.x_qscale)) : __half();
+    for (int base = 0; base < items; base += blockDim.x) { // every lane of a warp takes every trip: the shuffles below need all of them
+        const int idx = min(base + (int)threadIdx.x, items - 1);
+        const bool mine = base + (int)threadIdx.x < items;
+        const int m = idx / words, kwl = idx - m * words;
+        const int ul = kwl >> 2, t = kwl & 3;
+        uint32_t r[8];
+        int sum = 0;
+        if (mine && m < a.M && ul < n_units) {
+            const int kw = u_first * 4 + kwl;
+            if (a.x_qscale) {
+                x_bytes_from_half(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.X) + (size_t)m * a.K + (size_t)kw * 32), hscale,
+                                  a.x_bits, r);
+            } else {
+                switch (a.x_bits) {
+                case 1: stream_record_item<1>(a, m, kw, r); break;
+                case 2: stream_record_item<2>(a, m, kw, r); break;
+                case 3: stream_record_item<3>(a, m, kw, r); break;
+                case 4: stream_record_item<4>(a, m, kw, r); break;
+                case 5: stream_record_item<5>(a, m, kw, r); break;
+                case 6: stream_record_item<6>(a, m, kw, r); break;
+                case 7: stream_record_item<7>(a, m, kw, r); break;
+                default: stream_record_item<8>(a, m, kw, r); break;
+                }
+            }
+            if (a.x_signed) {
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    sum = __dp4a((int)r[s], 0x01010101, sum);
+            } else {
+                unsigned usum = 0;
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    usum = __dp4a(r[s], 0x01010101u, usum);
+                sum = (int)usum;
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                r[s] = 0;
+        }
+        // the four 32-feature runs of a unit sit in four consecutive lanes (words is a multiple of 4)
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (!mine)
+            continue;
+        uint8_t *dst = rec_base + ((size_t)ul * MR + m) * 128 + t * 32;
+        const int swz = (m & 1) << 4;
+        *reinterpret_cast<uint4 *>(dst + swz) = make_uint4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<uint4 *>(dst + (16 ^ swz)) = make_uint4(r[4], r[5], r[6], r[7]);
+        if (t == 0)
+            sums[ul * MR + m] = sum;
+    }
+}
+
+// D(16x8, s32) = A(16x32, u8) * B(32x8, s8) + 0: first step of an accumulation (saves clearing the accumulators)
+__device__ __forceinline__ void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    const int z = 0;
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(z));
+}
+
+// Shared-memory carve-up, the same arithmetic on the host (planner) and in the kernel.
+struct StreamSmem {
+    size_t ring, rec, sums, zero, red, bars, total;
+};
+__host__ __device__ inline StreamSmem stream_smem_layout(int nw, int ring, int cu, int unit_bytes, int units_pad, int MR, int tiles_per_cta, int MT)
+{
+    StreamSmem L;
+    size_t at = 0;
+    L.ring = at;
+    at += (size_t)nw * ring * cu * unit_bytes;
+    L.rec = at;
+    at += (size_t)units_pad * MR * 128;
+    L.sums = at;
+    at += ((size_t)units_pad * MR * 4 + 15) & ~(size_t)15;
+    L.zero = at;
+    at += 32;
+    L.red = at;
+    at += (size_t)(nw + tiles_per_cta) * MT * 512; // [pair][token tile][16 rows][8 columns] 32-bit
+    L.bars = at;
+    at += (size_t)nw * kStreamMaxRing * 8;
+    L.total = at + 128; // slack for aligning the base to 128 bytes
+    return L;
+}
+
+// Q: weight bits.  MT: token tiles of 8 (2 for 9..16 tokens).  MP: token rows per column block (1, 2, 4, 8).
+// GS = 8 / MP units share one set of accumulators (GROUPED only).  GROUPED: per-group scale / zero point in the stream.
+template <int Q, int MT, int MP, bool GROUPED>
+__global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const StreamArgs a)
+{
+    using F = StreamFormat<Q>;
+    constexpr int GS = GROUPED ? 8 / MP : 1;
+    constexpr int MR = MT == 2 ? 16 : MP; // token rows of a record
+    static_assert(MT == 1 || MP == 8, "two token tiles only with full column blocks");
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int nw = a.nw;
+    const int s = blockIdx.x / a.ctas_per_slice;
+    const int cb = blockIdx.x - s * a.ctas_per_slice;
+    const int r_begin = (int)((long long)cb * a.tiles / a.ctas_per_slice);
+    const int r_end = (int)((long long)(cb + 1) * a.tiles / a.ctas_per_slice);
+    const int T = r_end - r_begin;
+    const int max_T = (a.tiles + a.ctas_per_slice - 1) / a.ctas_per_slice;
+    const int u0 = s * a.units_per_slice;                        // first unit of this CTA's K range
+    const int n_units = max(0, min(a.units - u0, a.units_per_slice)); // its unit count
+    const int units_pad = a.units_per_slice;                     // records are padded to whole chunks
+    const int cpt = (n_units + a.cu - 1) / a.cu;                 // chunks per tile
+    const int total_chunks = T * cpt;
+    const int chunk_bytes = a.cu * a.unit_bytes;
+
+    const StreamSmem L = stream_smem_layout(nw, a.ring, a.cu, a.unit_bytes, units_pad, MR, max_T, MT);
+    uint8_t *ring_base = smem + L.ring;
+    uint8_t *rec_base = smem + L.rec;
+    int *sums = reinterpret_cast<int *>(smem + L.sums);
+    const uint8_t *zero_base = smem + L.zero;
+    int *red = reinterpret_cast<int *>(smem + L.red);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars) + warp * kStreamMaxRing;
+
+    if (lane == 0) {
+        for (int i = 0; i < a.ring; ++i)
+            mbar_init(&full[i], 1);
+        fence_mbar_init();
+    }
+    if (threadIdx.x < 8)
+        reinterpret_cast<uint32_t *>(smem + L.zero)[threadIdx.x] = 0;
+    __syncwarp();
+    pdl_launch_dependents();
+
+    // ---- this warp's chunks: [c_begin, c_end) of the CTA's T * cpt chunks (tile-major)
+    const int c_begin = (int)((long long)warp * total_chunks / nw);
+    const int c_end = (int)((long long)(warp + 1) * total_chunks / nw);
+    uint8_t *my_ring = ring_base + (size_t)warp * a.ring * chunk_bytes;
+
+    // request side (lane 0): cursor over the chunks in consumption order
+    int q_tile = 0, q_cit = 0, q_left = 0;
+    if (cpt > 0) {
+        q_tile = c_begin / cpt;
+        q_cit = c_begin - q_tile * cpt;
+        q_left = c_end - c_begin;
+    }
+    auto issue = [&](int slot) {
+        const int uf = q_cit * a.cu;
+        const int nu = min(a.cu, n_units - uf);
+        const uint32_t bytes = (uint32_t)nu * a.unit_bytes;
+        const uint8_t *src = a.Wp + ((size_t)(r_begin + q_tile) * a.units + u0 + uf) * a.unit_bytes;
+        mbar_arrive_expect_tx(&full[slot], bytes);
+        bulk_load(my_ring + (size_t)slot * chunk_bytes, src, bytes, &full[slot]);
+        --q_left;
+        if (++q_cit == cpt) {
+            q_cit = 0;
+            ++q_tile;
+        }
+    };
+    if (lane == 0) {
+        for (int slot = 0; slot < a.ring && q_left > 0; ++slot)
+            issue(slot); // weights never depend on an earlier kernel: request them before the dependency wait
+    }
+
+    // ---- activations: everything below may depend on the kernel launched just before
+    pdl_wait_prior_grid();
+    stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR);
+    __syncthreads();
+
+    // lane constants of the B fragment fetch: column c = g holds token (g % MP) of unit (g / MP) of a block
+    const int my_m = g & (MP - 1);
+    const int my_slot = GS > 1 ? g / MP : 0;
+    const int rec_lane = my_m * 128 + t * 32;
+    const int swz = (my_m & 1) << 4;
+    const int zoff = a.w_signed ? (1 << (Q - 1)) : 0;
+
+    bool ok = true;
+    int slot = 0;
+    uint32_t phase = 0;
+    int tile_l = cpt > 0 ? c_begin / cpt : 0; // tile (local) and chunk within it of the chunk being consumed
+    int cit = cpt > 0 ? c_begin - tile_l * cpt : 0;
+
+    int acc[F::kSets][MT][4];
+    float facc[MT][4];
+    int xs[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+#pragma unroll
+            for (int k = 0; k < F::kSets; ++k)
+                acc[k][mt][e] = 0;
+            facc[mt][e] = 0.f;
+        }
+        xs[mt][0] = xs[mt][1] = 0;
+    }
+
+    // |acc0 + acc1 / 2^kShift - (zero + offset) * sum(x)| of one 128-feature group stays below 2^22 for the narrow widths:
+    // int -> float by the 1.5 * 2^23 trick (two plain ALU/FMA operations) instead of a conversion instruction
+    constexpr long long kBound = 128LL * 128 * (((1 << Q) - 1) + ((1 << Q) - 1) + (1 << (Q - 1)));
+    constexpr bool kMagic = kBound < (1LL << 22);
+
+    for (int ci = c_begin; ci < c_end && ok; ++ci) {
+        ok = mbar_wait_bounded(&full[slot], phase, a.status, STATUS_TIMEOUT_TMA);
+        if (!ok)
+            break;
+        const uint8_t *stage = my_ring + (size_t)slot * chunk_bytes;
+        const int uf = cit * a.cu;              // first unit of the chunk within this CTA's K range
+        const int nu = min(a.cu, n_units - uf); // units in the chunk
+        for (int ub = 0; ub < nu; ub += GS) {
+            const uint8_t *blk = stage + (size_t)ub * a.unit_bytes;
+            const int left = nu - ub; // units of this block that exist
+#pragma unroll
+            for (int ui = 0; ui < GS; ++ui) {
+                if (GS == 1 || ui < left) {
+                    const uint8_t *unit = blk + ui * a.unit_bytes;
+                    uint32_t R[4][4];
+                    F::expand(unit, lane, R);
+                    const uint8_t *rec = rec_base + (size_t)(uf + ub + ui) * MR * 128;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint8_t *bp = (GS == 1 || my_slot == ui) ? rec + mt * 1024 + rec_lane : zero_base;
+                        const uint4 blo = *reinterpret_cast<const uint4 *>(bp + swz);
+                        const uint4 bhi = *reinterpret_cast<const uint4 *>(bp + (16 ^ swz));
+                        const uint32_t b[8] = { blo.x, blo.y, blo.z, blo.w, bhi.x, bhi.y, bhi.z, bhi.w };
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // GROUPED: the first step of every set in a block starts from zero
+                            const bool first = GROUPED && ui == 0 && stream_first_in_set<F>(j);
+                            if (first)
+                                mma_u8s8_first(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
+                            else
+                                mma_u8<false>(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
+                        }
+                    }
+                    if (!GROUPED) {
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const int2 sv = *reinterpret_cast<const int2 *>(sums + (uf + ub + ui) * MR + 8 * mt + 2 * t);
+                            xs[mt][0] += sv.x;
+                            xs[mt][1] += sv.y;
+                        }
+                    }
+                }
+            }
+            if (GROUPED) {
+                // fold the block: column 2 t + j of the accumulators is token (col % MP) of unit ub + col / MP
+                const int ul = uf + ub; // first unit of the block within the CTA's K range (a multiple of GS)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    uint2 pk[2]; // [column of the pair] -> (row g, row g + 8)
+                    int xv[2];
+                    if (MP == 1) {
+                        pk[0] = (2 * t < left) ? *reinterpret_cast<const uint2 *>(blk + (2 * t) * a.unit_bytes + Q * 256 + 8 * g) : make_uint2(0, 0);
+                        pk[1] = (2 * t + 1 < left) ? *reinterpret_cast<const uint2 *>(blk + (2 * t + 1) * a.unit_bytes + Q * 256 + 8 * g) : make_uint2(0, 0);
+                        const int2 sv = *reinterpret_cast<const int2 *>(sums + ul + 2 * t);
+                        xv[0] = sv.x;
+                        xv[1] = sv.y;
+                    } else {
+                        const int sl = (2 * t) / MP; // both columns of the pair belong to the same unit
+                        pk[0] = (GS == 1 || sl < left) ? *reinterpret_cast<const uint2 *>(blk + sl * a.unit_bytes + Q * 256 + 8 * g) : make_uint2(0, 0);
+                        pk[1] = pk[0];
+                        const int2 sv = *reinterpret_cast<const int2 *>(sums + (ul + sl) * MR + 8 * mt + ((2 * t) & (MP - 1)));
+                        xv[0] = sv.x;
+                        xv[1] = sv.y;
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t p = (e >> 1) ? pk[e & 1].y : pk[e & 1].x;
+                        const float sc_w = __uint_as_float(p & ~kZeroMask);
+                        const int z = (int)(p & kZeroMask);
+                        int v = acc[0][mt][e];
+                        if (F::kSets == 2)
+                            v += acc[F::kSets - 1][mt][e] >> F::kShift; // exact: every term of that set is a multiple of 2^kShift
+                        v -= z * xv[e & 1];
+                        const float fv = kMagic ? __int_as_float(v + 0x4b400000) - 12582912.0f : (float)v;
+                        facc[mt][e] = fmaf(fv, sc_w, facc[mt][e]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && q_left > 0)
+            issue(slot); // the slot just consumed is free again
+        if (++slot == a.ring) {
+            slot = 0;
+            phase ^= 1;
+        }
+        // ---- end of this warp's share of a tile: hand the partial sums over
+        const bool tile_done = cit == cpt - 1 || ci == c_end - 1;
+        if (tile_done) {
+            int *dst = red + (size_t)(warp + tile_l) * MT * 128; // [token tile][16 rows][8 columns]
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                int v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (GROUPED) {
+                        v[e] = __float_as_int(facc[mt][e]);
+                        facc[mt][e] = 0.f;
+                    } else {
+                        int z = zoff;
+                        const int n = (r_begin + tile_l) * 16 + g + 8 * (e >> 1);
+                        if (a.scale_mode == ABQ_SCALE_CHANNEL && a.w_zero && n < a.N)
+                            z += a.w_zero[n];
+                        int x = acc[0][mt][e];
+                        if (F::kSets == 2)
+                            x += acc[F::kSets - 1][mt][e] >> F::kShift;
+                        v[e] = x - z * xs[mt][e & 1];
+#pragma unroll
+                        for (int k = 0; k < F::kSets; ++k)
+                            acc[k][mt][e] = 0;
+                    }
+                }
+                xs[mt][0] = xs[mt][1] = 0;
+                *reinterpret_cast<int2 *>(dst + mt * 128 + g * 8 + 2 * t) = make_int2(v[0], v[1]);
+                *reinterpret_cast<int2 *>(dst + mt * 128 + (g + 8) * 8 + 2 * t) = make_int2(v[2], v[3]);
+            }
+        }
+        if (++cit == cpt) {
+            cit = 0;
+            ++tile_l;
+        }
+    }
+    // A wait that expired may have left copies in flight: give them one more bounded chance to land before the shared
+    // memory they target is released.
+    if (!ok && lane == 0) {
+        for (int i = 0; i < a.ring; ++i)
+            mbar_wait_bounded(&full[i], 0, nullptr, 0);
+    }
+    __syncthreads();
+
+    // ---- the CTA's tiles: add the warps' partial sums in warp order, finish, store.  Thread per (tile, token, row).
+    const int outs = T * a.M * 16;
+    auto tile_sum = [&](int tl, int m, int row, bool &any) -> int {
+        int isum = 0;
+        float fsum = 0.f;
+        for (int w = 0; w < nw; ++w) {
+            const int wb = (int)((long long)w * total_chunks / nw), we = (int)((long long)(w + 1) * total_chunks / nw);
+            if (wb < we && wb < (tl + 1) * cpt && we > tl * cpt) {
+                const int *src = red + (size_t)(w + tl) * MT * 128 + (m >> 3) * 128 + row * 8;
+                if (GROUPED) {
+#pragma unroll
+                    for (int sl = 0; sl < GS; ++sl)
+                        fsum += __int_as_float(src[sl * MP + (m & (MP - 1))]);
+                } else {
+                    isum += src[m & 7];
+                }
+                any = true;
+            }
+        }
+        return GROUPED ? __float_as_int(fsum) : isum;
+    };
+    auto finish = [&](int r, int m, int row, int v) {
+        const int n = r * 16 + row;
+        if (n >= a.N)
+            return;
+        const size_t o = (size_t)m * a.N + n;
+        if (a.out_dtype == ABQ_OUT_INT32) {
+            reinterpret_cast<int *>(a.D)[o] = v;
+        } else {
+            __half h;
+            if (a.scale_mode == ABQ_SCALE_TENSOR_COMPAT) {
+                h = __hmul(__int2half_rn(v), ld_half(a.C));
+            } else {
+                float f = GROUPED ? __int_as_float(v) : (float)v * __half2float(ld_half(a.w_scale + n));
+                if (a.x_scale)
+                    f *= a.x_scale[m];
+                h = __float2half_rn(f);
+            }
+            reinterpret_cast<__half *>(a.D)[o] = h;
+        }
+    };
+    if (a.slices == 1) {
+        for (int idx = threadIdx.x; idx < outs; idx += blockDim.x) {
+            const int tl = idx / (a.M * 16), rem = idx - tl * a.M * 16;
+            const int m = rem >> 4, row = rem & 15;
+            bool any = false;
+            const int v = tile_sum(tl, m, row, any);
+            finish(r_begin + tl, m, row, v);
+        }
+        return;
+    }
+    // ---- K split over CTAs as well: a workspace slot per slice, the CTA arriving last at a tile's counter adds the
+    // slots in slice order (the result does not depend on who finishes)
+    for (int idx = threadIdx.x; idx < outs; idx += blockDim.x) {
+        const int tl = idx / (a.M * 16), rem = idx - tl * a.M * 16;
+        bool any = false;
+        const int v = tile_sum(tl, rem >> 4, rem & 15, any);
+        a.partials[((size_t)s * a.tiles + r_begin + tl) * (size_t)a.M * 16 + rem] = v;
+    }
+    __threadfence();
+    __syncthreads();
+    int *last = red; // reuse: one flag per tile of this CTA
+    if ((int)threadIdx.x < T) {
+        const int old = atomicAdd(a.counters + r_begin + threadIdx.x, 1);
+        last[threadIdx.x] = old == a.slices - 1;
+        if (old == a.slices - 1)
+            a.counters[r_begin + threadIdx.x] = 0; // leave the counter ready for the next launch
+    }
+    __syncthreads();
+    __threadfence();
+    for (int idx = threadIdx.x; idx < outs; idx += blockDim.x) {
+        const int tl = idx / (a.M * 16), rem = idx - tl * a.M * 16;
+        if (!last[tl])
+            continue;
+        int isum = 0;
+        float fsum = 0.f;
+        for (int sl = 0; sl < a.slices; ++sl) {
+            const int pv = __ldcg(a.partials + ((size_t)sl * a.tiles + r_begin + tl) * (size_t)a.M * 16 + rem);
+            if (GROUPED)
+                fsum += __int_as_float(pv);
+            else
+                isum += pv;
+        }
+        finish(r_begin + tl, rem >> 4, rem & 15, GROUPED ? __float_as_int(fsum) : isum);
+    }
+}
+
+// ------------------------------------------------------------------------------------------- host side
+template <int Q, int MT, int MP, bool GROUPED>
+static cudaError_t stream_launch_variant(const abq_gemm_state *st, const StreamArgs &args, cudaStream_t stream)
+{
+    auto kern = stream_kernel<Q, MT, MP, GROUPED>;
+    static thread_local SmemOptIn opted;
+    cudaError_t e = opted.ensure(kern, st->shared_mem_size);
+    if (e != cudaSuccess)
+        return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(st->grid[0], 1, 1);
+    cfg.blockDim = dim3(args.nw * 32);
+    cfg.dynamicSmemBytes = st->shared_mem_size;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (st->p.flags & ABQ_FLAG_PDL) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kern, args);
+}
+
+template <int Q>
+static cudaError_t stream_launch_q(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, bool grouped, cudaStream_t stream)
+{
+    if (!grouped)
+        return MT == 2 ? stream_launch_variant<Q, 2, 8, false>(st, args, stream) : stream_launch_variant<Q, 1, 8, false>(st, args, stream);
+    if (MT == 2)
+        return stream_launch_variant<Q, 2, 8, true>(st, args, stream);
+    switch (MP) {
+    case 1: return stream_launch_variant<Q, 1, 1, true>(st, args, stream);
+    case 2: return stream_launch_variant<Q, 1, 2, true>(st, args, stream);
+    case 4: return stream_launch_variant<Q, 1, 4, true>(st, args, stream);
+    default: return stream_launch_variant<Q, 1, 8, true>(st, args, stream);
+    }
+}
+
+template <int Q>
+static cudaError_t stream_prepare_q(const uint32_t *planes, const __half *w_scale, const uint8_t *w_zero, uint8_t *out, int N, int K, int w_signed,
+                                    int grouped, int groups_per_scale, int scale_groups, cudaStream_t stream)
+{
+    const long long threads = (long long)((N + 15) / 16) * (K / 128) * 32;
+    prepare_stream_kernel<Q><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(planes, w_scale, w_zero, out, N, K, w_signed, grouped,
+                                                                                   groups_per_scale, scale_groups);
+    return cudaGetLastError();
+}
+
+// one definition per weight width, in gemm_stream_w<Q>.cu
+#define ABQ_STREAM_WIDTH(Q)                                                                                                                     \
+    cudaError_t stream_launch_w##Q(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, bool grouped, cudaStream_t stream)        \
+    {                                                                                                                                           \
+        return stream_launch_q<Q>(st, args, MT, MP, grouped, stream);                                                                           \
+    }                                                                                                                                           \
+    cudaError_t stream_prepare_w##Q(const uint32_t *planes, const __half *w_scale, const uint8_t *w_zero, uint8_t *out, int N, int K,          \
+                                    int w_signed, int grouped, int groups_per_scale, int scale_groups, cudaStream_t stream)                    \
+    {                                                                                                                                           \
+        return stream_prepare_q<Q>(planes, w_scale, w_zero, out, N, K, w_signed, grouped, groups_per_scale, scale_groups, stream);              \
+    }
+#define ABQ_STREAM_DECLARE(Q)                                                                                                                   \
+    cudaError_t stream_launch_w##Q(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, bool grouped, cudaStream_t stream);       \
+    cudaError_t stream_prepare_w##Q(const uint32_t *planes, const __half *w_scale, const uint8_t *w_zero, uint8_t *out, int N, int K,          \
+                                    int w_signed, int grouped, int groups_per_scale, int scale_groups, cudaStream_t stream);
+ABQ_STREAM_DECLARE(2)
+ABQ_STREAM_DECLARE(3)
+ABQ_STREAM_DECLARE(4)
+ABQ_STREAM_DECLARE(8)
+
+} // namespace abq

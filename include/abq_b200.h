@@ -70,10 +70,21 @@ typedef enum abq_route {
 } abq_route;
 
 enum {
-    ABQ_FLAG_PDL = 1, /* launch with programmatic dependent launch so that consecutive GEMMs overlap */
-    /* Route I8_UMMA only: the int8 expansion of W already sits in this plan's workspace (abq_gemm_prepare_weights
-     * put it there and nothing has overwritten it since): abq_gemm_exec expands the activations only.  For weights
-     * that stay the same from call to call, with a workspace of their own. */
+    /* Launch with programmatic dependent launch so that consecutive GEMMs overlap.  The decode kernels then request
+     * their first weights BEFORE waiting for the kernel launched ahead of them on the stream: W (or w_prepared) must
+     * be complete before that kernel starts -- do not launch a PDL GEMM directly behind the kernel that writes its
+     * weights (abq_pack_int32, abq_gemm_prepare_weights, an upload); X, scales and D are read / written after the wait. */
+    ABQ_FLAG_PDL = 1,
+    /* The weights have been brought into the form the route computes on, once, by abq_gemm_prepare_weights; later calls
+     * skip that work.  For weights that stay the same from call to call (a model's linear layers).
+     *   Route I8_UMMA: the int8 expansion of W sits in this plan's workspace (a workspace of its own, which nothing
+     *     else overwrites): abq_gemm_exec expands the activations only.
+     *   Route I8_MMA (decode shapes): params.w_prepared points to abq_gemm_prepared_weight_bytes() bytes owned by the
+     *     caller; abq_gemm_prepare_weights re-orders the planes W (and per-group scales / zero points) into it -- the
+     *     same bits in the order the kernel consumes them -- and abq_gemm_exec reads w_prepared instead of W.  One
+     *     prepared copy serves every token count up to 16 with the same scale mode and signedness.  Where
+     *     abq_gemm_prepared_weight_bytes() is 0 (widths 1, 5, 6, 7; unsigned 8-bit activations) or w_prepared is
+     *     NULL the flag is ignored on this route and W is read. */
     ABQ_FLAG_WEIGHTS_PREPARED = 2,
     /* X points to fp16 activations [M][K] instead of planes; the call quantises them itself exactly as the
      * FasterTransformer wrapper's pack does (abq_gemm_wrapper.cu:29-54): code = (int)(half(x) * half(x_quant_scale[0])),
@@ -101,7 +112,9 @@ typedef struct abq_gemm_params {
     int scale_mode;         /* abq_scale_mode */
     int group_size;         /* ABQ_SCALE_GROUP: multiple of 128 dividing K */
     const void *w_scale;    /* fp16 [N] (CHANNEL) or [N][K/group_size] (GROUP) */
-    const uint8_t *w_zero;  /* optional zero points, same shape as w_scale, NULL = 0 */
+    const uint8_t *w_zero;  /* optional zero points, same shape as w_scale, NULL = 0; each must lie in the code range,
+                               0 .. 2^w_bits - 1: the kernels' exactness bounds (int8 operands, the 2^22 bound of the
+                               integer-to-float step) assume it and nothing checks device data */
     const float *x_scale;   /* optional per-token fp32 scale [M], NULL = 1 */
     int route;              /* abq_route */
     int flags;              /* ABQ_FLAG_* */
@@ -109,6 +122,7 @@ typedef struct abq_gemm_params {
     size_t workspace_bytes;
     int *status_word;       /* optional device int, set non-zero by a kernel whose bounded wait expired */
     const float *x_quant_scale; /* ABQ_FLAG_X_HALF: device float, the static activation scale */
+    void *w_prepared;           /* ABQ_FLAG_WEIGHTS_PREPARED on route I8_MMA: the re-ordered weights, 16-byte aligned */
 } abq_gemm_params;
 
 /*
@@ -175,9 +189,19 @@ ABQ_API abq_status abq_quantize_pack_half(const void *in_half, const float *scal
                                   int bits, int mode, abq_stream_t stream);
 
 /*
- * Expand the weight planes of a planned GEMM into its workspace once, for plans with ABQ_FLAG_WEIGHTS_PREPARED
- * (a no-op returning ABQ_OK on routes that read the planes directly).  No reference counterpart: the reference
- * multiplies the planes themselves.
+ * Bytes of the prepared copy of W that a decode-shape plan (route I8_MMA) with ABQ_FLAG_WEIGHTS_PREPARED reads through
+ * params->w_prepared: the planes' own w_bits * N * K / 8 bytes (N rounded up to 16) plus, with per-group scales, 4
+ * bytes per row and 128 input features.  Depends on N, K, w_bits, scale_mode, x_bits / x_signed only.  0 = this problem
+ * has no prepared form on that route.  No reference counterpart.
+ */
+ABQ_API size_t abq_gemm_prepared_weight_bytes(const abq_gemm_params *params);
+
+/*
+ * Bring the weights of a planned GEMM with ABQ_FLAG_WEIGHTS_PREPARED into the form its route computes on, once: the
+ * int8 expansion in the plan's workspace (route I8_UMMA) or the re-ordered copy in params.w_prepared (route I8_MMA).
+ * A no-op returning ABQ_OK for plans that read the planes directly.  No reference counterpart: the reference
+ * multiplies the planes themselves (its weights are packed offline into planes, engine/common/pack.cu, and that
+ * format stays the input here).
  */
 ABQ_API abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_stream_t stream);
 

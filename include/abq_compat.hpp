@@ -37,6 +37,21 @@ inline void set_workspace(void *device_ptr, size_t bytes)
     workspace().bytes = bytes;
 }
 
+// abq_gemm_static_scratch, and for problems whose planned route needs more scratch than the built-in array holds
+// (e.g. 128 x 4096 x 4096 on the tensor-core route: 17 MB of expanded operands) the same call on the route that needs
+// next to none (16 rows per launch, reading the planes directly): slower, but the reference's signatures leave no way
+// to ask the caller for memory.
+inline abq_status static_scratch(const abq_gemm_params &p, cudaStream_t stream)
+{
+    abq_status s = abq_gemm_static_scratch(&p, stream);
+    if (s == ABQ_ERR_WORKSPACE && p.route == ABQ_ROUTE_AUTO) {
+        abq_gemm_params q = p;
+        q.route = ABQ_ROUTE_I8_MMA;
+        s = abq_gemm_static_scratch(&q, stream);
+    }
+    return s;
+}
+
 inline abq_status run(abq_gemm_params &p, cudaStream_t stream)
 {
     const Workspace &w = workspace();
@@ -45,7 +60,7 @@ inline abq_status run(abq_gemm_params &p, cudaStream_t stream)
         p.workspace_bytes = w.bytes;
         return abq_gemm(&p, stream);
     }
-    return abq_gemm_static_scratch(&p, stream);
+    return static_scratch(p, stream);
 }
 
 } // namespace abq_compat
@@ -152,7 +167,7 @@ void AqBMMAExecFn(AqBMMAOpState &state, cudaStream_t stream = NULL)
     else if (state.plan.init_success)
         s = abq_gemm_exec(&state.plan, stream);
     else
-        s = abq_gemm_static_scratch(&state.plan.p, stream);
+        s = abq_compat::static_scratch(state.plan.p, stream);
     if (s != ABQ_OK)
         std::fprintf(stderr, "AqBMMAExecFn: %s\n", abq_status_string(s));
 }
@@ -267,7 +282,7 @@ public:
             p.workspace_bytes = abq_gemm_ws_bytes - used;
             s = abq_gemm(&p, stream);
         } else { // the reference's layers size it for the planes only
-            s = abq_gemm_static_scratch(&p, stream);
+            s = abq_compat::static_scratch(p, stream);
         }
         report(s, "gemm");
     }

@@ -1,0 +1,170 @@
+"""Decode route over prepared weights (ABQ_FLAG_WEIGHTS_PREPARED + w_prepared: the planes re-ordered once at load time).
+
+Same bar as the plane path: int32 bit for bit against the oracle's exact product, the reference-compatible fp16 mode bit
+for bit, per-channel / per-group fp16 within the tolerance stated in test_gpu_gemm_fp16.py of the oracle's float64
+dequantised product.  The prepared copy is made by the library from the reference's plane format, which stays the input."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import dev, planes_dev, rand_codes
+from test_gpu_gemm_fp16 import check_close
+
+pytestmark = pytest.mark.gpu
+
+
+def run_prepared(abq, xp, wp, M, N, K, *, x_bits, w_bits, x_signed, w_signed, out_fp16=False, scale_mode=0, group_size=0, C=None,
+                 w_scale=None, w_zero=None, x_scale=None, flags=0, x_quant_scale=None, calls=1):
+    from abq_llm_b200 import binding as B
+    out = torch.full((M, N), -7, dtype=torch.float16 if out_fp16 else torch.int32, device="cuda")
+    ws = torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, x_bits, w_bits, abq.ROUTE_I8_MMA)), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    p = B.make_params(M, N, K, xp, wp, out, x_bits=x_bits, w_bits=w_bits, x_signed=x_signed, w_signed=w_signed,
+                      out_dtype=abq.OUT_FP16 if out_fp16 else abq.OUT_INT32, scale_mode=scale_mode, group_size=group_size, C=C,
+                      w_scale=w_scale, w_zero=w_zero, x_scale=x_scale, route=abq.ROUTE_I8_MMA, flags=flags | abq.FLAG_WEIGHTS_PREPARED,
+                      workspace=ws, status_word=status, x_quant_scale=x_quant_scale)
+    nbytes = abq.gemm_prepared_weight_bytes(p)
+    assert nbytes >= w_bits * N * K // 8
+    prepared = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    p.w_prepared = prepared.data_ptr()
+    st = abq.gemm_init(p)
+    abq.gemm_prepare_weights(st)
+    torch.cuda.synchronize()
+    for _ in range(calls):
+        abq.gemm_exec(st)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, f"device status word {int(status.item())}"
+    return out.cpu().numpy(), st
+
+
+INT_CASES = [
+    # M, N, K, x_bits, w_bits, x_signed, w_signed
+    (1, 4096, 4096, 8, 2, True, False), (1, 48, 128, 8, 2, True, True), (2, 200, 1152, 8, 3, True, False), (3, 520, 640, 4, 4, False, False),
+    (4, 1000, 2048, 8, 4, True, True), (5, 72, 384, 6, 3, True, True), (8, 4096, 1024, 8, 8, True, True), (9, 136, 1152, 7, 2, False, False),
+    (16, 512, 4096, 8, 4, True, False), (16, 1024, 11008, 8, 3, True, False), (20, 96, 2176, 8, 2, True, True), (33, 320, 1280, 8, 8, True, False),
+    (1, 11008, 4096, 8, 3, True, False), (7, 4096, 11008, 8, 4, True, False), (1, 16, 128, 1, 2, False, False), (12, 4096, 4096, 3, 3, True, True),
+]
+
+
+@pytest.mark.parametrize("case", INT_CASES, ids=lambda c: "M{}N{}K{}a{}w{}{}{}".format(*c[:5], "s" if c[5] else "u", "s" if c[6] else "u"))
+def test_int32_bit_exact(abq, oracle, cuda, case):
+    M, N, K, p, q, xs, ws = case
+    rng = np.random.default_rng(sum(case[:5]))
+    x, w = rand_codes(rng, M, K, p, xs), rand_codes(rng, N, K, q, ws)
+    got, st = run_prepared(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=xs, w_signed=ws, calls=2)
+    want = oracle.gemm_values_blas(x, w)
+    if M * N * K * p * q <= 1 << 26:
+        assert np.array_equal(oracle.compute_ref(oracle.pack(w, q), oracle.pack(x, p), xs, ws), want)
+    assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} of {got.size} differ"
+
+
+@pytest.mark.parametrize("env", [{"ABQ_STREAM_FULL": "1"}, {"ABQ_STREAM_CU": "8", "ABQ_STREAM_RING": "2"}, {"ABQ_STREAM_SLICES": "3"},
+                                 {"ABQ_STREAM_WARPS": "4", "ABQ_STREAM_CTAS": "37"}, {"ABQ_STREAM_WARPS": "16", "ABQ_STREAM_FULL": "1", "ABQ_STREAM_CTAS": "296"}],
+                         ids=lambda e: ",".join(f"{k[11:]}={v}" for k, v in e.items()))
+@pytest.mark.parametrize("M,q", [(1, 2), (4, 3), (8, 4), (16, 2)])
+def test_plan_variants(abq, oracle, cuda, monkeypatch, env, M, q):
+    """Other launch shapes than the planner's default (one CTA per SM, deeper / shallower rings, K split over CTAs, fewer
+    or more CTAs and warps): the same bits."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    N, K = 1512, 2688
+    rng = np.random.default_rng(M + q)
+    x, w = rand_codes(rng, M, K, 8, True), rand_codes(rng, N, K, q, False)
+    xp, wp = planes_dev(oracle, x, 8), planes_dev(oracle, w, q)
+    got, st = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, calls=2)
+    assert np.array_equal(got, oracle.gemm_values_blas(x, w))
+    scale = rng.uniform(0.001, 0.02, size=(N, K // 128)).astype(np.float16)
+    zero = rng.integers(0, 1 << q, size=(N, K // 128)).astype(np.uint8)
+    got16, _ = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_fp16=True, scale_mode=abq.SCALE_GROUP,
+                            group_size=128, w_scale=dev(scale), w_zero=dev(zero), calls=2)
+    check_close(got16, oracle.dequant_gemm(x, w, scale, zero.astype(np.int32), None, 128))
+
+
+@pytest.mark.parametrize("M,N,K,q,group", [(1, 4096, 4096, 2, 128), (2, 512, 4096, 3, 128), (4, 320, 11008, 4, 128), (8, 128, 2048, 4, 256),
+                                           (3, 64, 1536, 2, 384), (16, 4096, 4096, 4, 128), (1, 72, 1152, 8, 128), (5, 200, 640, 3, 128),
+                                           (40, 320, 1024, 4, 128), (33, 96, 11008, 3, 256), (16, 512, 11008, 2, 128), (1, 4096, 11008, 3, 128)])
+@pytest.mark.parametrize("w_signed", [False, True])
+def test_per_group(abq, oracle, cuda, M, N, K, q, group, w_signed):
+    rng = np.random.default_rng(N + K + q + group)
+    x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+    w = rand_codes(rng, N, K, q, w_signed)
+    G = K // group
+    ws = rng.uniform(0.001, 0.02, size=(N, G)).astype(np.float16)
+    wz = rng.integers(0, 1 << q, size=(N, G)).astype(np.uint8)
+    xs = rng.uniform(0.5, 2.0, size=M).astype(np.float32)
+    got, st = run_prepared(abq, planes_dev(oracle, x, 8), planes_dev(oracle, w, q), M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=w_signed,
+                           out_fp16=True, scale_mode=abq.SCALE_GROUP, group_size=group, w_scale=dev(ws), w_zero=dev(wz), x_scale=dev(xs), calls=2)
+    check_close(got, oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), xs, group))
+
+
+@pytest.mark.parametrize("M,N,K,q", [(1, 4096, 4096, 2), (4, 1024, 4096, 3), (16, 512, 11008, 4), (7, 200, 1152, 4), (1, 64, 128, 8)])
+@pytest.mark.parametrize("with_zero", [False, True])
+def test_per_channel_and_tensor_compat(abq, oracle, cuda, M, N, K, q, with_zero):
+    rng = np.random.default_rng(N + K + q)
+    x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+    w = rand_codes(rng, N, K, q, False)
+    ws = rng.uniform(0.001, 0.02, size=N).astype(np.float16)
+    wz = rng.integers(0, 1 << q, size=N).astype(np.uint8) if with_zero else None
+    xs = rng.uniform(0.01, 0.05, size=M).astype(np.float32)
+    xp, wp = planes_dev(oracle, x, 8), planes_dev(oracle, w, q)
+    got, _ = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_fp16=True, scale_mode=abq.SCALE_CHANNEL,
+                          w_scale=dev(ws), w_zero=None if wz is None else dev(wz), x_scale=dev(xs))
+    check_close(got, oracle.dequant_gemm(x, w, ws, None if wz is None else wz.astype(np.int32), xs, None))
+    if not with_zero:
+        scale = np.float16(0.0123)
+        got, _ = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_fp16=True,
+                              scale_mode=abq.SCALE_TENSOR_COMPAT, C=dev(np.array([scale])))
+        want = oracle.dequant_tensor_compat(oracle.gemm_values_blas(x, w), scale)
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("M,N,K,q", [(1, 1024, 4096, 2), (6, 320, 1152, 4), (16, 256, 11008, 3)])
+def test_fp16_activations_into_prepared_weights(abq, oracle, cuda, M, N, K, q):
+    """ABQ_FLAG_X_HALF together with prepared weights: the codes of the FasterTransformer quantiser, the exact product."""
+    rng = np.random.default_rng(M + N)
+    x = rng.normal(0, 2.0, size=(M, K)).astype(np.float16)
+    w = rand_codes(rng, N, K, q, False)
+    qs = torch.full((1,), 13.0, dtype=torch.float32, device="cuda")
+    got, _ = run_prepared(abq, torch.from_numpy(x).cuda(), planes_dev(oracle, w, q), M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False,
+                          flags=abq.FLAG_X_HALF, x_quant_scale=qs)
+    _, codes = oracle.quantize_half_compat(x, 13.0, 8)
+    codes = ((codes + 128) % 256) - 128
+    assert np.array_equal(got, oracle.gemm_values_blas(codes, w))
+
+
+def test_widths_without_a_prepared_form_read_the_planes(abq, oracle, cuda):
+    from abq_llm_b200 import binding as B
+    M, N, K, p, q = 4, 256, 512, 8, 5
+    rng = np.random.default_rng(1)
+    x, w = rand_codes(rng, M, K, p, True), rand_codes(rng, N, K, q, False)
+    out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    junk = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    prm = B.make_params(M, N, K, planes_dev(oracle, x, p), planes_dev(oracle, w, q), out, x_bits=p, w_bits=q, x_signed=True, w_signed=False,
+                        route=abq.ROUTE_I8_MMA, flags=abq.FLAG_WEIGHTS_PREPARED, w_prepared=junk)
+    assert abq.gemm_prepared_weight_bytes(prm) == 0
+    st = abq.gemm_init(prm)
+    abq.gemm_prepare_weights(st)  # nothing to do
+    abq.gemm_exec(st)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), oracle.gemm_values_blas(x, w))
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (12288, 4096), (11008, 4096), (4096, 11008)])
+@pytest.mark.parametrize("q", [2, 3, 4])
+def test_full_size_sweep_shapes(abq, oracle, cuda, N, K, q):
+    """The 36 GEMMs of the benchmark at full size on prepared weights: fp16 against the oracle, int32 bit for bit, and the
+    fp16 bits of the plane path where both fold the same groups in the same order (they do not promise that: only
+    reported closeness is required)."""
+    rng = np.random.default_rng(N + K + q)
+    w = rand_codes(rng, N, K, q, False)
+    ws = rng.uniform(0.001, 0.02, size=(N, K // 128)).astype(np.float16)
+    wz = rng.integers(0, 1 << q, size=(N, K // 128)).astype(np.uint8)
+    wp, dws, dwz = planes_dev(oracle, w, q), dev(ws), dev(wz)
+    for M in (1, 4, 16):
+        x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+        xp = planes_dev(oracle, x, 8)
+        got, _ = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_fp16=True, scale_mode=abq.SCALE_GROUP,
+                              group_size=128, w_scale=dws, w_zero=dwz, flags=abq.FLAG_PDL)
+        check_close(got, oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), None, 128))
+        acc, _ = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False)
+        assert np.array_equal(acc, oracle.gemm_values_blas(x, w)), f"M={M}"
