@@ -23,6 +23,12 @@ class AbqError(RuntimeError):
         super().__init__(f"{what}: abq_status {status} ({_status_string(status)})")
 
 
+class FusedAllreduce(ctypes.Structure):
+    """Mirror of ``abq_fused_allreduce``."""
+    _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("recv", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8),
+                ("counter", ctypes.c_void_p), ("rows_cap", ctypes.c_int)]
+
+
 class GemmParams(ctypes.Structure):
     """Mirror of ``abq_gemm_params`` (field order is part of the ABI)."""
     _fields_ = [
@@ -38,6 +44,7 @@ class GemmParams(ctypes.Structure):
         ("status_word", ctypes.c_void_p),
         ("x_quant_scale", ctypes.c_void_p),
         ("w_prepared", ctypes.c_void_p),
+        ("allreduce", ctypes.POINTER(FusedAllreduce)),
     ]
 
 
@@ -50,6 +57,7 @@ class GemmState(ctypes.Structure):
         ("shared_mem_size", ctypes.c_size_t),
         ("tile", ctypes.c_int * 4),
         ("tmap", (ctypes.c_ulonglong * 16) * 3),
+        ("ar", FusedAllreduce),
     ]
 
 
@@ -84,6 +92,8 @@ def lib() -> ctypes.CDLL:
         L.abq_pack_int4.argtypes = L.abq_pack_int32.argtypes
         L.abq_quantize_pack_half.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                              ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        L.abq_quantize_weights_half.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         L.abq_unpack_int8.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_void_p]
         _lib = L
@@ -134,7 +144,7 @@ def gemm_workspace_bytes(M: int, N: int, K: int, x_bits: int, w_bits: int, route
 
 def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dtype=OUT_INT32, scale_mode=SCALE_NONE,
                 group_size=0, C=None, w_scale=None, w_zero=None, x_scale=None, route=ROUTE_AUTO, flags=0, workspace=None,
-                status_word=None, x_quant_scale=None, w_prepared=None) -> GemmParams:
+                status_word=None, x_quant_scale=None, w_prepared=None, allreduce=None) -> GemmParams:
     p = GemmParams()
     p.M, p.N, p.K = M, N, K
     p.X, p.W, p.C, p.D = _ptr(X), _ptr(W), _ptr(C), _ptr(D)
@@ -148,7 +158,21 @@ def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dty
     p.status_word = _ptr(status_word)
     p.x_quant_scale = _ptr(x_quant_scale)
     p.w_prepared = _ptr(w_prepared)
+    if allreduce is not None:
+        p.allreduce = ctypes.pointer(allreduce)
+        p._keep_allreduce = allreduce  # the struct must outlive the call that reads it
     return p
+
+
+def make_fused_allreduce(world: int, rank: int, recv_ptrs, flag_ptrs, counter, rows_cap: int) -> FusedAllreduce:
+    """``recv_ptrs`` / ``flag_ptrs``: every rank's receive buffer / flag array as mapped into this process (ints)."""
+    d = FusedAllreduce()
+    d.world, d.rank, d.rows_cap = world, rank, rows_cap
+    for r in range(world):
+        d.recv[r] = int(recv_ptrs[r])
+        d.flags[r] = int(flag_ptrs[r])
+    d.counter = _ptr(counter)
+    return d
 
 
 def gemm_prepared_weight_bytes(params: GemmParams) -> int:
@@ -203,6 +227,12 @@ def pack_int4(nibbles, planes, rows: int, K: int, bits: int = 4, stream=None) ->
 def quantize_pack_half(x_half, scale, planes, rows: int, K: int, bits: int, mode: int = 0, stream=None) -> None:
     _check(lib().abq_quantize_pack_half(_ptr(x_half), _ptr(scale), _ptr(planes), rows, K, bits, mode, _stream(stream)),
            "abq_quantize_pack_half")
+
+
+def quantize_weights_half(w_half, planes, scale, zero, N: int, K: int, bits: int, group_size: int = 0, symmetric: bool = False, stream=None) -> None:
+    """fp16 weights [N][K] -> bit-planes + fp16 scale + u8 zero point (min/max calibration of the reference's quantiser)."""
+    _check(lib().abq_quantize_weights_half(_ptr(w_half), N, K, bits, group_size, int(symmetric), _ptr(planes), _ptr(scale), _ptr(zero), _stream(stream)),
+           "abq_quantize_weights_half")
 
 
 def unpack_int8(planes, out_i8, rows: int, K: int, bits: int, signed: bool, stream=None) -> None:

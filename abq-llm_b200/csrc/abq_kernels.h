@@ -14,6 +14,10 @@ cudaError_t pack_int4(const void *in, uint32_t *planes, int rows, int K, int bit
 cudaError_t quantize_pack_half(const __half *in, const float *scale, uint32_t *planes, int rows, int K, int bits, int mode,
                                cudaStream_t stream);
 
+// ---- wquant.cu
+cudaError_t quantize_weights(const __half *w, uint32_t *planes, __half *scale, uint8_t *zero, int N, int K, int bits, int group_size, int symmetric,
+                             cudaStream_t stream);
+
 // Largest dynamic shared-memory size already opted in for one kernel, per device (the attribute is per device and
 // function).  One instance per kernel instantiation and host thread: `static thread_local SmemOptIn done;`
 struct SmemOptIn {

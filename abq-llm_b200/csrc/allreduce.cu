@@ -10,8 +10,9 @@
 // gets the same bits.  The flag value is a call counter kept on the device, so a CUDA graph can replay the launch.
 // Several blocks share the message (remote loads are latency-bound: more of them in flight); block 0 flags the peers,
 // every block waits for the peers' flags, and the last block to finish advances the counter.
-// A buffer may be written again only after another all-reduce of the same ranks has completed in between (each
-// all-reduce is a barrier), which holds when every layer owns its buffer.
+// The call ends with a second flag round ("I have read your buffer"): a rank leaves the kernel only when every peer has
+// finished reading its partial, so whatever follows on its stream may overwrite the buffer at once -- a call site can be
+// used back to back -- and a flag can never be a call ahead of the one a rank is waiting for (it waits for equality).
 #include <cuda_fp16.h>
 
 #include "abq_common.cuh"
@@ -43,7 +44,7 @@ __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const
         for (;;) {
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-            if ((int)(v - epoch) >= 0)
+            if (v == epoch)
                 break;
             if (globaltimer_ns() - t0 > kWaitLimitNs) { // the peer never arrived: record it and carry on (the sum is then void)
                 if (status)
@@ -73,15 +74,41 @@ __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const
         *reinterpret_cast<uint4 *>(out + i) = o;
     }
     __syncthreads();
-    if (threadIdx.x == 0 && gridDim.x == 1) {
-        counter[0] = epoch; // a lone block needs no ticket
-    } else if (threadIdx.x == 0) {
+    bool last = gridDim.x == 1; // a lone block needs no ticket
+    if (threadIdx.x == 0 && gridDim.x > 1) {
         const uint32_t done = atomicAdd(counter + 1, 1u);
-        if (done == gridDim.x - 1) { // every block of this call has read the counter and finished
-            counter[1] = 0;
-            __threadfence();
-            counter[0] = epoch;
+        last = done == gridDim.x - 1; // every block of this call has read the counter and the peers' buffers
+    }
+    if (threadIdx.x == 0)
+        s_epoch = last ? 1u : 0u;
+    __syncthreads();
+    if (s_epoch == 0u)
+        return;
+    // ---- closing round, by the block that finished last: tell the peers that their buffers have been read, wait until
+    // they have read ours
+    if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
+        const int peer = threadIdx.x;
+        uint32_t *theirs = signals[peer] + signal_offset + world + rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+        const uint32_t *mine = signals[rank] + signal_offset + world + peer;
+        const unsigned long long t0 = globaltimer_ns();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v == epoch)
+                break;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                if (status)
+                    atomicOr(status, STATUS_TIMEOUT_PIPE);
+                break;
+            }
         }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        counter[1] = 0;
+        __threadfence();
+        counter[0] = epoch;
     }
 }
 

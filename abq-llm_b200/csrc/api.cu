@@ -169,6 +169,18 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
     abq_status s = validate(*params);
     if (s != ABQ_OK)
         return s;
+    if (params->allreduce) {
+        const abq_fused_allreduce &ar = *params->allreduce;
+        if (ar.world < 2 || ar.world > 8 || ar.rank < 0 || ar.rank >= ar.world || !ar.counter || ar.rows_cap < params->M)
+            return ABQ_ERR_INVALID_ARG;
+        for (int r = 0; r < ar.world; ++r)
+            if (!ar.recv[r] || !ar.flags[r] || (reinterpret_cast<uintptr_t>(ar.recv[r]) & 15))
+                return ABQ_ERR_INVALID_ARG;
+        if (params->out_dtype != ABQ_OUT_FP16)
+            return ABQ_ERR_INVALID_ARG;
+        state->ar = ar;
+        state->p.allreduce = nullptr; // the copy in the state is what the launch uses
+    }
     int route = params->route;
     if (route == ABQ_ROUTE_AUTO) {
         // up to 16 rows: one launch of the mma.sync route.  17..32 rows: two such launches still beat the tensor-core
@@ -193,6 +205,8 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
     if (s != ABQ_OK)
         return s;
     state->route = route;
+    if (state->ar.world > 0 && !(route == ABQ_ROUTE_I8_MMA && stream_planned(state) && state->cluster == 1))
+        return ABQ_ERR_UNSUPPORTED; // the fused all-reduce lives in the epilogue of the prepared-weights decode kernel
     state->init_success = 1;
     return ABQ_OK;
 }
@@ -300,6 +314,22 @@ abq_status abq_quantize_pack_half(const void *in_half, const float *scale, void 
         return ABQ_ERR_INVALID_ARG;
     return wrap(quantize_pack_half(reinterpret_cast<const __half *>(in_half), scale, reinterpret_cast<uint32_t *>(planes), rows, K,
                                    bits, mode, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+abq_status abq_quantize_weights_half(const void *w_half, int N, int K, int bits, int group_size, int symmetric, void *planes, void *scale_half,
+                                     uint8_t *zero, abq_stream_t stream)
+{
+    abq_status s = check_pack_args(w_half, planes, N, K, bits);
+    if (s != ABQ_OK)
+        return s;
+    if (!scale_half || !zero || group_size < 0 || (group_size > 0 && (group_size % 32 != 0 || K % group_size != 0)) || K > 32768 * 4)
+        return ABQ_ERR_INVALID_ARG;
+    if (symmetric && bits < 2)
+        return ABQ_ERR_INVALID_ARG;
+    if (reinterpret_cast<uintptr_t>(scale_half) & 1)
+        return ABQ_ERR_INVALID_ARG;
+    return wrap(quantize_weights(reinterpret_cast<const __half *>(w_half), reinterpret_cast<uint32_t *>(planes), reinterpret_cast<__half *>(scale_half),
+                                 zero, N, K, bits, group_size, symmetric != 0, reinterpret_cast<cudaStream_t>(stream)));
 }
 
 abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, int K, int bits, int is_signed, abq_stream_t stream)

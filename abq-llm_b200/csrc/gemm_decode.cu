@@ -114,8 +114,11 @@ abq_status decode_plan(abq_gemm_state *st, bool clear_counters)
 {
     const abq_gemm_params &p = st->p;
     // weights already re-laid-out for this route: the stream kernel (widths and modes it does not take read the planes)
-    if ((p.flags & ABQ_FLAG_WEIGHTS_PREPARED) && p.w_prepared && stream_supported(p))
-        return stream_plan(st, clear_counters);
+    if ((p.flags & ABQ_FLAG_WEIGHTS_PREPARED) && p.w_prepared && stream_supported(p)) {
+        const abq_status s = stream_plan(st, clear_counters);
+        if (s != ABQ_ERR_UNSUPPORTED)
+            return s; // (a shape the stream kernel has no launch for reads the planes after all)
+    }
     if (p.scale_mode == ABQ_SCALE_GROUP && (p.group_size % 128 != 0))
         return ABQ_ERR_UNSUPPORTED;
     DecodeLayout L;

@@ -1,5 +1,7 @@
 // Decode route over prepared weights (stream layout, gemm_stream_kernel.cuh): planner, load-time re-layout and launch
 // entry.  The kernel is instantiated per weight width in gemm_stream_w2.cu .. gemm_stream_w8.cu.
+#include <cstdlib>
+
 #include "gemm_stream_kernel.cuh"
 
 namespace abq {
@@ -9,7 +11,7 @@ namespace {
 // What abq_gemm_init decided for this route, kept in the state's route-specific words (tmap[1]).
 struct StreamPlan {
     int magic;
-    int nw, cu, ring, slices, units_per_slice, ctas_per_slice, MT, MP, grouped, unit_bytes, max_tiles_per_cta;
+    int nw, cu, ring, prefill, slices, units_per_slice, ctas_per_slice, MT, MP, grouped, unit_bytes, max_tiles_per_cta;
 };
 constexpr int kStreamMagic = 0x5354524d;
 
@@ -55,58 +57,87 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
     P->magic = kStreamMagic;
     P->grouped = grouped;
     P->MT = rows > 8 ? 2 : 1;
-    P->MP = P->MT == 2 || !grouped ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
+    P->unit_bytes = unit_bytes_of(p);
+    // token rows per column block: the fewest that hold the tokens, but more (fewer units per fold) while a block of
+    // 8 / MP units would be too large a chunk for the ring
+    int MP = P->MT == 2 || !grouped ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
+    while (MP < 8 && (8 / MP) * P->unit_bytes > 5120)
+        MP *= 2;
+    MP = env_int("ABQ_STREAM_MP", MP);
+    if ((MP != 1 && MP != 2 && MP != 4 && MP != 8) || MP < (rows > 8 ? 8 : rows) || ((P->MT == 2 || !grouped) && MP != 8))
+        return false;
+    P->MP = MP;
     const int GS = grouped && P->MT == 1 ? 8 / P->MP : 1;
     const int MR = P->MT == 2 ? 16 : P->MP;
-    P->unit_bytes = unit_bytes_of(p);
     const int units = p.K / 128;
     const int tiles = (p.N + 15) / 16;
     const int sms = device_sms();
     const int force_full = env_int("ABQ_STREAM_FULL", 0);
     const int force_slices = env_int("ABQ_STREAM_SLICES", 0);
-    for (int mode = force_full ? 1 : 0; mode < 2; ++mode) { // 0: two CTAs per SM, 1: one
-        const size_t budget = mode == 0 ? 112 * 1024 : 226 * 1024;
-        const int nw = env_int("ABQ_STREAM_WARPS", mode == 0 ? 8 : 16);
-        if (nw < 1 || nw > kStreamMaxWarps)
-            return false;
-        int cu = env_int("ABQ_STREAM_CU", 0);
-        if (cu <= 0) {
-            cu = (4608 / P->unit_bytes) / GS * GS;
-            cu = cu < GS ? GS : cu;
-            cu = cu > 8 ? 8 : cu;
-        }
-        if (cu % GS != 0)
-            return false;
-        for (int sl = force_slices > 0 ? force_slices : 1; sl <= kDecodeMaxSlices; ++sl) {
-            int ups = (units + sl - 1) / sl;
-            ups = (ups + cu - 1) / cu * cu;
-            const int slices = (units + ups - 1) / ups; // drop slices that would be empty
-            int cps = env_int("ABQ_STREAM_CTAS", sms) / slices;
-            cps = cps > tiles ? tiles : cps;
-            cps = cps < 1 ? 1 : cps;
-            const int max_T = (tiles + cps - 1) / cps;
-            const StreamSmem L0 = stream_smem_layout(nw, 0, cu, P->unit_bytes, ups, MR, max_T, P->MT);
-            if (L0.total < budget) {
-                int ring = (int)((budget - L0.total) / ((size_t)nw * cu * P->unit_bytes));
-                ring = ring > kStreamMaxRing ? kStreamMaxRing : ring;
-                const int forced = env_int("ABQ_STREAM_RING", 0);
-                if (forced > 0 && forced <= ring)
-                    ring = forced;
-                if (ring >= 2) {
-                    P->nw = nw;
-                    P->cu = cu;
-                    P->ring = ring;
-                    P->slices = slices;
-                    P->units_per_slice = ups;
-                    P->ctas_per_slice = cps;
-                    P->max_tiles_per_cta = max_T;
-                    *smem_bytes = stream_smem_layout(nw, ring, cu, P->unit_bytes, ups, MR, max_T, P->MT).total;
-                    return true;
+    const int force_warps = env_int("ABQ_STREAM_WARPS", 0);
+    if (force_warps < 0 || force_warps > kStreamMaxWarps)
+        return false;
+    // Preference: no K split before a K split (its partial sums go through global memory); then eight warps in a CTA that
+    // leaves room for a second one on the SM, sixteen in one that fills it, and so on down.
+    // A CTA of fewer than eight warps only when no K split makes room for eight.
+    for (int pass = 0; pass < 2; ++pass)
+    for (int sl = force_slices > 0 ? force_slices : 1; sl <= kDecodeMaxSlices; ++sl) {
+        // (two CTAs per SM?, warps) in order of preference
+        // (9 to 16 tokens: sixteen warps first -- twice the activation records to expand, twice the MMAs per unit)
+        static const int kShapes1[][2] = { { 1, 8 }, { 0, 16 }, { 0, 8 }, { 1, 4 }, { 0, 4 }, { 0, 2 } };
+        static const int kShapes2[][2] = { { 0, 16 }, { 1, 8 }, { 0, 8 }, { 1, 4 }, { 0, 4 }, { 0, 2 } };
+        for (const auto &shape : (P->MT == 2 ? kShapes2 : kShapes1)) {
+            if ((force_full && shape[0]) || (!force_warps && (shape[1] >= 8) != (pass == 0)))
+                continue;
+            const size_t budget = shape[0] ? 112 * 1024 : 226 * 1024;
+            {
+                const int nw = force_warps ? force_warps : shape[1];
+                int cu0 = env_int("ABQ_STREAM_CU", 0);
+                const bool cu_forced = cu0 > 0;
+                if (!cu_forced) {
+                    cu0 = (4608 / P->unit_bytes) / GS * GS;
+                    cu0 = cu0 < GS ? GS : cu0;
+                    cu0 = cu0 > 8 ? 8 : cu0;
+                }
+                if (cu0 % GS != 0)
+                    return false;
+                // smaller chunks before fewer warps or a K split: the ring of a shape that does not fit is halved first
+                for (int cu = cu0; cu >= GS && cu >= (cu_forced ? cu0 : 2) && (cu == cu0 || cu * P->unit_bytes >= 2048); cu = (cu / 2) / GS * GS) {
+                int ups = (units + sl - 1) / sl;
+                ups = (ups + cu - 1) / cu * cu;
+                const int slices = (units + ups - 1) / ups; // drop slices that would be empty
+                int cps = env_int("ABQ_STREAM_CTAS", sms) / slices;
+                cps = cps > tiles ? tiles : cps;
+                cps = cps < 1 ? 1 : cps;
+                const int max_T = (tiles + cps - 1) / cps;
+                const StreamSmem L0 = stream_smem_layout(nw, 0, cu, P->unit_bytes, ups, MR, max_T, P->MT);
+                if (L0.total < budget && max_T <= 64) { // (the kernel keeps a 64-entry table of its tiles)
+                    int ring = (int)((budget - L0.total) / ((size_t)nw * cu * P->unit_bytes));
+                    ring = ring > kStreamMaxRing ? kStreamMaxRing : ring;
+                    const int forced = env_int("ABQ_STREAM_RING", 0);
+                    if (forced > 0 && forced <= ring)
+                        ring = forced;
+                    if (ring >= 2) {
+                        P->nw = nw;
+                        P->cu = cu;
+                        P->ring = ring;
+                        P->prefill = env_int("ABQ_STREAM_PREFILL", ring);
+                        P->prefill = P->prefill < 0 ? 0 : (P->prefill > ring ? ring : P->prefill);
+                        P->slices = slices;
+                        P->units_per_slice = ups;
+                        P->ctas_per_slice = cps;
+                        P->max_tiles_per_cta = max_T;
+                        *smem_bytes = stream_smem_layout(nw, ring, cu, P->unit_bytes, ups, MR, max_T, P->MT).total;
+                        return true;
+                    }
+                }
+                if (cu == GS)
+                    break;
                 }
             }
-            if (force_slices > 0)
-                break;
         }
+        if (force_slices > 0)
+            break;
     }
     return false;
 }
@@ -186,6 +217,7 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.ctas_per_slice = P.ctas_per_slice;
     a.cu = P.cu;
     a.ring = P.ring;
+    a.prefill = P.prefill;
     a.nw = P.nw;
     a.Wp = reinterpret_cast<const uint8_t *>(p.w_prepared);
     a.x_plane_words = (size_t)p.M * (p.K / 32);
@@ -207,6 +239,20 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.scale_mode = p.scale_mode;
     a.w_signed = p.w_signed;
     a.status = p.status_word;
+    a.ar.world = st->ar.world;
+    a.ar.rank = st->ar.rank;
+    a.ar.rows_cap = st->ar.rows_cap;
+    a.ar.counter = st->ar.counter;
+    for (int r = 0; r < 8; ++r) {
+        a.ar.recv[r] = reinterpret_cast<__half *>(st->ar.recv[r]);
+        a.ar.flags[r] = st->ar.flags[r];
+    }
+#ifdef ABQ_STREAM_TRACE
+    {
+        const char *tp = std::getenv("ABQ_TRACE_PTR");
+        a.trace = tp ? reinterpret_cast<unsigned long long *>(std::strtoull(tp, nullptr, 0)) : nullptr;
+    }
+#endif
     const size_t out_row_bytes = (size_t)p.N * (p.out_dtype == ABQ_OUT_INT32 ? 4 : 2);
     for (int m0 = 0; m0 < p.M; m0 += 16) { // taller problems: 16 rows per launch, in stream order (they share the workspace)
         a.M = p.M - m0 < 16 ? p.M - m0 : 16;
@@ -214,6 +260,7 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
                                           : reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
         a.D = reinterpret_cast<uint8_t *>(p.D) + (size_t)m0 * out_row_bytes;
         a.x_scale = p.x_scale ? p.x_scale + m0 : nullptr;
+        a.ar.row0 = m0;
         cudaError_t e;
         switch (p.w_bits) {
         case 2: e = stream_launch_w2(st, a, P.MT, P.MP, P.grouped != 0, stream); break;

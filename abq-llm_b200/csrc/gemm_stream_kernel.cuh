@@ -28,6 +28,7 @@
 #pragma once
 #include <cuda.h>
 #include <cstring>
+#include <type_traits>
 
 #include "abq_common.cuh"
 #include "abq_kernels.h"
@@ -39,6 +40,14 @@ constexpr int kStreamMaxWarps = 16;
 constexpr int kStreamMaxRing = 8;
 constexpr uint32_t kZeroMask = 0x1fffu; // low mantissa bits of the packed (scale, zero) word that hold the zero point
 
+// Fused all-reduce (abq_fused_allreduce): every rank's receive buffer and flag array as mapped here.
+struct StreamAllreduce {
+    int world, rank, rows_cap, row0; // row0: first token row of this launch within the receive buffers
+    __half *recv[8];
+    uint32_t *flags[8];
+    uint32_t *counter;
+};
+
 struct StreamArgs {
     int M, N, K;
     int tiles;           // ceil(N / 16)
@@ -49,6 +58,7 @@ struct StreamArgs {
     int ctas_per_slice;
     int cu;              // units per chunk (multiple of GS)
     int ring;            // chunks per warp ring
+    int prefill;         // chunks per warp requested before the wait on the previous kernel (the rest right after it)
     int nw;              // warps per CTA
     const uint8_t *Wp;   // weights in stream layout
     const uint32_t *X;   // activation planes [x_bits][rows][K/32], first row of this launch (fp16 [rows][K] with x_qscale)
@@ -64,7 +74,23 @@ struct StreamArgs {
     const __half *C;
     int out_dtype, scale_mode, w_signed;
     int *status;
+    StreamAllreduce ar; // world <= 1: none
+#ifdef ABQ_STREAM_TRACE
+    unsigned long long *trace; // development builds only: per-CTA time stamps (see trace_mark)
+#endif
 };
+
+#ifdef ABQ_STREAM_TRACE
+__shared__ unsigned trace_slot_g;
+#define ABQ_TRACE(i) trace_mark(a, trace_slot, i)
+__device__ __forceinline__ void trace_mark(const StreamArgs &a, unsigned slot, int i)
+{
+    if (a.trace && threadIdx.x == 0)
+        a.trace[16 + (size_t)slot * 16 + i] = globaltimer_ns();
+}
+#else
+#define ABQ_TRACE(i)
+#endif
 
 // ------------------------------------------------------------------------------------------ formats
 // StreamFormat<Q>: how the codes of one lane (rows g and g + 8, 32 features each) are packed, and how they come back.
@@ -286,77 +312,193 @@ __global__ void __launch_bounds__(256) prepare_stream_kernel(const uint32_t *__r
 }
 
 // ------------------------------------------------------------------------------------------ activation records
-// Records of units [u_first, u_first + n_units) of this CTA's K range, zero-padded to n_pad units and MR token rows:
-// rec[(ul * MR + m) * 128 + t * 32 + {0, 16} ^ ((m & 1) << 4)] = the lane-t halves (registers 0..3 and 4..7 of x_bytes)
-// of token m, and sums[ul * MR + m] = the sum of its 128 codes.
-template <int P>
-__device__ __forceinline__ void stream_record_item(const StreamArgs &a, int m, int kw, uint32_t (&r)[8])
+// Store one expanded item (token m, 32-feature run t of unit ul) and, from lane t == 0 of each group of four, the unit's code sum.
+__device__ __forceinline__ void stream_store_item(uint8_t *rec_base, int *sums, int MR, int ul, int m, int t, const uint32_t (&r)[8], int sum, bool mine)
 {
-    uint32_t p[P];
-    const uint32_t *src = a.X + (size_t)m * (a.K >> 5) + kw;
-#pragma unroll
-    for (int b = 0; b < P; ++b)
-        p[b] = __ldg(src + b * a.x_plane_words);
-    x_bytes<P>(p, a.x_signed != 0, r);
+    // the four 32-feature runs of a unit sit in four consecutive lanes (the item count per token is a multiple of 4)
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (!mine)
+        return;
+    uint8_t *dst = rec_base + ((size_t)ul * MR + m) * 128 + t * 32;
+    const int swz = (m & 1) << 4;
+    *reinterpret_cast<uint4 *>(dst + swz) = make_uint4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<uint4 *>(dst + (16 ^ swz)) = make_uint4(r[4], r[5], r[6], r[7]);
+    if (t == 0)
+        sums[ul * MR + m] = sum;
 }
 
-__device__ __forceinline__ void stream_build_records(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR)
+__device__ __forceinline__ int stream_code_sum(const uint32_t (&r)[8], bool x_signed)
+{
+    if (x_signed) {
+        int sum = 0;
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            sum = __dp4a((int)r[s], 0x01010101, sum);
+        return sum;
+    }
+    unsigned usum = 0;
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+        usum = __dp4a(r[s], 0x01010101u, usum);
+    return (int)usum;
+}
+
+__device__ __forceinline__ void prefetch_l2(const void *p)
+{
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// The build runs between "the previous kernel is complete" and the first MMA, so it is kept short: items are dealt to all
+// threads of the CTA (index arithmetic by a multiply-high, no division), a thread first requests the plane words of all B
+// items of a batch and then expands them (one round trip to L2 per batch, not per item), and the code is instantiated
+// per activation width so that only the path taken is ever fetched.
+// It is preceded, BEFORE the wait on the previous kernel, by a pass over the same items (WARM) that touches no activation
+// value: it asks for the lines the build will read to be brought into L2 -- which also walks the page table for them, the
+// larger part of a first access after gigabytes of weights have gone through the TLBs -- and writes the zero padding
+// (token rows and units beyond the real ones), so that the build itself only handles real items.
+template <int P, int B, bool WARM>
+__device__ __forceinline__ void stream_records_planes(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR)
 {
     const int words = n_pad * 4;
     const int items = MR * words;
-    const __half hscale = a.x_qscale ? __float2half(__ldg(a.x_qscale)) : __half();
-    for (int base = 0; base < items; base += blockDim.x) { // every lane of a warp takes every trip: the shuffles below need all of them
-        const int idx = min(base + (int)threadIdx.x, items - 1);
-        const bool mine = base + (int)threadIdx.x < items;
-        const int m = idx / words, kwl = idx - m * words;
-        const int ul = kwl >> 2, t = kwl & 3;
+    const uint32_t magic = 0xffffffffu / (uint32_t)words + 1u; // idx / words == umulhi(idx, magic) for idx * words < 2^32
+    const int KW = a.K >> 5;
+    for (int base = 0; base < items; base += blockDim.x * B) { // every lane of a warp takes every trip (shuffles inside)
+        uint32_t pl[B][P];
+        int mm[B], kk[B];
+        bool live[B];
+#pragma unroll
+        for (int i = 0; i < B; ++i) {
+            const int idx = base + i * (int)blockDim.x + (int)threadIdx.x;
+            mm[i] = (int)__umulhi((uint32_t)idx, magic);
+            kk[i] = idx - mm[i] * words;
+            live[i] = idx < items && mm[i] < a.M && (kk[i] >> 2) < n_units;
+            const uint32_t *src = a.X + (size_t)mm[i] * KW + u_first * 4 + kk[i];
+            if (WARM) {
+                if (live[i] && (kk[i] & 31) == 0) { // one request per 128-byte line of every plane row
+#pragma unroll
+                    for (int b = 0; b < P; ++b)
+                        prefetch_l2(src + b * a.x_plane_words);
+                }
+            } else {
+#pragma unroll
+                for (int b = 0; b < P; ++b)
+                    pl[i][b] = live[i] ? __ldg(src + b * a.x_plane_words) : 0u;
+            }
+        }
+#ifdef ABQ_STREAM_TRACE
+        if (!WARM && a.trace && threadIdx.x == 0 && base == 0)
+            a.trace[16 + (size_t)(*(volatile unsigned *)&trace_slot_g) * 16 + 7] = globaltimer_ns() + (pl[0][P - 1] & 0u); // after the loads have landed
+#endif
+#pragma unroll
+        for (int i = 0; i < B; ++i) {
+            const int idx = base + i * (int)blockDim.x + (int)threadIdx.x;
+            uint32_t r[8];
+            int sum = 0;
+            if (WARM) {
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                    r[s] = 0;
+                stream_store_item(rec_base, sums, MR, kk[i] >> 2, mm[i], kk[i] & 3, r, 0, idx < items && !live[i]);
+            } else {
+                if (live[i]) {
+                    x_bytes<P>(pl[i], a.x_signed != 0, r);
+                    sum = stream_code_sum(r, a.x_signed != 0);
+                } else {
+#pragma unroll
+                    for (int s = 0; s < 8; ++s)
+                        r[s] = 0;
+                }
+                stream_store_item(rec_base, sums, MR, kk[i] >> 2, mm[i], kk[i] & 3, r, sum, live[i]);
+            }
+        }
+    }
+}
+
+template <bool WARM>
+__device__ __forceinline__ void stream_records_half(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR)
+{
+    const int words = n_pad * 4;
+    const int items = MR * words;
+    const uint32_t magic = 0xffffffffu / (uint32_t)words + 1u;
+    const __half hscale = WARM ? __half() : __float2half(__ldg(a.x_qscale));
+    for (int base = 0; base < items; base += blockDim.x) {
+        const int idx = base + (int)threadIdx.x;
+        const int m = (int)__umulhi((uint32_t)idx, magic), kwl = idx - m * words;
+        const bool live = idx < items && m < a.M && (kwl >> 2) < n_units;
+        const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.X) + (size_t)m * a.K + (size_t)(u_first * 4 + kwl) * 32);
         uint32_t r[8];
         int sum = 0;
-        if (mine && m < a.M && ul < n_units) {
-            const int kw = u_first * 4 + kwl;
-            if (a.x_qscale) {
-                x_bytes_from_half(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.X) + (size_t)m * a.K + (size_t)kw * 32), hscale,
-                                  a.x_bits, r);
-            } else {
-                switch (a.x_bits) {
-                case 1: stream_record_item<1>(a, m, kw, r); break;
-                case 2: stream_record_item<2>(a, m, kw, r); break;
-                case 3: stream_record_item<3>(a, m, kw, r); break;
-                case 4: stream_record_item<4>(a, m, kw, r); break;
-                case 5: stream_record_item<5>(a, m, kw, r); break;
-                case 6: stream_record_item<6>(a, m, kw, r); break;
-                case 7: stream_record_item<7>(a, m, kw, r); break;
-                default: stream_record_item<8>(a, m, kw, r); break;
-                }
-            }
-            if (a.x_signed) {
 #pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    sum = __dp4a((int)r[s], 0x01010101, sum);
-            } else {
-                unsigned usum = 0;
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    usum = __dp4a(r[s], 0x01010101u, usum);
-                sum = (int)usum;
-            }
+        for (int s = 0; s < 8; ++s)
+            r[s] = 0;
+        if (WARM) {
+            if (live && (kwl & 1) == 0)
+                prefetch_l2(src); // 64 bytes per item: one request per 128-byte line
+            if (live && idx == 0)
+                prefetch_l2(a.x_qscale);
+            stream_store_item(rec_base, sums, MR, kwl >> 2, m, kwl & 3, r, 0, idx < items && !live);
         } else {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-                r[s] = 0;
+            if (live) {
+                x_bytes_from_half(src, hscale, a.x_bits, r);
+                sum = stream_code_sum(r, true);
+            }
+            stream_store_item(rec_base, sums, MR, kwl >> 2, m, kwl & 3, r, sum, live);
         }
-        // the four 32-feature runs of a unit sit in four consecutive lanes (words is a multiple of 4)
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (!mine)
-            continue;
-        uint8_t *dst = rec_base + ((size_t)ul * MR + m) * 128 + t * 32;
-        const int swz = (m & 1) << 4;
-        *reinterpret_cast<uint4 *>(dst + swz) = make_uint4(r[0], r[1], r[2], r[3]);
-        *reinterpret_cast<uint4 *>(dst + (16 ^ swz)) = make_uint4(r[4], r[5], r[6], r[7]);
-        if (t == 0)
-            sums[ul * MR + m] = sum;
     }
+}
+
+// Records of units [u_first, u_first + n_units) of this CTA's K range, zero-padded to n_pad units and MR token rows:
+// rec[(ul * MR + m) * 128 + t * 32 + {0, 16} ^ ((m & 1) << 4)] = the lane-t halves (registers 0..3 and 4..7 of x_bytes)
+// of token m, and sums[ul * MR + m] = the sum of its 128 codes.  warm: the pass before the dependency wait (see above).
+// One copy of this code per compile unit.
+static __device__ __noinline__ void stream_build_records(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR,
+                                                         bool warm)
+{
+    if (a.x_qscale) {
+        if (warm)
+            stream_records_half<true>(a, rec_base, sums, u_first, n_units, n_pad, MR);
+        else
+            stream_records_half<false>(a, rec_base, sums, u_first, n_units, n_pad, MR);
+        return;
+    }
+    if (warm) { // no arithmetic on activation values: one instantiation serves all widths
+        switch (a.x_bits) {
+        case 1: stream_records_planes<1, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        case 2: stream_records_planes<2, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        case 3: stream_records_planes<3, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        case 4: stream_records_planes<4, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        case 5: stream_records_planes<5, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        case 6: stream_records_planes<6, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        case 7: stream_records_planes<7, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        default: stream_records_planes<8, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
+        }
+        return;
+    }
+    const bool one = MR * n_pad * 4 <= (int)blockDim.x; // one item per thread at most: no batching needed
+#define ABQ_RECORDS_CASE(P)                                                                                      \
+    case P:                                                                                                      \
+        if (one)                                                                                                 \
+            stream_records_planes<P, 1, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);                  \
+        else                                                                                                     \
+            stream_records_planes<P, 4, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);                  \
+        break;
+    switch (a.x_bits) {
+        ABQ_RECORDS_CASE(1)
+        ABQ_RECORDS_CASE(2)
+        ABQ_RECORDS_CASE(3)
+        ABQ_RECORDS_CASE(4)
+        ABQ_RECORDS_CASE(5)
+        ABQ_RECORDS_CASE(6)
+        ABQ_RECORDS_CASE(7)
+    default:
+        if (one)
+            stream_records_planes<8, 1, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);
+        else
+            stream_records_planes<8, 4, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);
+    }
+#undef ABQ_RECORDS_CASE
 }
 
 // D(16x8, s32) = A(16x32, u8) * B(32x8, s8) + 0: first step of an accumulation (saves clearing the accumulators)
@@ -407,6 +549,18 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int nw = a.nw;
+#ifdef ABQ_STREAM_TRACE
+    __shared__ unsigned trace_slot_s;
+    if (a.trace && threadIdx.x == 0) {
+        trace_slot_s = (unsigned)atomicAdd(a.trace, 1ull);
+        trace_slot_g = trace_slot_s;
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.trace[16 + (size_t)trace_slot_s * 16 + 15] = ((unsigned long long)smid << 32) | blockIdx.x;
+    }
+    const unsigned trace_slot = a.trace && threadIdx.x == 0 ? trace_slot_s : 0;
+#endif
+    ABQ_TRACE(0);
     const int s = blockIdx.x / a.ctas_per_slice;
     const int cb = blockIdx.x - s * a.ctas_per_slice;
     const int r_begin = (int)((long long)cb * a.tiles / a.ctas_per_slice);
@@ -439,8 +593,13 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     pdl_launch_dependents();
 
     // ---- this warp's chunks: [c_begin, c_end) of the CTA's T * cpt chunks (tile-major)
-    const int c_begin = (int)((long long)warp * total_chunks / nw);
-    const int c_end = (int)((long long)(warp + 1) * total_chunks / nw);
+    __shared__ int chunk_bound[kStreamMaxWarps + 1];
+    // (the same share for every warp, the first warps served first: the warps that hold a share of a tile are then consecutive)
+    const int chunks_per_warp = (total_chunks + nw - 1) / nw;
+    if ((int)threadIdx.x <= nw)
+        chunk_bound[threadIdx.x] = min((int)threadIdx.x * chunks_per_warp, total_chunks); // read again after the barriers below
+    const int c_begin = min(warp * chunks_per_warp, total_chunks);
+    const int c_end = min((warp + 1) * chunks_per_warp, total_chunks);
     uint8_t *my_ring = ring_base + (size_t)warp * a.ring * chunk_bytes;
 
     // request side (lane 0): cursor over the chunks in consumption order
@@ -464,14 +623,62 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
         }
     };
     if (lane == 0) {
-        for (int slot = 0; slot < a.ring && q_left > 0; ++slot)
+        for (int slot = 0; slot < a.prefill && q_left > 0; ++slot)
             issue(slot); // weights never depend on an earlier kernel: request them before the dependency wait
     }
 
+    // ---- everything that does not depend on the previous kernel happens before the wait on it, where it costs nothing:
+    // which warps hold a share of which tile (for the final reduction), and which output this thread finishes first
+    __shared__ unsigned short tile_warps[64]; // [tile of this CTA] -> first warp | (last warp + 1) << 8
+    __syncthreads();                          // chunk_bound is written
+    for (int tl = threadIdx.x; tl < T && tl < 64; tl += blockDim.x) {
+        const int lo = tl * cpt, hi = lo + cpt;
+        int w_lo = nw, w_hi = 0;
+        for (int w = 0; w < nw; ++w) {
+            if (chunk_bound[w] < chunk_bound[w + 1] && chunk_bound[w] < hi && chunk_bound[w + 1] > lo) {
+                w_lo = min(w_lo, w);
+                w_hi = w + 1;
+            }
+        }
+        tile_warps[tl] = (unsigned short)(min(w_lo, w_hi) | (w_hi << 8));
+    }
+    const int per_tile = a.M * 16; // outputs of a tile; output idx of the CTA is tile idx / per_tile, token (idx % per_tile) / 16, row idx % 16
+    const int first_tl = (int)threadIdx.x / per_tile, first_i = (int)threadIdx.x - first_tl * per_tile;
+    // Nothing of the previous kernel's output is touched yet: bring the activations' lines (and page-table entries) towards
+    // L2, write the records' zero padding, and ask for the lines this CTA will store its results to.
+    stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, true);
+    {
+        const size_t esz = a.out_dtype == ABQ_OUT_INT32 ? 4 : 2;
+        for (int i = threadIdx.x; i < a.M; i += blockDim.x)
+            prefetch_l2(reinterpret_cast<const uint8_t *>(a.D) + ((size_t)i * a.N + (size_t)r_begin * 16) * esz);
+    }
     // ---- activations: everything below may depend on the kernel launched just before
+    ABQ_TRACE(1);
     pdl_wait_prior_grid();
-    stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR);
+    ABQ_TRACE(2);
+#ifdef ABQ_STREAM_TRACE
+    if (a.trace && threadIdx.x == 0) { // latency of one load right after the wait: a line every CTA reads, then a line only this CTA reads
+        uint32_t v, v2;
+        const unsigned long long t0 = globaltimer_ns();
+        asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(a.X) : "memory");
+        const unsigned long long t1 = globaltimer_ns() + (v & 0u);
+        asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v2) : "l"(a.Wp + (size_t)blockIdx.x * 8192 + 4096 + (t1 & 0u)) : "memory");
+        const unsigned long long t2 = globaltimer_ns() + (v2 & 0u);
+        a.trace[16 + (size_t)trace_slot * 16 + 9] = t1 - t0;
+        a.trace[16 + (size_t)trace_slot * 16 + 10] = t2 - t1;
+    }
+#endif
+    if (lane == 0) {
+        for (int slot = a.prefill; slot < a.ring && q_left > 0; ++slot)
+            issue(slot);
+    }
+    __shared__ uint32_t ar_epoch;
+    if (a.ar.world > 1 && threadIdx.x == 0) // (only the last CTA of a launch advances the counter, after all have read it)
+        ar_epoch = *reinterpret_cast<volatile uint32_t *>(a.ar.counter) + 1u;
+    stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, false);
+    ABQ_TRACE(8);
     __syncthreads();
+    ABQ_TRACE(3);
 
     // lane constants of the B fragment fetch: column c = g holds token (g % MP) of unit (g / MP) of a block
     const int my_m = g & (MP - 1);
@@ -486,7 +693,7 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     int tile_l = cpt > 0 ? c_begin / cpt : 0; // tile (local) and chunk within it of the chunk being consumed
     int cit = cpt > 0 ? c_begin - tile_l * cpt : 0;
 
-    int acc[F::kSets][MT][4];
+    int acc_run[F::kSets][MT][4]; // without per-group scales: integer sums over the whole K range of a tile
     float facc[MT][4];
     int xs[MT][2];
 #pragma unroll
@@ -495,7 +702,7 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
         for (int e = 0; e < 4; ++e) {
 #pragma unroll
             for (int k = 0; k < F::kSets; ++k)
-                acc[k][mt][e] = 0;
+                acc_run[k][mt][e] = 0;
             facc[mt][e] = 0.f;
         }
         xs[mt][0] = xs[mt][1] = 0;
@@ -513,42 +720,59 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
         const uint8_t *stage = my_ring + (size_t)slot * chunk_bytes;
         const int uf = cit * a.cu;              // first unit of the chunk within this CTA's K range
         const int nu = min(a.cu, n_units - uf); // units in the chunk
+        // (two blocks per trip: with accumulators of its own, a block's MMAs can run under the fold of the block before it)
+#pragma unroll 2
         for (int ub = 0; ub < nu; ub += GS) {
             const uint8_t *blk = stage + (size_t)ub * a.unit_bytes;
             const int left = nu - ub; // units of this block that exist
+            int acc_block[F::kSets][MT][4]; // GROUPED: the block's own accumulators (its first MMA step overwrites them)
+            int(&acc)[F::kSets][MT][4] = GROUPED ? acc_block : acc_run;
+            // A whole block runs without a branch between its units, so that the compiler overlaps the loads of one unit
+            // with the arithmetic of another; only the last block of a tile's K range may be short.
+            auto run_block = [&](auto whole_tag) {
+                constexpr bool kWhole = decltype(whole_tag)::value;
 #pragma unroll
-            for (int ui = 0; ui < GS; ++ui) {
-                if (GS == 1 || ui < left) {
-                    const uint8_t *unit = blk + ui * a.unit_bytes;
-                    uint32_t R[4][4];
-                    F::expand(unit, lane, R);
-                    const uint8_t *rec = rec_base + (size_t)(uf + ub + ui) * MR * 128;
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const uint8_t *bp = (GS == 1 || my_slot == ui) ? rec + mt * 1024 + rec_lane : zero_base;
-                        const uint4 blo = *reinterpret_cast<const uint4 *>(bp + swz);
-                        const uint4 bhi = *reinterpret_cast<const uint4 *>(bp + (16 ^ swz));
-                        const uint32_t b[8] = { blo.x, blo.y, blo.z, blo.w, bhi.x, bhi.y, bhi.z, bhi.w };
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            // GROUPED: the first step of every set in a block starts from zero
-                            const bool first = GROUPED && ui == 0 && stream_first_in_set<F>(j);
-                            if (first)
-                                mma_u8s8_first(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
-                            else
-                                mma_u8<false>(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
-                        }
-                    }
-                    if (!GROUPED) {
+                for (int ui = 0; ui < GS; ++ui) {
+                    if (kWhole || ui < left) {
+                        const uint8_t *unit = blk + ui * a.unit_bytes;
+                        uint32_t R[4][4];
+                        F::expand(unit, lane, R);
+                        const uint8_t *rec = rec_base + (size_t)(uf + ub + ui) * MR * 128;
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
-                            const int2 sv = *reinterpret_cast<const int2 *>(sums + (uf + ub + ui) * MR + 8 * mt + 2 * t);
-                            xs[mt][0] += sv.x;
-                            xs[mt][1] += sv.y;
+                            const uint8_t *bp = (GS == 1 || my_slot == ui) ? rec + mt * 1024 + rec_lane : zero_base;
+                            const uint4 blo = *reinterpret_cast<const uint4 *>(bp + swz);
+                            const uint4 bhi = *reinterpret_cast<const uint4 *>(bp + (16 ^ swz));
+                            const uint32_t b[8] = { blo.x, blo.y, blo.z, blo.w, bhi.x, bhi.y, bhi.z, bhi.w };
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                // GROUPED: the first step of every set in a block starts from zero
+                                const bool first = GROUPED && ui == 0 && stream_first_in_set<F>(j);
+                                if (first)
+                                    mma_u8s8_first(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
+                                else
+                                    mma_u8<false>(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
+                            }
+                        }
+                        if (!GROUPED) {
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const int2 sv = *reinterpret_cast<const int2 *>(sums + (uf + ub + ui) * MR + 8 * mt + 2 * t);
+                                xs[mt][0] += sv.x;
+                                xs[mt][1] += sv.y;
+                            }
                         }
                     }
                 }
-            }
+            };
+#ifdef ABQ_STREAM_BRANCHY // development builds only: every unit behind its own branch, for comparison
+            run_block(std::false_type{});
+#else
+            if (GS == 1 || left >= GS)
+                run_block(std::true_type{});
+            else
+                run_block(std::false_type{});
+#endif
             if (GROUPED) {
                 // fold the block: column 2 t + j of the accumulators is token (col % MP) of unit ub + col / MP
                 const int ul = uf + ub; // first unit of the block within the CTA's K range (a multiple of GS)
@@ -609,18 +833,36 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
                         const int n = (r_begin + tile_l) * 16 + g + 8 * (e >> 1);
                         if (a.scale_mode == ABQ_SCALE_CHANNEL && a.w_zero && n < a.N)
                             z += a.w_zero[n];
-                        int x = acc[0][mt][e];
+                        int x = acc_run[0][mt][e];
                         if (F::kSets == 2)
-                            x += acc[F::kSets - 1][mt][e] >> F::kShift;
+                            x += acc_run[F::kSets - 1][mt][e] >> F::kShift;
                         v[e] = x - z * xs[mt][e & 1];
 #pragma unroll
                         for (int k = 0; k < F::kSets; ++k)
-                            acc[k][mt][e] = 0;
+                            acc_run[k][mt][e] = 0;
                     }
                 }
                 xs[mt][0] = xs[mt][1] = 0;
-                *reinterpret_cast<int2 *>(dst + mt * 128 + g * 8 + 2 * t) = make_int2(v[0], v[1]);
-                *reinterpret_cast<int2 *>(dst + mt * 128 + (g + 8) * 8 + 2 * t) = make_int2(v[2], v[3]);
+                if (GS > 1) {
+                    // columns c and c' with c % MP == c' % MP are the same token seen through different units: add them here,
+                    // in the warp, so that the tile's partial is [16 rows][MP tokens] (columns 0 .. MP - 1)
+                    float f[4] = { __int_as_float(v[0]), __int_as_float(v[1]), __int_as_float(v[2]), __int_as_float(v[3]) };
+                    if (MP == 1) {
+                        f[0] += f[1];
+                        f[2] += f[3];
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (MP <= 2)
+                            f[e] += __shfl_xor_sync(0xffffffffu, f[e], 1);
+                        f[e] += __shfl_xor_sync(0xffffffffu, f[e], 2);
+                        v[e] = __float_as_int(f[e]);
+                    }
+                }
+                if (GS == 1 || 2 * t < MP || t == 0) {
+                    *reinterpret_cast<int2 *>(dst + mt * 128 + g * 8 + 2 * t) = make_int2(v[0], v[1]);
+                    *reinterpret_cast<int2 *>(dst + mt * 128 + (g + 8) * 8 + 2 * t) = make_int2(v[2], v[3]);
+                }
             }
         }
         if (++cit == cpt) {
@@ -634,26 +876,21 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
         for (int i = 0; i < a.ring; ++i)
             mbar_wait_bounded(&full[i], 0, nullptr, 0);
     }
+    ABQ_TRACE(4);
     __syncthreads();
+    ABQ_TRACE(5);
 
     // ---- the CTA's tiles: add the warps' partial sums in warp order, finish, store.  Thread per (tile, token, row).
-    const int outs = T * a.M * 16;
-    auto tile_sum = [&](int tl, int m, int row, bool &any) -> int {
+    auto tile_sum = [&](int tl, int m, int row) -> int {
         int isum = 0;
         float fsum = 0.f;
-        for (int w = 0; w < nw; ++w) {
-            const int wb = (int)((long long)w * total_chunks / nw), we = (int)((long long)(w + 1) * total_chunks / nw);
-            if (wb < we && wb < (tl + 1) * cpt && we > tl * cpt) {
-                const int *src = red + (size_t)(w + tl) * MT * 128 + (m >> 3) * 128 + row * 8;
-                if (GROUPED) {
-#pragma unroll
-                    for (int sl = 0; sl < GS; ++sl)
-                        fsum += __int_as_float(src[sl * MP + (m & (MP - 1))]);
-                } else {
-                    isum += src[m & 7];
-                }
-                any = true;
-            }
+        const int w_lo = tile_warps[tl] & 0xff, w_hi = tile_warps[tl] >> 8; // the warps that hold a share of this tile
+        for (int w = w_lo; w < w_hi; ++w) {
+            const int v = red[(size_t)(w + tl) * MT * 128 + (m >> 3) * 128 + row * 8 + (m & 7)];
+            if (GROUPED)
+                fsum += __int_as_float(v);
+            else
+                isum += v;
         }
         return GROUPED ? __float_as_int(fsum) : isum;
     };
@@ -677,49 +914,119 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
             reinterpret_cast<__half *>(a.D)[o] = h;
         }
     };
-    if (a.slices == 1) {
-        for (int idx = threadIdx.x; idx < outs; idx += blockDim.x) {
-            const int tl = idx / (a.M * 16), rem = idx - tl * a.M * 16;
-            const int m = rem >> 4, row = rem & 15;
-            bool any = false;
-            const int v = tile_sum(tl, m, row, any);
-            finish(r_begin + tl, m, row, v);
+    if (a.slices == 1 && a.ar.world > 1) {
+        // ---- all-reduce over the ranks, fused: push this CTA's partial tiles to every rank, flag them, wait for the
+        // other ranks' flags of the same tiles, add what they pushed (rank order, fp32).
+        const uint32_t epoch = ar_epoch;
+        const int W = a.ar.world, par = (int)(epoch & 1u);
+        auto half_of = [&](int r, int m, int row, int v) -> __half {
+            const int n = r * 16 + row;
+            float f = GROUPED ? __int_as_float(v) : (float)v * (n < a.N ? __half2float(ld_half(a.w_scale + n)) : 0.f);
+            if (a.x_scale)
+                f *= a.x_scale[m];
+            return __float2half_rn(f);
+        };
+        for (int idx = threadIdx.x; idx < T * per_tile; idx += blockDim.x) {
+            const int tl = idx == (int)threadIdx.x ? first_tl : idx / per_tile, i = idx == (int)threadIdx.x ? first_i : idx - tl * per_tile;
+            const int m = i >> 4, row = i & 15, n = (r_begin + tl) * 16 + row;
+            if (n < a.N) {
+                const __half h = half_of(r_begin + tl, m, row, tile_sum(tl, m, row));
+                const size_t at = ((size_t)(par * W + a.ar.rank) * a.ar.rows_cap + a.ar.row0 + m) * a.N + n;
+                for (int p = 0; p < W; ++p)
+                    a.ar.recv[p][at] = h; // 16 consecutive threads write the 32 bytes of a token row of the tile
+            }
         }
+        __threadfence_system(); // this thread's pushes are visible system-wide before ...
+        __syncthreads();        // ... any flag of this CTA goes out
+        bool arrived = true;
+        for (int i = threadIdx.x; i < W * T; i += blockDim.x) {
+            const int p = i / T, tl = i - p * T;
+            if (p == a.ar.rank)
+                continue;
+            uint32_t *theirs = a.ar.flags[p] + (size_t)(par * W + a.ar.rank) * a.tiles + r_begin + tl;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+            const uint32_t *mine = a.ar.flags[a.ar.rank] + (size_t)(par * W + p) * a.tiles + r_begin + tl;
+            const unsigned long long t0 = globaltimer_ns();
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                if (v == epoch)
+                    break;
+                if (globaltimer_ns() - t0 > kWaitLimitNs) { // the peer never arrived: record it and carry on (the sum is then void)
+                    if (a.status)
+                        atomicOr(a.status, STATUS_TIMEOUT_PIPE);
+                    arrived = false;
+                    break;
+                }
+            }
+        }
+        (void)arrived;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < T * per_tile; idx += blockDim.x) {
+            const int tl = idx / per_tile, i = idx - tl * per_tile;
+            const int m = i >> 4, row = i & 15, n = (r_begin + tl) * 16 + row;
+            if (n >= a.N)
+                continue;
+            float f = 0.f;
+            for (int p = 0; p < W; ++p) {
+                const size_t at = ((size_t)(par * W + p) * a.ar.rows_cap + a.ar.row0 + m) * a.N + n;
+                // written by another GPU into this one's memory: read past the L1 (no stale line)
+                f += __half2float(__ushort_as_half(__ldcv(reinterpret_cast<const unsigned short *>(a.ar.recv[a.ar.rank] + at))));
+            }
+            reinterpret_cast<__half *>(a.D)[(size_t)m * a.N + n] = __float2half_rn(f);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) { // the last CTA of the launch advances the call counter
+            const uint32_t done = atomicAdd(a.ar.counter + 1, 1u);
+            if (done == gridDim.x - 1) {
+                a.ar.counter[1] = 0;
+                __threadfence();
+                a.ar.counter[0] = epoch;
+            }
+        }
+        ABQ_TRACE(6);
+        return;
+    }
+    if (a.slices == 1) {
+        for (int idx = threadIdx.x; idx < T * per_tile; idx += blockDim.x) { // all threads busy, whatever the token count
+            const int tl = idx == (int)threadIdx.x ? first_tl : idx / per_tile, i = idx == (int)threadIdx.x ? first_i : idx - tl * per_tile;
+            finish(r_begin + tl, i >> 4, i & 15, tile_sum(tl, i >> 4, i & 15));
+        }
+        ABQ_TRACE(6);
         return;
     }
     // ---- K split over CTAs as well: a workspace slot per slice, the CTA arriving last at a tile's counter adds the
     // slots in slice order (the result does not depend on who finishes)
-    for (int idx = threadIdx.x; idx < outs; idx += blockDim.x) {
-        const int tl = idx / (a.M * 16), rem = idx - tl * a.M * 16;
-        bool any = false;
-        const int v = tile_sum(tl, rem >> 4, rem & 15, any);
-        a.partials[((size_t)s * a.tiles + r_begin + tl) * (size_t)a.M * 16 + rem] = v;
+    for (int idx = threadIdx.x; idx < T * per_tile; idx += blockDim.x) {
+        const int tl = idx / per_tile, i = idx - tl * per_tile;
+        a.partials[((size_t)s * a.tiles + r_begin + tl) * (size_t)per_tile + i] = tile_sum(tl, i >> 4, i & 15);
     }
     __threadfence();
     __syncthreads();
     int *last = red; // reuse: one flag per tile of this CTA
-    if ((int)threadIdx.x < T) {
-        const int old = atomicAdd(a.counters + r_begin + threadIdx.x, 1);
-        last[threadIdx.x] = old == a.slices - 1;
+    for (int tl = threadIdx.x; tl < T; tl += blockDim.x) {
+        const int old = atomicAdd(a.counters + r_begin + tl, 1);
+        last[tl] = old == a.slices - 1;
         if (old == a.slices - 1)
-            a.counters[r_begin + threadIdx.x] = 0; // leave the counter ready for the next launch
+            a.counters[r_begin + tl] = 0; // leave the counter ready for the next launch
     }
     __syncthreads();
     __threadfence();
-    for (int idx = threadIdx.x; idx < outs; idx += blockDim.x) {
-        const int tl = idx / (a.M * 16), rem = idx - tl * a.M * 16;
+    for (int tl = 0; tl < T; ++tl) {
         if (!last[tl])
             continue;
-        int isum = 0;
-        float fsum = 0.f;
-        for (int sl = 0; sl < a.slices; ++sl) {
-            const int pv = __ldcg(a.partials + ((size_t)sl * a.tiles + r_begin + tl) * (size_t)a.M * 16 + rem);
-            if (GROUPED)
-                fsum += __int_as_float(pv);
-            else
-                isum += pv;
+        for (int i = threadIdx.x; i < per_tile; i += blockDim.x) {
+            int isum = 0;
+            float fsum = 0.f;
+            for (int sl = 0; sl < a.slices; ++sl) {
+                const int pv = __ldcg(a.partials + ((size_t)sl * a.tiles + r_begin + tl) * (size_t)per_tile + i);
+                if (GROUPED)
+                    fsum += __int_as_float(pv);
+                else
+                    isum += pv;
+            }
+            finish(r_begin + tl, i >> 4, i & 15, GROUPED ? __float_as_int(fsum) : isum);
         }
-        finish(r_begin + tl, rem >> 4, rem & 15, GROUPED ? __float_as_int(fsum) : isum);
     }
 }
 

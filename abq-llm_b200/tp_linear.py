@@ -118,10 +118,13 @@ class TensorParallelBlockLinears:
 
 class AbqLinear:
     """One sharded quantized linear layer on the GPU: one GEMM call that quantises the fp16 activations with a static
-    scale (ABQ_FLAG_X_HALF) and writes fp16 through its fused dequantisation (per-channel or per-group scale and zero point, per-token activation scale)."""
+    scale (ABQ_FLAG_X_HALF) and writes fp16 through its fused dequantisation (per-channel or per-group scale and zero
+    point, per-token activation scale).  The weights are re-ordered once at construction into the decode kernel's
+    prepared form (ABQ_FLAG_WEIGHTS_PREPARED); a row-parallel layer on several ranks can have the sum over the ranks
+    done inside the GEMM (``fused_reduce``: abq_fused_allreduce over symmetric memory)."""
 
     def __init__(self, abq, torch, codes, scale, zero, w_bits: int, group: int, x_bits: int = 8, x_scale: float = 16.0,
-                 max_tokens: int = 64, make_out=None):
+                 max_tokens: int = 64, make_out=None, fused_reduce=None, status=None):
         self.abq, self.torch = abq, torch
         self.make_out = make_out  # row-parallel layers: output buffers that the other ranks can read
         self.out_features, self.in_features = codes.shape
@@ -135,7 +138,26 @@ class AbqLinear:
         self.max_tokens = max_tokens
         self.inv = torch.full((max_tokens,), 1.0 / x_scale, dtype=torch.float32, device="cuda")
         self.work = torch.empty(max(256, abq.gemm_workspace_bytes(max_tokens, N, K, x_bits, w_bits)), dtype=torch.uint8, device="cuda")
+        self.status = status
         self.plans = {}
+        self.prepared = None
+        self.prepared_done = False
+        self.fused = None
+        if fused_reduce is not None:  # (dist, world, rank): receive buffers + flags of all ranks in one symmetric allocation
+            import torch.distributed._symmetric_memory as symm
+            dist, world, rank = fused_reduce
+            tiles = (N + 15) // 16
+            recv_bytes = 2 * world * max_tokens * N * 2
+            flag_bytes = 2 * world * tiles * 4
+            buf = symm.empty(((recv_bytes + 255) // 256 * 256 + flag_bytes,), dtype=torch.uint8, device="cuda")
+            buf.zero_()
+            h = symm.rendezvous(buf, dist.group.WORLD)
+            torch.cuda.synchronize()
+            dist.barrier()  # every rank's flags are zero before anybody's first GEMM
+            base = [int(p) for p in h.buffer_ptrs]
+            counter = torch.zeros(2, dtype=torch.int32, device="cuda")
+            self.fused = dict(buf=buf, handle=h, counter=counter,
+                              desc=abq.make_fused_allreduce(world, rank, base, [b + (recv_bytes + 255) // 256 * 256 for b in base], counter, max_tokens))
 
     def _plan(self, M):
         """Plan and output buffer per token count, made on first use (outside stream capture: planning may touch the
@@ -146,12 +168,34 @@ class AbqLinear:
             out = (self.make_out(M, self.out_features) if self.make_out else
                    self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda"))
             x_view = self.torch.empty((M, self.in_features), dtype=self.torch.float16, device="cuda")  # the GEMM reads fp16 here
-            p = B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out, x_bits=self.x_bits, w_bits=self.w_bits,
-                              x_signed=True, w_signed=False, out_dtype=self.abq.OUT_FP16,
-                              scale_mode=self.abq.SCALE_GROUP if self.group else self.abq.SCALE_CHANNEL, group_size=self.group,
-                              w_scale=self.scale, w_zero=self.zero, x_scale=self.inv, flags=self.abq.FLAG_PDL | self.abq.FLAG_X_HALF, x_quant_scale=self.q_scale,
-                              workspace=self.work)
-            self.plans[key] = (self.abq.gemm_init(p), x_view, out)
+            flags = self.abq.FLAG_PDL | self.abq.FLAG_X_HALF
+            kw = dict(x_bits=self.x_bits, w_bits=self.w_bits, x_signed=True, w_signed=False, out_dtype=self.abq.OUT_FP16,
+                      scale_mode=self.abq.SCALE_GROUP if self.group else self.abq.SCALE_CHANNEL, group_size=self.group,
+                      w_scale=self.scale, w_zero=self.zero, x_scale=self.inv, x_quant_scale=self.q_scale, workspace=self.work,
+                      status_word=self.status)
+            probe = B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out, flags=flags, **kw)
+            nbytes = self.abq.gemm_prepared_weight_bytes(probe) if M <= 32 else 0
+            st = None
+            if nbytes:
+                if self.prepared is None:
+                    self.prepared = self.torch.empty(nbytes, dtype=self.torch.uint8, device="cuda")
+                try:
+                    st = self.abq.gemm_init(B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out,
+                                                          flags=flags | self.abq.FLAG_WEIGHTS_PREPARED, route=self.abq.ROUTE_I8_MMA,
+                                                          w_prepared=self.prepared, allreduce=None if self.fused is None else self.fused["desc"], **kw))
+                except self.abq.AbqError:
+                    st = None
+                    if self.fused is not None:
+                        raise
+                if st is not None and not self.prepared_done:
+                    self.abq.gemm_prepare_weights(st)
+                    self.torch.cuda.synchronize()  # a PDL GEMM must not be launched behind the kernel that writes its weights
+                    self.prepared_done = True
+            if st is None:
+                if self.fused is not None:
+                    raise RuntimeError("the fused all-reduce needs the prepared-weights decode kernel")
+                st = self.abq.gemm_init(probe)
+            self.plans[key] = (st, x_view, out)
         return self.plans[key]
 
     def input(self, M):
@@ -179,13 +223,32 @@ class AbqBackend:
         self.abq, self.torch, self.dist = abq, torch, dist
         self.x_bits, self.x_scale, self.max_tokens = x_bits, x_scale, max_tokens
         import os
-        self.peer_reduce = dist is not None and dist.get_world_size() > 1 and os.environ.get("ABQ_TP_NCCL", "0") != "1"
+        several = dist is not None and dist.get_world_size() > 1
+        # how the row-parallel partials are summed: "fused" (inside the GEMM, default), "peer" (the library's one-shot
+        # all-reduce kernel after the GEMM) or "nccl" (torch.distributed)
+        self.reduce_kind = os.environ.get("ABQ_TP_REDUCE", "nccl" if os.environ.get("ABQ_TP_NCCL", "0") == "1" else "fused") if several else "none"
+        if self.reduce_kind not in ("none", "fused", "peer", "nccl"):
+            raise ValueError(f"ABQ_TP_REDUCE={self.reduce_kind}")
+        self.peer_reduce = self.reduce_kind in ("fused", "peer")  # no NCCL call on the data path: the step can be one CUDA graph
         self._reduced = {}
+        self._fused_outputs = set()
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def make_linear(self, codes, scale, zero, w_bits, group, reduce_output=False):
-        make_out = self._peer_visible_output if (reduce_output and self.peer_reduce) else None
-        return AbqLinear(self.abq, self.torch, codes, scale, zero, w_bits, group, self.x_bits, self.x_scale, self.max_tokens, make_out)
+        make_out = self._peer_visible_output if (reduce_output and self.reduce_kind == "peer") else None
+        fused = (self.dist, self.dist.get_world_size(), self.dist.get_rank()) if (reduce_output and self.reduce_kind == "fused") else None
+        layer = AbqLinear(self.abq, self.torch, codes, scale, zero, w_bits, group, self.x_bits, self.x_scale, self.max_tokens, make_out,
+                          fused_reduce=fused, status=self.status)
+        if fused is not None:
+            layer.owner = self
+            plan = layer._plan
+
+            def plan_and_note(M, _plan=plan):
+                res = _plan(M)
+                self._fused_outputs.add(res[2].data_ptr())  # all_reduce() leaves these alone: the GEMM already summed them
+                return res
+            layer._plan = plan_and_note
+        return layer
 
     # ---- all-reduce of the row-parallel partials.  Several ranks on one node: the partial buffers live in symmetric
     # memory (every rank has every rank's buffer mapped) and the library's one-shot kernel adds them over NVLink peer
@@ -199,7 +262,7 @@ class AbqBackend:
         return t
 
     def all_reduce(self, t):
-        if self.dist is None or self.dist.get_world_size() == 1:
+        if self.dist is None or self.dist.get_world_size() == 1 or t.data_ptr() in self._fused_outputs:
             return t
         entry = self._reduced.get(t.data_ptr())
         if entry is None:

@@ -7,17 +7,21 @@ Workload at every N (one replica per GPU, no data-path collective): the decode-s
 W2A8, W3A8, W4A8 x M in {1, 4, 16} over the LLaMA-7B linear shapes (N, K) in {(4096, 4096),
 (12288, 4096), (11008, 4096), (4096, 11008)}; weights unsigned uniform over their bit range with a
 per-128-group fp16 scale ~U(0.001, 0.02) and an integer zero point, activations int8 ~N(0, 30)
-clipped, fp16 dequantised output.  One step = one pass over the 36 GEMMs.  All data is synthetic and
-seeded; it stands in for real checkpoints, which are not needed to time a GEMM.
+clipped, fp16 dequantised output.  One pass = the 36 GEMMs once; one step = PASSES_PER_STEP passes
+(one CUDA graph), so that the timed region is long enough for the clock sampler.  All data is synthetic
+and seeded; it stands in for real checkpoints, which are not needed to time a GEMM.
 
-Metric: algorithmic GB/s (weight planes + activation planes + scales + zero points + output, each
+Metric: algorithmic GB/s (weight bits + activation planes + scales + zero points + output, each
 counted once per GEMM) summed over the sweep -- the decode path is HBM-bound, so this is the number
-its roofline is stated in; effective TOPS (2*M*N*K / t) per WxAy is reported beside it.
+its roofline is stated in; per-WxAy figures (time, GB/s, fraction of the HBM peak, effective TOPS) are in
+`detail`.  The weights are read in the library's prepared (load-time re-ordered) form, `planes` holds the
+same sweep reading the reference's plane format directly.
 
 The line also carries `e2e` (same metric through the C ABI with host buffers: activation planes are
 copied from pinned host memory and the fp16 result is copied back inside the timed region),
-`roofline` (dominant kernel against the measured HBM peak) and `cpu_baseline` (the reference's CPU
-loop on a bounded sample, rank 0, N=1 only).
+`roofline` (dominant kernel against the measured HBM peak), `cpu_baseline` (the reference's CPU loop on
+a bounded sample, rank 0, N=1 only), `config0` (the reference's own CPU-checkable case), `prefill`
+(tensor-core route) and, on several GPUs, `tp_decode` (the tensor-parallel LLaMA-7B linear stack).
 """
 from __future__ import annotations
 
@@ -42,11 +46,14 @@ WBITS = [2, 3, 4]
 MS = [1, 4, 16]
 XBITS = 8
 GROUP = 128
-WEIGHT_COPIES = 2  # every weight exists twice and the copies alternate, so a pass never finds its planes in L2
+# Every weight exists once per token count and GEMM (q, M, N, K) reads copy MS.index(M): two reads of one buffer are a
+# whole pass apart (the 36 GEMMs move 569 MB, 4.5 x the 126 MB L2), so no launch finds its weights in L2.
+WEIGHT_COPIES = len(MS)
+PASSES_PER_STEP = 200
 METRIC = "quant_gemm_decode_sweep_algorithmic_GBps"
-# dram__bytes_read + dram__bytes_write over algorithmic bytes, from the ncu capture of decode_kernel summarised in
-# profiles/decode_kernel_sweep_and_w4a8_m1_32768x4096.md (a smaller single-shape case; traffic grows with the bytes)
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.018
+# dram__bytes_read + dram__bytes_write per algorithmic byte of the dominant kernel, from an ncu capture of a sweep-sized
+# launch (W4A8, M=1, 12288 x 4096); traffic grows with the bytes, so it is scaled to the mean launch of the sweep
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = {"stream_kernel": None, "decode_kernel": 1.018}
 
 
 def load_package():
@@ -117,11 +124,24 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _params(abq, g, xbuf, obuf, kind, status):
+    """abq_gemm_params of sweep GEMM `g` reading its weights as planes or in the prepared form."""
+    B = abq.binding
+    flags = abq.FLAG_PDL if os.environ.get("ABQ_BENCH_PDL", "1") == "1" else 0
+    prepared = None
+    if kind == "prepared":
+        flags |= abq.FLAG_WEIGHTS_PREPARED
+        prepared = g["prepared"]
+    return B.make_params(g["M"], g["N"], g["K"], xbuf, g["planes"], obuf, x_bits=XBITS, w_bits=g["q"], x_signed=True, w_signed=False,
+                         out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP, group_size=GROUP, w_scale=g["w_scale"], w_zero=g["w_zero"],
+                         flags=flags, workspace=g["work"], status_word=status, w_prepared=prepared)
+
+
 def build_workload(abq, torch, seed):
-    """Seeded device-resident operands (packed by the library's own pack kernel) and one launch plan per GEMM."""
+    """Seeded device-resident operands (packed by the library's own pack kernel), the prepared copy of every weight
+    (made once here by abq_gemm_prepare_weights, as a model loader would) and the launch plans of every GEMM."""
     gen = torch.Generator(device="cuda")
     gen.manual_seed(seed)
-    B = abq.binding
 
     def pack(codes, bits):
         rows, K = codes.shape
@@ -129,17 +149,7 @@ def build_workload(abq, torch, seed):
         abq.pack_int32(codes.contiguous(), planes, rows, K, bits)
         return planes
 
-    weights = {}
-    for q in WBITS:
-        for (N, K) in SHAPES:
-            copies = []
-            for c in range(WEIGHT_COPIES):
-                codes = torch.randint(0, 1 << q, (N, K), dtype=torch.int32, device="cuda", generator=gen)
-                planes = pack(codes, q)
-                ws = (torch.rand((N, K // GROUP), device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16)
-                wz = torch.randint(0, 1 << q, (N, K // GROUP), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8)
-                copies.append((planes, ws, wz))
-            weights[(q, N, K)] = copies
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     acts = {}
     for M in MS:
         for K in sorted({k for _, k in SHAPES}):
@@ -148,73 +158,73 @@ def build_workload(abq, torch, seed):
             host = torch.empty(dev_x.shape, dtype=torch.int32).pin_memory()
             host.copy_(dev_x)
             acts[(M, K)] = (host, dev_x)
-    torch.cuda.synchronize()
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    gemms = []
     # e2e mode: the activation planes of a whole pass travel in ONE pinned host buffer -> one device buffer, the fp16
-    # results of a pass in one device buffer -> one pinned host buffer; every GEMM works on its views of the two
+    # results of a pass in one device buffer -> one pinned host buffer; every GEMM works on its views of the two.
+    # One bit width after the other, as a model with one weight format runs them: consecutive GEMMs use the same kernel.
     order = [(q, M, N, K) for q in WBITS for M in MS for (N, K) in SHAPES]
     x_words = sum(XBITS * M * (K // 32) for (_, M, _, K) in order)
     out_elems = sum(M * N for (_, M, N, _) in order)
     e2e = {"x_host": torch.empty(x_words, dtype=torch.int32).pin_memory(), "x_dev": torch.empty(x_words, dtype=torch.int32, device="cuda"),
            "out_dev": torch.empty(out_elems, dtype=torch.float16, device="cuda"), "out_host": torch.empty(out_elems, dtype=torch.float16).pin_memory()}
+    gemms = []
     x_at = out_at = 0
-    # one bit width after the other, as a model with one weight format runs them: consecutive GEMMs use the same kernel
     for (q, M, N, K) in order:
-        ws_bytes = abq.gemm_workspace_bytes(M, N, K, XBITS, q)
+        codes = torch.randint(0, 1 << q, (N, K), dtype=torch.int32, device="cuda", generator=gen)
+        g = dict(q=q, M=M, N=N, K=K, planes=pack(codes, q),
+                 w_scale=(torch.rand((N, K // GROUP), device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16),
+                 w_zero=torch.randint(0, 1 << q, (N, K // GROUP), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8),
+                 work=torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, XBITS, q)), dtype=torch.uint8, device="cuda"),
+                 out=torch.empty((M, N), dtype=torch.float16, device="cuda"), bytes=algorithmic_bytes(M, N, K, XBITS, q), ops=2 * M * N * K)
+        del codes
         host_x, dev_x = acts[(M, K)]
         nx, no = XBITS * M * (K // 32), M * N
         e2e["x_host"][x_at:x_at + nx].copy_(host_x.view(-1))
         stage_x = e2e["x_dev"][x_at:x_at + nx].view(XBITS, M, K // 32)
         out_e2e = e2e["out_dev"][out_at:out_at + no].view(M, N)
         x_at, out_at = x_at + nx, out_at + no
-        for c in range(WEIGHT_COPIES):
-            planes, wsc, wz = weights[(q, N, K)][c]
-            out = torch.empty((M, N), dtype=torch.float16, device="cuda")
-            work = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
-            states = {}
-            for name, xbuf, obuf in (("resident", dev_x, out), ("e2e", stage_x, out_e2e)):
-                p = B.make_params(M, N, K, xbuf, planes, obuf, x_bits=XBITS, w_bits=q, x_signed=True, w_signed=False,
-                                  out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP, group_size=GROUP, w_scale=wsc, w_zero=wz,
-                                  flags=abq.FLAG_PDL if os.environ.get("ABQ_BENCH_PDL", "1") == "1" else 0, workspace=work,
-                                  status_word=status)
-                states[name] = abq.gemm_init(p)
-            gemms.append(dict(M=M, N=N, K=K, q=q, copy=c, states=states, out=out, host_x=host_x,
-                              keep=(planes, wsc, wz, work, dev_x), bytes=algorithmic_bytes(M, N, K, XBITS, q), ops=2 * M * N * K))
-    for g in gemms:
+        g["host_x"], g["dev_x"] = host_x, dev_x
+        probe = _params(abq, g, dev_x, g["out"], "planes", status)
+        nbytes = abq.gemm_prepared_weight_bytes(probe)
+        g["prepared"] = torch.empty(nbytes, dtype=torch.uint8, device="cuda") if nbytes else None
+        g["states"] = {"planes": abq.gemm_init(probe)}
+        if nbytes:
+            g["states"]["prepared"] = abq.gemm_init(_params(abq, g, dev_x, g["out"], "prepared", status))
+            abq.gemm_prepare_weights(g["states"]["prepared"])
+            g["states"]["e2e"] = abq.gemm_init(_params(abq, g, stage_x, out_e2e, "prepared", status))
+        else:
+            g["states"]["prepared"] = g["states"]["planes"]
+            g["states"]["e2e"] = abq.gemm_init(_params(abq, g, stage_x, out_e2e, "planes", status))
         g["e2e"] = e2e
+        gemms.append(g)
+    torch.cuda.synchronize()
     return gemms, status
 
 
-def one_pass(abq, gemms, copy, mode):
-    """One pass over the 36 GEMMs (weight copy `copy`).  mode 'resident': operands already in HBM;
-    mode 'e2e': the pass's activation planes come from pinned host memory in one copy and its results go back to
-    pinned host memory in one copy, both inside the pass."""
-    mine = [g for g in gemms if g["copy"] == copy]
-    if mode == "e2e" and mine:
-        mine[0]["e2e"]["x_dev"].copy_(mine[0]["e2e"]["x_host"], non_blocking=True)      # this pass's activation planes, host -> device
-    for g in mine:
-        abq.gemm_exec(g["states"]["e2e" if mode == "e2e" else "resident"])
-    if mode == "e2e" and mine:
-        mine[0]["e2e"]["out_host"].copy_(mine[0]["e2e"]["out_dev"], non_blocking=True)  # this pass's results, device -> host
+def one_pass(abq, gemms, mode):
+    """One pass over the 36 GEMMs.  mode 'prepared' / 'planes': operands already in HBM, weights in the prepared form /
+    as the reference's planes; mode 'e2e': the pass's activation planes come from pinned host memory in one copy and its
+    results go back to pinned host memory in one copy, both inside the pass (weights prepared)."""
+    if mode == "e2e" and gemms:
+        gemms[0]["e2e"]["x_dev"].copy_(gemms[0]["e2e"]["x_host"], non_blocking=True)      # this pass's activation planes, host -> device
+    for g in gemms:
+        abq.gemm_exec(g["states"][mode])
+    if mode == "e2e" and gemms:
+        gemms[0]["e2e"]["out_host"].copy_(gemms[0]["e2e"]["out_dev"], non_blocking=True)  # this pass's results, device -> host
 
 
-def capture_passes(torch, abq, gemms, mode):
-    """One CUDA graph per weight copy holding a whole pass (72 kernels, plus the copies in e2e mode), so that the
-    timed region measures the device and not the Python launch loop.  Returns a callable step(i)."""
+def capture_step(torch, abq, gemms, mode, passes):
+    """One CUDA graph holding `passes` passes (36 kernels each, plus the two copies in e2e mode), so that the timed region
+    measures the device and not the Python launch loop.  Returns a callable step(i)."""
     side = torch.cuda.Stream()
-    graphs = []
     with torch.cuda.stream(side):
-        for c in range(WEIGHT_COPIES):
-            one_pass(abq, gemms, c, mode)  # first launches outside capture: kernel attributes get set here
+        one_pass(abq, gemms, mode)  # first launches outside capture: kernel attributes get set here
         side.synchronize()
-        for c in range(WEIGHT_COPIES):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                one_pass(abq, gemms, c, mode)
-            graphs.append(g)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(passes):
+                one_pass(abq, gemms, mode)
     torch.cuda.synchronize()
-    return lambda i: graphs[i % WEIGHT_COPIES].replay()
+    return lambda i: g.replay()
 
 
 def max_over_ranks(torch, dist, value: float, device) -> float:
@@ -254,45 +264,105 @@ def timed(torch, dist, fn, steps, warmup):
     return max_over_ranks(torch, dist, ms, "cuda"), wall_ms
 
 
-def per_config_detail(torch, abq, gemms, reps=20):
-    """Device time of every (WxAy, M, shape) GEMM alone, alternating the weight copies: TOPS and GB/s per config."""
+def per_config_detail(torch, abq, gemms, status, peak, mode="prepared"):
+    """Device time of every (WxAy, M, shape) GEMM by itself: a CUDA graph of back-to-back launches of that one GEMM, each
+    on its own copy of the weights (enough copies that 260 MB of other weights pass between two reads of one buffer, so
+    none is served from L2).  GB/s, fraction of the measured HBM peak and effective TOPS per config."""
     rows = []
-    by_key = {}
+    side = torch.cuda.Stream()
     for g in gemms:
-        by_key.setdefault((g["q"], g["M"], g["N"], g["K"]), []).append(g)
-    for (q, M, N, K), gs in sorted(by_key.items()):
-        for i in range(4):
-            abq.gemm_exec(gs[i % len(gs)]["states"]["resident"])
+        src = g["prepared"] if (mode == "prepared" and g["prepared"] is not None) else g["planes"]
+        nbytes = src.numel() * src.element_size()
+        copies = int(260e6 // nbytes) + 2
+        clones = [src] + [src.clone() for _ in range(copies - 1)]
+        states = []
+        for c in clones:
+            gg = dict(g)
+            gg["prepared" if src is g["prepared"] else "planes"] = c
+            states.append(abq.gemm_init(_params(abq, gg, g["dev_x"], g["out"], "prepared" if src is g["prepared"] else "planes", status)))
+        with torch.cuda.stream(side):
+            abq.gemm_exec(states[0])
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for st in states:
+                    abq.gemm_exec(st)
+        torch.cuda.synchronize()
+        graph.replay()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
         e0.record()
-        for i in range(reps):
-            abq.gemm_exec(gs[i % len(gs)]["states"]["resident"])
+        for _ in range(reps):
+            graph.replay()
         e1.record()
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / reps
-        rows.append({"wxay": f"W{q}A{XBITS}", "M": M, "N": N, "K": K, "us": round(us, 3), "GBps": round(gs[0]["bytes"] / us / 1e3, 1),
-                     "TOPS": round(gs[0]["ops"] / us / 1e6, 3)})
+        us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+        rows.append({"wxay": f"W{g['q']}A{XBITS}", "M": g["M"], "N": g["N"], "K": g["K"], "us": round(us, 3), "GBps": round(g["bytes"] / us / 1e3, 1),
+                     "frac_of_hbm": round(g["bytes"] / us / 1e3 / peak, 3), "TOPS": round(g["ops"] / us / 1e6, 3)})
+        del clones, states, graph
     return rows
 
 
-PREFILL_CASES = [(4, 4, 4096, 4096, 4096, 0), (4, 4, 4096, 11008, 4096, 0), (2, 8, 4096, 12288, 4096, 0), (8, 8, 4096, 4096, 11008, 0),
-                 (4, 4, 2048, 4096, 4096, 0), (4, 4, 512, 12288, 4096, 0),
-                 (4, 8, 4096, 4096, 4096, 128), (2, 8, 2048, 11008, 4096, 128)]  # (w bits, x bits, M, N, K, scale group: 0 = per channel)
+# (w bits, x bits, M, N, K, scale group: 0 = per channel): every width pair of the prefill sweep at M = 2048 on one shape, the M
+# sweep on W4A4 over two shapes, the four largest cases, and two with per-group scales + zero points
+PREFILL_CASES = ([(x, x, 2048, 4096, 4096, 0) for x in (2, 3, 4, 5, 6, 7, 8)] + [(2, 4, 2048, 4096, 4096, 0), (2, 6, 2048, 4096, 4096, 0)] +
+                 [(4, 4, M, N, K, 0) for M in (512, 4096) for (N, K) in ((4096, 4096), (12288, 4096))] + [(4, 4, 2048, 12288, 4096, 0)] +
+                 [(4, 4, 4096, 11008, 4096, 0), (2, 8, 4096, 12288, 4096, 0), (8, 8, 4096, 4096, 11008, 0)] +
+                 [(4, 8, 4096, 4096, 4096, 128), (2, 8, 2048, 11008, 4096, 128)])
+
+
+def int8_library_rate(torch):
+    """Dense int8 x int8 -> int32 8192^3 through the vendor library (torch._int_mm -> cuBLASLt), burst: the practical
+    ceiling of the int8 tensor pipe next to the 2 x bf16 figure.  None if the call is not available."""
+    try:
+        n = 8192
+        a = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda")
+        b = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda").t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:  # noqa: BLE001 - a missing library kernel only removes a reported ceiling
+        return None
 
 
 def prefill_leg(torch, abq, reps=10):
-    """Prefill shapes (M >= 512) on the tcgen05 kind::i8 route, per-channel or per-group fp16 scale, fp16 output: device time of the
-    whole call (plane -> int8 expansion of both operands, the GEMM with its fused epilogue) per case, effective
-    TOPS = 2*M*N*K / t, and the fraction of twice the measured dense bf16 rate (the int8 rate of the same pipe)."""
+    """Prefill shapes (M >= 512) on the tcgen05 kind::i8 route, per-channel or per-group fp16 scale: device time of the whole
+    call (plane -> int8 expansion of both operands, the GEMM with its fused epilogue) per case with fp16 and with int32
+    output, effective TOPS = 2*M*N*K / t, as a fraction of twice the measured dense bf16 rate (the int8 rate of the same
+    pipe) and of the vendor library's int8 GEMM measured in this run; the same call with the weights expanded beforehand."""
     peak = None
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
         peak = 2.0 * float(json.loads(f.read_text())["bf16_tflops"])
+    lib_rate = int8_library_rate(torch)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(7)
     B = abq.binding
     rows = []
+
+    def time_state(st):
+        for _ in range(3):
+            abq.gemm_exec(st)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            abq.gemm_exec(st)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
     for (q, p, M, N, K, group) in PREFILL_CASES:
         def planes_of(rows_, bits):
             codes = torch.randint(0, 1 << bits, (rows_, K), dtype=torch.int32, device="cuda", generator=gen)
@@ -304,63 +374,76 @@ def prefill_leg(torch, abq, reps=10):
         wsc = (torch.rand(shape, device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16)
         wz = torch.randint(0, 1 << q, shape, dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8) if group else None
         out = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        out32 = torch.empty((M, N), dtype=torch.int32, device="cuda")
         work = torch.empty(abq.gemm_workspace_bytes(M, N, K, p, q), dtype=torch.uint8, device="cuda")
-        prm = B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=bool(group), w_signed=False, out_dtype=abq.OUT_FP16,
-                            scale_mode=abq.SCALE_GROUP if group else abq.SCALE_CHANNEL, group_size=group, w_scale=wsc, w_zero=wz,
-                            workspace=work)
-        st = abq.gemm_init(prm)
-        for _ in range(3):
-            abq.gemm_exec(st)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            abq.gemm_exec(st)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / reps
-        tops = 2.0 * M * N * K / us / 1e6
-        # the same call with the weight codes expanded once beforehand (weights that stay the same from call to call)
-        prm.flags = abq.FLAG_WEIGHTS_PREPARED
-        st2 = abq.gemm_init(prm)
+        kw = dict(x_bits=p, w_bits=q, x_signed=bool(group), w_signed=False, workspace=work)
+        kw16 = dict(kw, out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP if group else abq.SCALE_CHANNEL, group_size=group, w_scale=wsc, w_zero=wz)
+        us = time_state(abq.gemm_init(B.make_params(M, N, K, xp, wp, out, **kw16)))
+        us32 = None if group else time_state(abq.gemm_init(B.make_params(M, N, K, xp, wp, out32, **kw)))
+        st2 = abq.gemm_init(B.make_params(M, N, K, xp, wp, out, flags=abq.FLAG_WEIGHTS_PREPARED, **kw16))
         abq.gemm_prepare_weights(st2)
-        for _ in range(3):
-            abq.gemm_exec(st2)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(reps):
-            abq.gemm_exec(st2)
-        e1.record()
-        torch.cuda.synchronize()
-        us2 = e0.elapsed_time(e1) * 1e3 / reps
-        tops2 = 2.0 * M * N * K / us2 / 1e6
-        # ... and with fp16 activations handed to the call (quantised straight to int8 codes): the FasterTransformer wrapper's path
-        xh = (torch.randn((M, K), device="cuda", generator=gen) * 2).to(torch.float16)
-        qs = torch.full((1,), 1.5 if p < 8 else 12.0, dtype=torch.float32, device="cuda")
-        prm3 = B.make_params(M, N, K, xh, wp, out, x_bits=p, w_bits=q, x_signed=True, w_signed=False, out_dtype=abq.OUT_FP16,
-                             scale_mode=abq.SCALE_GROUP if group else abq.SCALE_CHANNEL, group_size=group, w_scale=wsc, w_zero=wz,
-                             workspace=work, flags=abq.FLAG_WEIGHTS_PREPARED | abq.FLAG_X_HALF, x_quant_scale=qs)
-        st3 = abq.gemm_init(prm3)
-        abq.gemm_prepare_weights(st3)
-        for _ in range(3):
-            abq.gemm_exec(st3)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(reps):
-            abq.gemm_exec(st3)
-        e1.record()
-        torch.cuda.synchronize()
-        us3 = e0.elapsed_time(e1) * 1e3 / reps
-        tops3 = 2.0 * M * N * K / us3 / 1e6
-        rows.append({"wxay": f"W{q}A{p}", "scales": f"g{group} + zero" if group else "channel", "M": M, "N": N, "K": K, "us": round(us, 2),
-                     "TOPS": round(tops, 1),
-                     "frac_of_int8_peak": round(tops / peak, 3) if peak else None, "us_weights_prepared": round(us2, 2),
-                     "TOPS_weights_prepared": round(tops2, 1), "frac_weights_prepared": round(tops2 / peak, 3) if peak else None,
-                     "us_half_x_prepared_w": round(us3, 2), "TOPS_half_x_prepared_w": round(tops3, 1),
-                     "frac_half_x_prepared_w": round(tops3 / peak, 3) if peak else None})
-        del xp, wp, out, work, xh
+        us2 = time_state(st2)
+        ops = 2.0 * M * N * K
+        row = {"wxay": f"W{q}A{p}", "scales": f"g{group} + zero" if group else "channel", "M": M, "N": N, "K": K, "us_fp16_out": round(us, 2),
+               "TOPS": round(ops / us / 1e6, 1), "frac_of_2x_bf16": round(ops / us / 1e6 / peak, 3) if peak else None,
+               "frac_of_library_int8": round(ops / us / 1e6 / lib_rate, 3) if lib_rate else None,
+               "us_int32_out": None if us32 is None else round(us32, 2), "TOPS_int32_out": None if us32 is None else round(ops / us32 / 1e6, 1),
+               "us_weights_prepared": round(us2, 2), "TOPS_weights_prepared": round(ops / us2 / 1e6, 1),
+               "frac_weights_prepared": round(ops / us2 / 1e6 / peak, 3) if peak else None}
+        rows.append(row)
+        del xp, wp, out, out32, work
     return {"route": "tcgen05 kind::i8 (plane->int8 expansion included in the time)", "int8_peak_TOPS": peak,
-            "peak_source": "2 x MEASURED_PEAKS.json bf16_tflops" if peak else None, "cases": rows}
+            "peak_source": "2 x MEASURED_PEAKS.json bf16_tflops" if peak else None,
+            "library_int8_TOPS": None if lib_rate is None else round(lib_rate, 1), "library_int8_source": "torch._int_mm 8192^3, best of 10, this run",
+            "cases": rows}
+
+
+def config0_leg(torch, abq, hbm_peak):
+    """The reference's own CPU-checkable case (W4A4 unsigned, M=128, N=K=4096, int32 out): device time of the whole call
+    on the route the planner picks, against both rooflines (it sits between the HBM-bound and the tensor-bound regime)."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3)
+    B = abq.binding
+    M, N, K, p, q = 128, 4096, 4096, 4, 4
+
+    def planes_of(rows_, bits):
+        codes = torch.randint(0, 1 << bits, (rows_, K), dtype=torch.int32, device="cuda", generator=gen)
+        out = torch.empty((bits, rows_, K // 32), dtype=torch.int32, device="cuda")
+        abq.pack_int32(codes, out, rows_, K, bits)
+        return out
+    xp = planes_of(M, p)
+    copies = 18  # 18 x 8.4 MB of planes between two reads of one buffer
+    wps = [planes_of(N, q) for _ in range(copies)]
+    out = torch.empty((M, N), dtype=torch.int32, device="cuda")
+    work = torch.empty(abq.gemm_workspace_bytes(M, N, K, p, q), dtype=torch.uint8, device="cuda")
+    states = [abq.gemm_init(B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=False, w_signed=False, workspace=work)) for wp in wps]
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        abq.gemm_exec(states[0])
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for st in states:
+                abq.gemm_exec(st)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (3 * copies)
+    nbytes = q * N * K // 8 + p * M * K // 8 + 4 * M * N
+    peak = None
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        peak = 2.0 * float(json.loads(f.read_text())["bf16_tflops"])
+    tops = 2.0 * M * N * K / us / 1e6
+    return {"workload": "W4A4 unsigned, M=128, N=4096, K=4096, int32 out", "route": {2: "I8_MMA", 3: "I8_UMMA"}.get(states[0].route),
+            "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm_peak, 3), "TOPS": round(tops, 1),
+            "frac_of_2x_bf16": round(tops / peak, 3) if peak else None}
 
 
 def _time_calls(torch, fn, reps=10, warm=3):
@@ -473,7 +556,7 @@ def cpu_baseline_sample(kind_pref: str, budget_s: float = 12.0):
             "seconds": t}
 
 
-WORKLOAD = ("decode sweep (BASELINE configs[1]): W{2,3,4}A8 x M{1,4,16} x (N,K) in "
+WORKLOAD = ("decode sweep: W{2,3,4}A8 x M{1,4,16} x (N,K) in "
             "{(4096,4096),(12288,4096),(11008,4096),(4096,11008)}, g128 fp16 scale + u8 zero, fp16 out")
 
 
@@ -525,20 +608,12 @@ def reference_gpu_kernels():
     return rows
 
 
-def run_tp_decode(args, rank, world, local):
+def tp_decode_measure(args, torch, dist, abq, rank, world):
     """`--workload tp_decode`: one decode step through the quantized linear layers of LLaMA-7B (32 blocks: fused QKV, O,
     fused gate+up, down; W4A4, per-channel scale + zero point, static activation scale), tensor parallel over the
     ranks: column-parallel QKV / gate+up, row-parallel O / down with an NCCL all-reduce after each.  Attention, norms,
     embedding and lm_head are outside the path (elementwise torch stand-ins keep the data flowing).  Strong scaling:
     the model is fixed, every rank holds 1/N of every weight."""
-    import torch
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
-        dist = dist_mod
-    abq = load_package()
     spec = importlib.util.spec_from_file_location("abq_llm_b200.tp_linear", ROOT / "abq-llm_b200" / "tp_linear.py")
     tp = importlib.util.module_from_spec(spec)
     sys.modules[spec.name] = tp
@@ -618,19 +693,39 @@ def run_tp_decode(args, rank, world, local):
                 if t is not None:
                     backend.all_reduce(t)
         fn = (lambda i: graph.replay()) if graph is not None else ((lambda i: step_pieces()) if pieces else (lambda i: step()))
-        ms, _ = timed(torch, dist, fn, max(3, args.steps // 10), 3)
-        n = max(3, args.steps // 10)
-        results.append({"batch": M, "ms_per_step": ms / n, "tokens_per_s": M * n / (ms * 1e-3), "cuda_graph": "whole step" if graph is not None else ("between the all-reduces" if pieces else "no")})
+        n = args.tp_steps
+        ms, _ = timed(torch, dist, fn, n, 3)
+        results.append({"batch": M, "steps": n, "ms_per_step": ms / n, "tokens_per_s": M * n / (ms * 1e-3), "cuda_graph": "whole step" if graph is not None else ("between the all-reduces" if pieces else "no")})
+    if int(backend.status.item()) != 0:
+        raise SystemExit(f"tp_decode: device status word {int(backend.status.item())} (a bounded wait expired): the numbers are void")
+    wbytes = layers * sum(sp.out_features * sp.in_features for sp in tp.llama_block_specs(hidden, ffn)) * q // 8
+    del blocks
+    return {"metric": "llama7b_w4a4_linear_stack_decode_tokens_per_s", "unit": "tokens/s", "tensor_parallel": world, "scaling": "strong",
+            "workload": f"LLaMA-7B linear layers only, {layers} blocks, W4A4 per-channel + zero point, static activation scale; attention, "
+                        "norms, embedding and lm_head are outside the path",
+            "all_reduce": "none (one rank)" if world == 1 else (backend.reduce_kind if hasattr(backend, "reduce_kind") else
+                                                                ("library peer all-reduce kernel" if backend.peer_reduce else "NCCL")),
+            "weight_bytes_all_ranks": wbytes, "batches": results,
+            "hbm_bound_tokens_per_s_batch1": world * measured_peaks()[0] * 1e9 / wbytes}
+
+
+def run_tp_decode(args, rank, world, local):
+    """`--workload tp_decode` by itself: the tensor-parallel linear stack as the headline of its own JSON line."""
+    import torch
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    abq = load_package()
+    res = tp_decode_measure(args, torch, dist, abq, rank, world)
     if rank == 0:
-        wbytes = layers * sum(sp.out_features * sp.in_features for sp in tp.llama_block_specs(hidden, ffn)) * q // 8
-        best = results[0]
-        line = {"metric": "llama7b_w4a4_linear_stack_decode_tokens_per_s", "value": best["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
-                "steps": max(3, args.steps // 10), "warmup": 3, "ms_per_step": best["ms_per_step"], "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-                "config": {"workload": f"LLaMA-7B linear layers only, {layers} blocks, W4A4 per-channel, tensor parallel {world}, batch 1 "
-                                       "(value); batches 8 and 32 in `batches`", "weight_bytes_all_ranks": wbytes},
-                "batches": results,
-                "hbm_bound_tokens_per_s_batch1": world * measured_peaks()[0] * 1e9 / wbytes}
+        best = res["batches"][0]
+        line = {"metric": res["metric"], "value": best["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": best["steps"], "warmup": 3,
+                "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
+                "data": "synthetic", "config": {"workload": res["workload"] + f"; tensor parallel {world}, batch 1 (value); batches 8 and 32 in `batches`"},
+                "tp_decode": res}
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
@@ -652,8 +747,9 @@ def run_reference(args, rank, world):
     value = statistics.mean(v["value"] for v in vals)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
             "ms_per_step": total_t / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
-            "data": "synthetic", "config": {"workload": WORKLOAD + "; each step a bounded sample (one M=16 W2A8 4096x4096 GEMM of the sweep, "
-                                                                   "repeated) on the host cores, reference compute_ref"},
+            "data": "synthetic", "config": {"workload": WORKLOAD + "; each step a bounded sample on the host cores, reference compute_ref",
+                                           "sample": "one of the 36 timed GEMMs of the sweep: W2A8, M=16, N=4096, K=4096 (repeated); the other arm "
+                                                     "reports its own time for this same GEMM as `reference_arm_gemm`"},
             "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     line["cpu_baseline"]["value"] = value
@@ -666,18 +762,22 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--detail", action="store_true", help="also time every GEMM of the sweep alone")
+    ap.add_argument("--passes", type=int, default=PASSES_PER_STEP, help="passes over the 36 GEMMs per step (one CUDA graph)")
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-(WxAy, M, shape) timings")
     ap.add_argument("--only", default="", help="profiling aid: restrict the sweep to GEMMs 'q:M:N:K[,q:M:N:K...]' (0 = any)")
     ap.add_argument("--shape", default="", help="profiling aid: replace the sweep by the single GEMM 'q:M:N:K' (any size the route takes)")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the short prefill-shape (tcgen05 route) leg")
+    ap.add_argument("--weights", default="prepared", choices=["prepared", "planes"], help="profiling aid: which weight form the headline sweep reads")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill / config0 / routes / pack legs")
     ap.add_argument("--workload", default="decode_sweep", choices=["decode_sweep", "tp_decode"],
                     help="decode_sweep (default, the headline metric) or tp_decode: tensor-parallel LLaMA-7B linear stack")
     ap.add_argument("--layers", type=int, default=32, help="tp_decode: decoder blocks")
+    ap.add_argument("--tp-steps", type=int, default=40, help="tp_decode: timed decode steps per batch size")
+    ap.add_argument("--no-tp", action="store_true", help="several GPUs: skip the tp_decode object")
     ap.add_argument("--tp-pieces", action="store_true", help="tp_decode on one GPU: graphs between the all-reduce points, as several ranks run it")
-    ap.add_argument("--no-graph", action="store_true", help="profiling aid: launch kernel by kernel instead of one CUDA graph per pass")
+    ap.add_argument("--no-graph", action="store_true", help="profiling aid: launch kernel by kernel instead of one CUDA graph per step")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling aid: skip the host-side reference timing")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -709,58 +809,83 @@ def main():
     if args.only:
         pats = [tuple(int(v) for v in item.split(":")) for item in args.only.split(",")]
         gemms = [g for g in gemms if any(all(a == 0 or a == b for a, b in zip(pat, (g["q"], g["M"], g["N"], g["K"]))) for pat in pats)]
-    n_gemm = len(gemms) // WEIGHT_COPIES
-    bytes_per_step = sum(g["bytes"] for g in gemms if g["copy"] == 0)
-    ops_per_step = sum(g["ops"] for g in gemms if g["copy"] == 0)
+    n_gemm = len(gemms)
+    passes = 1 if args.no_graph else max(1, args.passes)
+    bytes_per_pass = sum(g["bytes"] for g in gemms)
+    ops_per_pass = sum(g["ops"] for g in gemms)
+    bytes_per_step, ops_per_step = bytes_per_pass * passes, ops_per_pass * passes
+    headline = args.weights
+    other = "planes" if headline == "prepared" else "prepared"
 
+    def stepper(mode):
+        return capture_step(torch, abq, gemms, mode, passes) if not args.no_graph else (lambda i: one_pass(abq, gemms, mode))
+
+    step_res, step_e2e, step_other = stepper(headline), stepper("e2e"), stepper(other)
     sampler = ClockSampler(local)
     sampler.start()
-    use_graph = not args.no_graph
-    step_res = capture_passes(torch, abq, gemms, "resident") if use_graph else (lambda i: one_pass(abq, gemms, i % WEIGHT_COPIES, "resident"))
-    step_e2e = capture_passes(torch, abq, gemms, "e2e") if use_graph else (lambda i: one_pass(abq, gemms, i % WEIGHT_COPIES, "e2e"))
     ms, wall_ms = timed(torch, dist, step_res, args.steps, args.warmup)
     clocks = sampler.stop()
     ms_e2e, _ = timed(torch, dist, step_e2e, args.steps, args.warmup)
+    ms_other, _ = timed(torch, dist, step_other, max(3, args.steps // 4), args.warmup)
     if int(status.item()) != 0:
         raise SystemExit(f"device status word {int(status.item())}: a bounded wait expired, the numbers are void")
 
     value = whole_job_rate(world, bytes_per_step, args.steps, ms) / 1e9
     e2e = whole_job_rate(world, bytes_per_step, args.steps, ms_e2e) / 1e9
-    h2d = sum(g["host_x"].numel() * 4 for g in gemms if g["copy"] == 0)
-    d2h = sum(g["out"].numel() * 2 for g in gemms if g["copy"] == 0)
-    if args.only or args.shape:
-        h2d, d2h = gemms[0]["e2e"]["x_host"].numel() * 4, gemms[0]["e2e"]["out_host"].numel() * 2  # the buffers travel whole
+    value_other = whole_job_rate(world, bytes_per_step, max(3, args.steps // 4), ms_other) / 1e9
+    h2d = gemms[0]["e2e"]["x_host"].numel() * 4 * passes
+    d2h = gemms[0]["e2e"]["out_host"].numel() * 2 * passes
     peak, peak_kind = measured_peaks()
     per_gpu = bytes_per_step * args.steps / (ms * 1e-3) / 1e9
+    stream_launches = sum(1 for g in gemms if g["prepared"] is not None) if headline == "prepared" else 0
+    kernel = "stream_kernel" if stream_launches == n_gemm else ("decode_kernel" if stream_launches == 0 else "stream_kernel / decode_kernel")
+    ratio = DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE.get(kernel)
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD + f"; {n_gemm} GEMMs per step" + (f" (restricted by --only {args.only})" if args.only else ""),
-                   "l2": f"two alternating copies of every weight, {bytes_per_step / 1e6:.0f} MB of distinct operands between reuses (> 126 MB L2)",
-                   "replicas": world, "pdl": os.environ.get("ABQ_BENCH_PDL", "1") == "1", "cuda_graph_per_pass": use_graph},
+        "config": {"workload": WORKLOAD + f"; {n_gemm} GEMMs per pass" + (f" (restricted by --only {args.only})" if args.only else ""),
+                   "passes_per_step": passes, "ms_per_pass": ms / args.steps / passes,
+                   "weights": ("prepared: the reference's bit-planes re-ordered once at load time by abq_gemm_prepare_weights (same bits, +64 B of "
+                               "scale / zero point per 16 rows x 128 features); `planes` holds the sweep on the plane format itself")
+                              if headline == "prepared" else "the reference's bit-plane format, read directly",
+                   "l2": f"one copy of every weight per token count: {bytes_per_pass / 1e6:.0f} MB of other operands pass between two reads of a "
+                         "buffer (> 4 x the 126 MB L2); inputs larger than L2, no flush needed",
+                   "replicas": world, "pdl": os.environ.get("ABQ_BENCH_PDL", "1") == "1", "cuda_graph_per_step": not args.no_graph},
         "effective_TOPS": whole_job_rate(world, ops_per_step, args.steps, ms) / 1e12,
-        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": n_gemm * args.steps,  # one decode_kernel per GEMM
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "what": "per pass: one copy of all activation planes from pinned host memory, 36 GEMMs through the C ABI, one copy of all fp16 results back"},
+        other: {"value": value_other, "unit": "GB/s", "ms_per_pass": ms_other / max(3, args.steps // 4) / passes,
+                "frac_of_hbm": value_other / world / peak},
+        "gpu_launches": n_gemm * passes * args.steps,  # one kernel of this library per GEMM
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "decode_kernel (36 launches per step, all shapes)", "achieved": per_gpu, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": f"{kernel} ({n_gemm} launches per pass, all shapes)", "achieved": per_gpu, "peak": peak,
                      "unit": "GB/s", "frac": per_gpu / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
-                     "bytes_per_launch": bytes_per_step / max(1, n_gemm), "us_per_launch": ms * 1e3 / args.steps / max(1, n_gemm),
-                     "traffic": DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per_step / max(1, n_gemm),
-                     "traffic_source": "ncu dram bytes of a single-shape capture, scaled by algorithmic bytes (mean launch of the sweep)"},
+                     "bytes_per_launch": bytes_per_pass / max(1, n_gemm), "us_per_launch": ms * 1e3 / args.steps / passes / max(1, n_gemm),
+                     "traffic": None if ratio is None else ratio * bytes_per_pass / max(1, n_gemm),
+                     "traffic_source": "ncu dram bytes of a sweep-sized single-shape capture, scaled by algorithmic bytes to the mean launch of the sweep"},
         "wall_ms_per_step": wall_ms / args.steps,
     }
+    if args.shape:
+        line["config"]["workload"] = f"single GEMM --shape {args.shape} (profiling aid, not the sweep)"
+    extras = rank == 0 and world == 1 and not args.shape and not args.only
+    if rank == 0 and not args.no_detail and world == 1:
+        line["detail"] = per_config_detail(torch, abq, gemms, status, peak, headline)
+        same = [r for r in line["detail"] if (r["wxay"], r["M"], r["N"], r["K"]) == ("W2A8", 16, 4096, 4096)]
+        if same:  # the GEMM the reference arm samples, on this arm
+            line["reference_arm_gemm"] = dict(same[0], note="the one sweep GEMM `--impl reference` times on the host cores")
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         base = cpu_baseline_sample("reference")
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    if args.shape:
-        line["config"]["workload"] = f"single GEMM --shape {args.shape} (profiling aid, not the sweep)"
-    if rank == 0 and world == 1 and not args.no_prefill and not args.shape and not args.only:
+    if extras and not args.no_prefill:
+        line["config0"] = config0_leg(torch, abq, peak)
         line["prefill"] = prefill_leg(torch, abq)
         line["routes"] = routes_leg(torch, abq)
         line["pack"] = pack_leg(torch, abq)
-    if args.detail and rank == 0:
-        line["detail"] = per_config_detail(torch, abq, gemms)
+    if world > 1 and not args.no_tp and not args.shape and not args.only:
+        del gemms, step_res, step_e2e, step_other
+        torch.cuda.empty_cache()
+        line["tp_decode"] = tp_decode_measure(args, torch, dist, abq, rank, world)  # every rank takes part; rank 0 reports
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

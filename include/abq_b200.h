@@ -94,6 +94,31 @@ enum {
 };
 
 /*
+ * All-reduce fused into a row-parallel GEMM (decode shapes, prepared weights, fp16 output): D receives the SUM over the
+ * ranks of one node of what each rank's GEMM alone would have written (its fp16 partial), added in rank order in fp32 --
+ * the same bits on every rank.  Replaces, together with the GEMM, the ncclAllReduce that the reference's FasterTransformer
+ * fork issues after the attention output and FFN down projections (TensorParallelGptContextAttentionLayer.cc:50-53,
+ * TensorParallelSiluFfnLayer.cc:53-57).  How: as a CTA finishes its 16-row tiles it stores its partial straight into every
+ * rank's receive buffer (peer stores over NVLink), raises a flag per tile in every rank's flag array, waits (bounded,
+ * status_word) for the other ranks' flags of the same tiles and adds what they stored.  No separate kernel, no
+ * round trip for the data.  Buffers alternate with the parity of a device-side call counter, so a rank that runs ahead
+ * writes the other half; a launch replays inside a CUDA graph.
+ *   recv[r], flags[r]  rank r's receive buffer / flag array as mapped into THIS process (peer mappings, e.g. torch symmetric
+ *                      memory); entries [rank] are the local ones.  recv: 2 * world * rows_cap * N fp16
+ *                      ([parity][source rank][token][feature]); flags: 2 * world * ceil(N / 16) uint32, zero before first use
+ *   counter            local, two uint32, zero before first use (calls completed, CTA ticket); one per call site
+ *   rows_cap           token rows the receive buffers were sized for (>= M)
+ * Every rank must run the same sequence of fused GEMMs per call site.  Only plain peer stores and loads are used.
+ */
+typedef struct abq_fused_allreduce {
+    int world, rank; /* 2..8 ranks */
+    void *recv[8];
+    uint32_t *flags[8];
+    uint32_t *counter;
+    int rows_cap;
+} abq_fused_allreduce;
+
+/*
  * Problem description.  The first eight fields are the reference's launch arguments in the
  * reference's order (engine/mma_any/aq_bmma_op.h:24-31 `AqBMMAOpState::Argument_t`:
  * M, N, K, X, W, C, D, bias); the rest extends them.
@@ -123,6 +148,8 @@ typedef struct abq_gemm_params {
     int *status_word;       /* optional device int, set non-zero by a kernel whose bounded wait expired */
     const float *x_quant_scale; /* ABQ_FLAG_X_HALF: device float, the static activation scale */
     void *w_prepared;           /* ABQ_FLAG_WEIGHTS_PREPARED on route I8_MMA: the re-ordered weights, 16-byte aligned */
+    const abq_fused_allreduce *allreduce; /* optional (host pointer, copied by abq_gemm_init): sum D over the ranks inside the
+                                             GEMM; plans that cannot do it answer ABQ_ERR_UNSUPPORTED */
 } abq_gemm_params;
 
 /*
@@ -139,6 +166,7 @@ typedef struct abq_gemm_state {
     size_t shared_mem_size;
     int tile[4];       /* route specific tile description */
     unsigned long long tmap[3][16]; /* TMA tensor maps (128 B each), route specific */
+    abq_fused_allreduce ar;         /* copy of *p.allreduce (world == 0: none) */
 } abq_gemm_state;
 
 /* Bytes of caller-owned scratch a GEMM of this shape may need (route AUTO: the maximum over routes). */
@@ -189,6 +217,19 @@ ABQ_API abq_status abq_quantize_pack_half(const void *in_half, const float *scal
                                   int bits, int mode, abq_stream_t stream);
 
 /*
+ * Quantise-on-load: fp16 weights [N][K] -> unsigned w-bit codes written as bit-planes [bits][N][K/32] (the layout
+ * abq_pack_int32 writes), fp16 scale and u8 zero point per output channel (group_size 0: [N]) or per run of group_size
+ * input features (a multiple of 32 dividing K: [N][K/group_size]); dequantised weight = (code - zero) * scale.  Min/max
+ * calibration and code rule of the reference's quantiser (algorithm/quantize/quantizer.py:111-132, 149-179, without
+ * learnable clipping), in fp32; `symmetric` picks its symmetric variant (quantizer.py:163-167).  Codes and zero points are
+ * clamped into 0 .. 2^bits - 1, the range the planes can hold (the reference's 1/2-bit "bit balance" allows 2^bits).
+ * The reference has no GPU counterpart: its FasterTransformer loader expects planes packed offline
+ * (LlamaDecoderLayerWeight.cc:377-403) and random-initialises what it does not find.
+ */
+ABQ_API abq_status abq_quantize_weights_half(const void *w_half, int N, int K, int bits, int group_size, int symmetric, void *planes,
+                                             void *scale_half, uint8_t *zero, abq_stream_t stream);
+
+/*
  * Bytes of the prepared copy of W that a decode-shape plan (route I8_MMA) with ABQ_FLAG_WEIGHTS_PREPARED reads through
  * params->w_prepared: the planes' own w_bits * N * K / 8 bytes (N rounded up to 16) plus, with per-group scales, 4
  * bytes per row and 128 input features.  Depends on N, K, w_bits, scale_mode, x_bits / x_signed only.  0 = this problem
@@ -213,12 +254,13 @@ ABQ_API abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_str
  *                mappings, e.g. torch symmetric memory `buffer_ptrs_dev`); bufs_dev[rank] is the local one, already
  *                written by earlier work on `stream`
  *   signals_dev  device array of `world` pointers to the ranks' signal pads; uint32 words signal_offset .. signal_offset +
- *                world - 1 of every pad belong to this call site and are zero before first use
+ *                2 * world - 1 of every pad belong to this call site and are zero before first use
  *   out          local result, n_halves fp16 values (n_halves % 8 == 0); must not alias a partial buffer
  *   counter      two device uint32, zero before first use: the call count (lets a CUDA graph replay the launch) and a
  *                block ticket
- * Every rank adds in rank order in fp32: all ranks get the same bits.  A partial buffer may be written again only
- * after another all-reduce of the same ranks has completed.  The wait for the peers is bounded (status_word).
+ * Every rank adds in rank order in fp32: all ranks get the same bits.  The call returns (on the stream) only after every
+ * peer has read this rank's buffer, so the buffer may be rewritten by whatever comes next, and one call site can be used
+ * back to back.  The waits for the peers are bounded (status_word).  abq_fused_allreduce does the same sum inside the GEMM.
  */
 ABQ_API abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world,
                                            int signal_offset, void *out, long n_halves, uint32_t *counter, int *status_word,

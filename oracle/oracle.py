@@ -293,3 +293,29 @@ def ref_compute_ref(w_planes: np.ndarray, x_planes: np.ndarray, signed: bool) ->
     out = np.empty((M, N), dtype=np.int32)
     ref().compute_ref(_p(w, _i32p), _p(x, _i32p), _p(out, _i32p), M, N, kw * 32, wb, xb, bool(signed))
     return out
+
+
+def quantize_weights_minmax(w_half: np.ndarray, bits: int, group: int | None = None, symmetric: bool = False):
+    """Weight quantiser of the reference's PTQ side restated in float32 (algorithm/quantize/quantizer.py:149-179 min/max
+    calibration without learnable clipping; :111-132 code rule): returns (codes int32 [N][K], scale fp16 [N][G], zero u8
+    [N][G]) with G = K / group (1 for per-channel).  Codes and zero points are clamped into 0 .. 2^bits - 1, the range
+    bit-planes can hold (the reference lets 1- and 2-bit codes reach 2^bits, :66-68, and the zero point leave the range)."""
+    w = np.ascontiguousarray(w_half, dtype=np.float16).astype(np.float32)
+    N, K = w.shape
+    g = group if group else K
+    x = w.reshape(N, K // g, g)
+    lo, hi = x.min(axis=2), x.max(axis=2)
+    qmax = np.float32((1 << bits) - 1)
+    if symmetric:
+        scale = np.maximum(np.abs(lo), np.abs(hi)) / np.float32((1 << (bits - 1)) - 1)
+        scale = np.clip(scale, np.float32(1e-5), np.float32(1e4)).astype(np.float32)
+        zero = np.full_like(scale, (1 << (bits - 1)) - 1)
+    else:
+        levels = np.float32((1 << bits) if bits <= 2 else (1 << bits) - 1)
+        scale = ((hi - lo).astype(np.float32) / levels).astype(np.float32)
+        scale = np.clip(scale, np.float32(1e-5), np.float32(1e4)).astype(np.float32)
+        zero = np.rint(np.clip((-lo / scale).astype(np.float32), np.float32(-1e4), np.float32(1e4))).astype(np.float32)
+        zero = np.clip(zero, np.float32(0), qmax)
+    codes = np.rint((x / scale[:, :, None]).astype(np.float32)).astype(np.float32) + zero[:, :, None]
+    codes = np.clip(codes, np.float32(0), qmax).astype(np.int32).reshape(N, K)
+    return codes, scale.astype(np.float16), zero.astype(np.uint8)

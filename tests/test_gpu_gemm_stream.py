@@ -58,7 +58,7 @@ def test_int32_bit_exact(abq, oracle, cuda, case):
     assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} of {got.size} differ"
 
 
-@pytest.mark.parametrize("env", [{"ABQ_STREAM_FULL": "1"}, {"ABQ_STREAM_CU": "8", "ABQ_STREAM_RING": "2"}, {"ABQ_STREAM_SLICES": "3"},
+@pytest.mark.parametrize("env", [{"ABQ_STREAM_FULL": "1"}, {"ABQ_STREAM_MP": "8", "ABQ_STREAM_RING": "2"}, {"ABQ_STREAM_SLICES": "3"},
                                  {"ABQ_STREAM_WARPS": "4", "ABQ_STREAM_CTAS": "37"}, {"ABQ_STREAM_WARPS": "16", "ABQ_STREAM_FULL": "1", "ABQ_STREAM_CTAS": "296"}],
                          ids=lambda e: ",".join(f"{k[11:]}={v}" for k, v in e.items()))
 @pytest.mark.parametrize("M,q", [(1, 2), (4, 3), (8, 4), (16, 2)])

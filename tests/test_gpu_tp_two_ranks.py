@@ -1,4 +1,5 @@
-"""Two ranks on two GPUs: the tensor-parallel block linears with the library's one-shot all-reduce over peer memory give,
+"""Two ranks on two GPUs: the tensor-parallel block linears with the all-reduce fused into the row-parallel GEMM, and with
+the library's one-shot all-reduce kernel over peer memory, give,
 bit for bit, what the same block gives with NCCL all-reduces, and (within the tolerance of the one-GPU test) what the unsharded
 block gives when the CPU oracle does the GEMMs.  Skipped on a box with one GPU."""
 import os
@@ -23,4 +24,5 @@ def test_peer_all_reduce_equals_nccl(cuda):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert res.stdout.count("PEER_EQUALS_NCCL True") == 2, res.stdout[-2000:]
+    assert res.stdout.count("FUSED_EQUALS_NCCL True") == 2, res.stdout[-2000:]
     assert res.stdout.count("MATCHES_UNSHARDED_ORACLE True") == 2, res.stdout[-2000:]

@@ -1,5 +1,6 @@
 """Helper of test_gpu_tp_two_ranks.py, run under torch.distributed.run with two ranks (one GPU each): the block linears
-with the library's one-shot peer all-reduce against the same block with torch.distributed (NCCL) all-reduces."""
+with the all-reduce fused into the row-parallel GEMMs, and with the library's one-shot peer all-reduce kernel, against
+the same block with torch.distributed (NCCL) all-reduces and against the unsharded block computed by the CPU oracle."""
 import importlib.util
 import os
 import sys
@@ -33,10 +34,10 @@ def main():
         zero = torch.randint(0, 1 << q, (sp.out_features,), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8)
         weights.append((codes, scale, zero))
     outs = {}
-    for mode in ("0", "1"):
-        os.environ["ABQ_TP_NCCL"] = mode
+    for mode in ("fused", "peer", "nccl"):
+        os.environ["ABQ_TP_REDUCE"] = mode
         be = tp.AbqBackend(abq, torch, dist, x_bits=8, x_scale=8.0, max_tokens=32)
-        assert be.peer_reduce == (mode == "0")
+        assert be.reduce_kind == mode and be.peer_reduce == (mode != "nccl")
         block = tp.TensorParallelBlockLinears(be, hidden, ffn, rank, world, weights, q, 0)
         for M in (1, 8, 32):
             gen.manual_seed(M)
@@ -45,9 +46,20 @@ def main():
                 y = block.forward(x)
             torch.cuda.synchronize()
             outs[(mode, M)] = y.clone()
+        # one call site used back to back with data that changes from call to call: a rank that runs ahead must not
+        # overwrite what its peer is still adding up
+        gen.manual_seed(99)
+        xs = [torch.randn((8, hidden), device="cuda", generator=gen).half() for _ in range(12)]
+        ys = [block.forward(x).clone() for x in xs]   # no synchronisation between the calls
+        torch.cuda.synchronize()
+        outs[(mode, "chain")] = torch.stack(ys)
         assert int(be.status.item()) == 0
-    ok = all(torch.equal(outs[("0", M)], outs[("1", M)]) for M in (1, 8, 32))
+        del block, be
+    keys = (1, 8, 32, "chain")
+    ok = all(torch.equal(outs[("peer", M)], outs[("nccl", M)]) for M in keys)
     print(f"rank {rank} PEER_EQUALS_NCCL {ok}", flush=True)
+    ok = all(torch.equal(outs[("fused", M)], outs[("nccl", M)]) for M in keys)
+    print(f"rank {rank} FUSED_EQUALS_NCCL {ok}", flush=True)
 
     # ... and against the unsharded block computed by the CPU oracle (one rank, numpy stand-in for the GEMMs): what the
     # two ranks produce together is the model's result, not merely the same thing twice.  Tolerance of the one-GPU test:
@@ -61,7 +73,7 @@ def main():
         gen.manual_seed(M)
         x = torch.randn((M, hidden), device="cuda", generator=gen).half()
         ref = whole.forward(x.cpu().numpy()).astype(np.float64)
-        got = outs[("0", M)].cpu().numpy().astype(np.float64)
+        got = outs[("fused", M)].cpu().numpy().astype(np.float64)
         err = np.abs(got - ref)
         close = close and bool(np.all(err <= 2.0 ** -6 * np.abs(ref) + 2.0 ** -7 * np.abs(ref).max()))
     print(f"rank {rank} MATCHES_UNSHARDED_ORACLE {close}", flush=True)
