@@ -59,10 +59,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         list(ex.map(compile_one, jobs))
     objs = [OBJ / (s.stem + ".o") for s in sources()]
     if force or jobs or _stale(LIB, objs):
-        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+        cmd = [NVCC, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stderr}")
+    table = PKG / "abq_tune_table.txt"  # the planner looks for its tuning table beside the library
+    if table.exists():
+        (LIB.parent / table.name).write_bytes(table.read_bytes())
     return LIB
 
 

@@ -1,6 +1,12 @@
 // Decode route over prepared weights (stream layout, gemm_stream_kernel.cuh): planner, load-time re-layout and launch
 // entry.  The kernel is instantiated per weight width in gemm_stream_w2.cu .. gemm_stream_w8.cu.
+#include <dlfcn.h>
+
+#include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <string>
+#include <vector>
 
 #include "gemm_stream_kernel.cuh"
 
@@ -11,7 +17,7 @@ namespace {
 // What abq_gemm_init decided for this route, kept in the state's route-specific words (tmap[1]).
 struct StreamPlan {
     int magic;
-    int nw, cu, ring, prefill, slices, units_per_slice, ctas_per_slice, MT, MP, grouped, unit_bytes, max_tiles_per_cta;
+    int uw, nw, cu, ring, prefill, slices, units_per_slice, ctas_per_slice, MT, MP, grouped, unit_bytes, max_tiles_per_cta;
 };
 constexpr int kStreamMagic = 0x5354524d;
 
@@ -25,7 +31,95 @@ int device_sms()
 
 bool width_supported(int q) { return q == 2 || q == 3 || q == 4 || q == 8; }
 
-int unit_bytes_of(const abq_gemm_params &p) { return p.w_bits * 256 + (p.scale_mode == ABQ_SCALE_GROUP ? 64 : 0); }
+// Launch-shape choices that override the planner's heuristic; 0 = not given.  They come from environment variables
+// (ABQ_STREAM_MP / _CU / _RING / _WARPS / _FULL / _CTAS / _SLICES / _PREFILL: tuning runs) or, failing that, from the
+// entry of this problem in the tuning table -- the successor of the reference's "time every configuration, keep the best
+// per shape" (engine/test/test_mma/test_mma.h:33-46), written by abq-llm_b200/tune.py.
+struct StreamHints {
+    int mp, cu, ring, warps, full, ctas, slices, prefill;
+    int planes; // 1: this problem runs faster on the kernel that reads the planes themselves (no stream plan)
+};
+
+struct TuneEntry {
+    int w_bits, x_bits, rows_class, N, K, grouped, group_size;
+    StreamHints h;
+};
+
+int rows_class_of(int M)
+{
+    const int rows = M < 16 ? M : 16;
+    return rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : rows <= 8 ? 8 : 16;
+}
+
+// Table file: text, one entry per line, '#' starts a comment:
+//   w_bits x_bits rows_class N K grouped group_size : mp cu ring warps full ctas slices prefill planes
+// Path: ABQ_TUNE_TABLE, else abq_tune_table.txt beside the shared library.  Read once per process.
+const std::vector<TuneEntry> &tune_table()
+{
+    static std::vector<TuneEntry> table;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        std::string path;
+        if (const char *e = std::getenv("ABQ_TUNE_TABLE")) {
+            path = e;
+        } else {
+            Dl_info info;
+            if (dladdr(reinterpret_cast<const void *>(&rows_class_of), &info) && info.dli_fname) {
+                path = info.dli_fname;
+                const size_t slash = path.find_last_of('/');
+                path = (slash == std::string::npos ? std::string(".") : path.substr(0, slash)) + "/abq_tune_table.txt";
+            }
+        }
+        if (path.empty())
+            return;
+        FILE *f = std::fopen(path.c_str(), "r");
+        if (!f)
+            return;
+        char line[512];
+        while (std::fgets(line, sizeof(line), f)) {
+            if (line[0] == '#')
+                continue;
+            TuneEntry t = {};
+            if (std::sscanf(line, "%d %d %d %d %d %d %d : %d %d %d %d %d %d %d %d %d", &t.w_bits, &t.x_bits, &t.rows_class, &t.N, &t.K, &t.grouped,
+                            &t.group_size, &t.h.mp, &t.h.cu, &t.h.ring, &t.h.warps, &t.h.full, &t.h.ctas, &t.h.slices, &t.h.prefill, &t.h.planes) == 16)
+                table.push_back(t);
+        }
+        std::fclose(f);
+    });
+    return table;
+}
+
+StreamHints hints_for(const abq_gemm_params &p)
+{
+    StreamHints h = {};
+    if (!env_int("ABQ_TUNE_IGNORE", 0)) {
+        const int grouped = p.scale_mode == ABQ_SCALE_GROUP;
+        for (const TuneEntry &t : tune_table()) {
+            if (t.w_bits == p.w_bits && t.x_bits == p.x_bits && t.rows_class == rows_class_of(p.M) && t.N == p.N && t.K == p.K && t.grouped == grouped &&
+                (!grouped || t.group_size == p.group_size)) {
+                h = t.h;
+                break;
+            }
+        }
+    }
+    const struct {
+        const char *name;
+        int *field;
+    } env[] = { { "ABQ_STREAM_MP", &h.mp },     { "ABQ_STREAM_CU", &h.cu },     { "ABQ_STREAM_RING", &h.ring },     { "ABQ_STREAM_WARPS", &h.warps },
+                { "ABQ_STREAM_FULL", &h.full }, { "ABQ_STREAM_CTAS", &h.ctas }, { "ABQ_STREAM_SLICES", &h.slices }, { "ABQ_STREAM_PREFILL", &h.prefill },
+                { "ABQ_STREAM_PLANES", &h.planes } };
+    for (const auto &e : env) {
+        const int v = env_int(e.name, -1);
+        if (v >= 0)
+            *e.field = v;
+    }
+    return h;
+}
+
+// input features per unit: 128, or 64 when the scale groups are an odd multiple of 64 wide
+int unit_width_of(const abq_gemm_params &p) { return p.scale_mode == ABQ_SCALE_GROUP && p.group_size % 128 != 0 ? 64 : 128; }
+
+int unit_bytes_of(const abq_gemm_params &p) { return p.w_bits * 2 * unit_width_of(p) + (p.scale_mode == ABQ_SCALE_GROUP ? 64 : 0); }
 
 } // namespace
 
@@ -35,7 +129,7 @@ bool stream_supported(const abq_gemm_params &p)
         return false;
     if (!p.x_signed && p.x_bits == 8)
         return false; // unsigned 8-bit activations need the u8 x u8 MMA: the plane kernel has it
-    if (p.scale_mode == ABQ_SCALE_GROUP && p.group_size % 128 != 0)
+    if (p.scale_mode == ABQ_SCALE_GROUP && p.group_size % 64 != 0)
         return false;
     return true;
 }
@@ -44,7 +138,7 @@ size_t stream_prepared_bytes(const abq_gemm_params &p)
 {
     if (!stream_supported(p))
         return 0;
-    return (size_t)((p.N + 15) / 16) * (p.K / 128) * unit_bytes_of(p);
+    return (size_t)((p.N + 15) / 16) * (p.K / unit_width_of(p)) * unit_bytes_of(p);
 }
 
 // Launch shape.  Preference: a CTA small enough for two to share an SM (so that the next GEMM's CTAs move in and fetch
@@ -58,23 +152,28 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
     P->grouped = grouped;
     P->MT = rows > 8 ? 2 : 1;
     P->unit_bytes = unit_bytes_of(p);
+    P->uw = unit_width_of(p);
     // token rows per column block: the fewest that hold the tokens, but more (fewer units per fold) while a block of
     // 8 / MP units would be too large a chunk for the ring
+    const StreamHints H = hints_for(p);
+    if (H.planes > 0 && !p.allreduce)
+        return false;
     int MP = P->MT == 2 || !grouped ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
     while (MP < 8 && (8 / MP) * P->unit_bytes > 5120)
         MP *= 2;
-    MP = env_int("ABQ_STREAM_MP", MP);
+    if (H.mp > 0 && P->MT == 1 && grouped)
+        MP = H.mp;
     if ((MP != 1 && MP != 2 && MP != 4 && MP != 8) || MP < (rows > 8 ? 8 : rows) || ((P->MT == 2 || !grouped) && MP != 8))
         return false;
     P->MP = MP;
     const int GS = grouped && P->MT == 1 ? 8 / P->MP : 1;
     const int MR = P->MT == 2 ? 16 : P->MP;
-    const int units = p.K / 128;
+    const int units = p.K / P->uw;
     const int tiles = (p.N + 15) / 16;
     const int sms = device_sms();
-    const int force_full = env_int("ABQ_STREAM_FULL", 0);
-    const int force_slices = env_int("ABQ_STREAM_SLICES", 0);
-    const int force_warps = env_int("ABQ_STREAM_WARPS", 0);
+    const int force_full = H.full;
+    const int force_slices = H.slices;
+    const int force_warps = H.warps;
     if (force_warps < 0 || force_warps > kStreamMaxWarps)
         return false;
     // Preference: no K split before a K split (its partial sums go through global memory); then eight warps in a CTA that
@@ -92,7 +191,7 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
             const size_t budget = shape[0] ? 112 * 1024 : 226 * 1024;
             {
                 const int nw = force_warps ? force_warps : shape[1];
-                int cu0 = env_int("ABQ_STREAM_CU", 0);
+                int cu0 = H.cu;
                 const bool cu_forced = cu0 > 0;
                 if (!cu_forced) {
                     cu0 = (4608 / P->unit_bytes) / GS * GS;
@@ -106,28 +205,27 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
                 int ups = (units + sl - 1) / sl;
                 ups = (ups + cu - 1) / cu * cu;
                 const int slices = (units + ups - 1) / ups; // drop slices that would be empty
-                int cps = env_int("ABQ_STREAM_CTAS", sms) / slices;
+                int cps = (H.ctas > 0 ? H.ctas : sms) / slices;
                 cps = cps > tiles ? tiles : cps;
                 cps = cps < 1 ? 1 : cps;
                 const int max_T = (tiles + cps - 1) / cps;
-                const StreamSmem L0 = stream_smem_layout(nw, 0, cu, P->unit_bytes, ups, MR, max_T, P->MT);
-                if (L0.total < budget && max_T <= 64) { // (the kernel keeps a 64-entry table of its tiles)
+                const StreamSmem L0 = stream_smem_layout(nw, 0, cu, P->unit_bytes, ups, MR, max_T, P->MT, P->uw);
+                if (L0.total < budget && max_T <= 64 && (long long)tiles * (cps + 1) < (1LL << 31)) { // (the kernel keeps a 64-entry table of its tiles)
                     int ring = (int)((budget - L0.total) / ((size_t)nw * cu * P->unit_bytes));
                     ring = ring > kStreamMaxRing ? kStreamMaxRing : ring;
-                    const int forced = env_int("ABQ_STREAM_RING", 0);
+                    const int forced = H.ring;
                     if (forced > 0 && forced <= ring)
                         ring = forced;
                     if (ring >= 2) {
                         P->nw = nw;
                         P->cu = cu;
                         P->ring = ring;
-                        P->prefill = env_int("ABQ_STREAM_PREFILL", ring);
-                        P->prefill = P->prefill < 0 ? 0 : (P->prefill > ring ? ring : P->prefill);
+                        P->prefill = H.prefill > 0 ? (H.prefill > ring ? ring : H.prefill) : ring;
                         P->slices = slices;
                         P->units_per_slice = ups;
                         P->ctas_per_slice = cps;
                         P->max_tiles_per_cta = max_T;
-                        *smem_bytes = stream_smem_layout(nw, ring, cu, P->unit_bytes, ups, MR, max_T, P->MT).total;
+                        *smem_bytes = stream_smem_layout(nw, ring, cu, P->unit_bytes, ups, MR, max_T, P->MT, P->uw).total;
                         return true;
                     }
                 }
@@ -188,15 +286,16 @@ cudaError_t stream_prepare_weights(const abq_gemm_state *st, cudaStream_t stream
 {
     const abq_gemm_params &p = st->p;
     const int grouped = p.scale_mode == ABQ_SCALE_GROUP;
-    const int gps = grouped ? p.group_size / 128 : 1, sg = grouped ? p.K / p.group_size : 1;
+    const int uw = unit_width_of(p);
+    const int gps = grouped ? p.group_size / uw : 1, sg = grouped ? p.K / p.group_size : 1;
     const uint32_t *planes = reinterpret_cast<const uint32_t *>(p.W);
     const __half *ws = reinterpret_cast<const __half *>(p.w_scale);
     uint8_t *out = reinterpret_cast<uint8_t *>(p.w_prepared);
     switch (p.w_bits) {
-    case 2: return stream_prepare_w2(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
-    case 3: return stream_prepare_w3(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
-    case 4: return stream_prepare_w4(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
-    case 8: return stream_prepare_w8(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, gps, sg, stream);
+    case 2: return stream_prepare_w2(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, uw, gps, sg, stream);
+    case 3: return stream_prepare_w3(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, uw, gps, sg, stream);
+    case 4: return stream_prepare_w4(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, uw, gps, sg, stream);
+    case 8: return stream_prepare_w8(planes, ws, p.w_zero, out, p.N, p.K, p.w_signed, grouped, uw, gps, sg, stream);
     }
     return cudaErrorInvalidValue;
 }
@@ -210,7 +309,8 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.N = p.N;
     a.K = p.K;
     a.tiles = (p.N + 15) / 16;
-    a.units = p.K / 128;
+    a.uw = P.uw;
+    a.units = p.K / P.uw;
     a.unit_bytes = P.unit_bytes;
     a.slices = P.slices;
     a.units_per_slice = P.units_per_slice;

@@ -51,8 +51,9 @@ struct StreamAllreduce {
 struct StreamArgs {
     int M, N, K;
     int tiles;           // ceil(N / 16)
-    int units;           // K / 128: units per tile in the stream
-    int unit_bytes;      // Q * 256 (+ 64 with group parameters)
+    int uw;              // input features per unit: 128, or 64 when the scale groups are 64 wide
+    int units;           // K / uw: units per tile in the stream
+    int unit_bytes;      // Q * 2 * uw (+ 64 with group parameters)
     int slices;          // K split over CTAs (1 unless the records of all K do not fit in shared memory)
     int units_per_slice; // multiple of cu
     int ctas_per_slice;
@@ -98,11 +99,12 @@ __device__ __forceinline__ void trace_mark(const StreamArgs &a, unsigned slot, i
 //   high half) of MMA step j of the unit = the row's code at feature 32 t + 31 - 8 y - (2 j + (a >> 1)).
 //   pack():   the codes of a lane as bytes c[row 0/1][s = 2 j + h] (byte y in bits 8y..8y+7) -> its kWords words
 //   expand(): shared memory -> R[j][a] = code bytes * 2^(kShift * set_of(j))
-template <int Q>
+template <int Q, int UW = 128>
 struct StreamFormat;
 
 template <>
-struct StreamFormat<2> {
+struct StreamFormat<2, 128> {
+    static constexpr int kSteps = 4;
     static constexpr int kWords = 4, kSets = 2, kShift = 2;
     __host__ __device__ static constexpr int set_of(int j) { return j & 1; }
     __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
@@ -131,7 +133,8 @@ struct StreamFormat<2> {
 };
 
 template <>
-struct StreamFormat<4> {
+struct StreamFormat<4, 128> {
+    static constexpr int kSteps = 4;
     static constexpr int kWords = 8, kSets = 2, kShift = 4;
     __host__ __device__ static constexpr int set_of(int j) { return j & 1; }
     __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
@@ -161,7 +164,8 @@ struct StreamFormat<4> {
 // slot_of(j, h) below; slots 0, 3, 6, 2 come out times 1, slots 1, 4, 7, 5 times 8.
 //   A = c0 | c1 << 3 | (c2 & 3) << 6;  B = c3 | c4 << 3 | (c5 & 3) << 6;  C = c6 | c7 << 3 | (c2 >> 2) << 6 | (c5 >> 2) << 7
 template <>
-struct StreamFormat<3> {
+struct StreamFormat<3, 128> {
+    static constexpr int kSteps = 4;
     static constexpr int kWords = 6, kSets = 2, kShift = 3;
     __host__ __device__ static constexpr int set_of(int j) { return j >> 1; }
     __host__ __device__ static constexpr int slot_of(int j, int h)
@@ -220,7 +224,8 @@ struct StreamFormat<3> {
 };
 
 template <>
-struct StreamFormat<8> {
+struct StreamFormat<8, 128> {
+    static constexpr int kSteps = 4;
     static constexpr int kWords = 16, kSets = 1, kShift = 0;
     __host__ __device__ static constexpr int set_of(int) { return 0; }
     __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
@@ -254,24 +259,145 @@ __host__ __device__ constexpr bool stream_first_in_set(int j)
     return true;
 }
 
-// Where lane `lane` finds word i of its kWords words inside a unit's code block (16-byte pieces first, lane-major).
-template <int Q>
+// Where lane `lane` finds word i of its kWords words inside a unit's code block: 16-byte pieces first (512 bytes per piece
+// index), then one 8-byte piece, then one 4-byte piece, each lane-major -- what the formats' expand() functions read.
+template <int Q, int UW>
 __host__ __device__ constexpr int stream_word_offset(int lane, int i)
 {
-    constexpr int kWords = StreamFormat<Q>::kWords;
-    constexpr int full = kWords / 4; // 16-byte pieces per lane
-    return i < full * 4 ? (i / 4) * 512 + lane * 16 + (i % 4) * 4 : full * 512 + lane * ((kWords % 4) * 4) + (i - full * 4) * 4;
+    constexpr int kWords = StreamFormat<Q, UW>::kWords;
+    constexpr int n16 = kWords / 4, has8 = (kWords % 4) >= 2 ? 1 : 0;
+    if (i < n16 * 4)
+        return (i / 4) * 512 + lane * 16 + (i % 4) * 4;
+    if (has8 && i < n16 * 4 + 2)
+        return n16 * 512 + lane * 8 + (i - n16 * 4) * 4;
+    return n16 * 512 + has8 * 256 + lane * 4;
 }
+
+// ---- 64-feature units (scale groups of 64): a lane owns rows g and g + 8 and 16 features; the unit has two MMA steps.
+// Lane t takes its 16 features from the 32-feature run t / 2 of the unit: code(j, a, y) = the row's code at element
+// 31 - 8 y - (4 (t % 2) + 2 j + (a >> 1)) of that run.  All four A registers of a step come out with the same power of two.
+template <>
+struct StreamFormat<2, 64> {
+    static constexpr int kSteps = 2, kWords = 2, kSets = 2, kShift = 2;
+    __host__ __device__ static constexpr int set_of(int j) { return j; }
+    // word 0: a0, a1 of both steps; word 1: a2, a3.  Bits 0-1: (j 0, first a), 2-3: (j 1, first a), 4-5: (j 0, second a), 6-7: (j 1, second a)
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            w[h] = c[0][h] | (c[0][2 + h] << 2) | (c[1][h] << 4) | (c[1][2 + h] << 6);
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[kSteps][4])
+    {
+        const uint2 v = *reinterpret_cast<const uint2 *>(unit + lane * 8);
+        const uint32_t w[2] = { v.x, v.y };
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t hi = w[h] >> 4;
+            R[0][2 * h] = w[h] & 0x03030303u;     // row g
+            R[1][2 * h] = w[h] & 0x0c0c0c0cu;
+            R[0][2 * h + 1] = hi & 0x03030303u;   // row g + 8
+            R[1][2 * h + 1] = hi & 0x0c0c0c0cu;
+        }
+    }
+};
+
+template <>
+struct StreamFormat<4, 64> {
+    static constexpr int kSteps = 2, kWords = 4, kSets = 2, kShift = 4;
+    __host__ __device__ static constexpr int set_of(int j) { return j; }
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+            w[a] = c[a & 1][a >> 1] | (c[a & 1][2 + (a >> 1)] << 4);
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[kSteps][4])
+    {
+        const uint4 v = *reinterpret_cast<const uint4 *>(unit + lane * 16);
+        const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            R[0][a] = w[a] & 0x0f0f0f0fu;
+            R[1][a] = w[a] & 0xf0f0f0f0u;
+        }
+    }
+};
+
+// three bits: the eight codes of a byte lane are the lane's (step, register) pairs; slots 0, 3, 6, 2 (times 1) hold step 0's
+// registers a0..a3, slots 1, 4, 7, 5 (times 8) step 1's.  Byte layout as the 128-feature format.
+template <>
+struct StreamFormat<3, 64> {
+    static constexpr int kSteps = 2, kWords = 3, kSets = 2, kShift = 3;
+    __host__ __device__ static constexpr int set_of(int j) { return j; }
+    __host__ __device__ static constexpr int slot_of(int j, int a) { return j == 0 ? (a == 0 ? 0 : a == 1 ? 3 : a == 2 ? 6 : 2) : (a == 0 ? 1 : a == 1 ? 4 : a == 2 ? 7 : 5); }
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+        uint32_t s[8];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+                s[slot_of(j, a)] = c[a & 1][2 * j + (a >> 1)];
+        w[0] = s[0] | (s[1] << 3) | ((s[2] & 0x03030303u) << 6);
+        w[1] = s[3] | (s[4] << 3) | ((s[5] & 0x03030303u) << 6);
+        w[2] = s[6] | (s[7] << 3) | (((s[2] >> 2) & 0x01010101u) << 6) | (((s[5] >> 2) & 0x01010101u) << 7);
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[kSteps][4])
+    {
+        const uint2 v = *reinterpret_cast<const uint2 *>(unit + lane * 8);
+        const uint32_t A = v.x, B = v.y, C = *reinterpret_cast<const uint32_t *>(unit + 256 + lane * 4);
+        uint32_t s[8];
+        s[0] = A & 0x07070707u;
+        s[1] = A & 0x38383838u;
+        s[3] = B & 0x07070707u;
+        s[4] = B & 0x38383838u;
+        s[6] = C & 0x07070707u;
+        s[7] = C & 0x38383838u;
+        s[2] = ((A >> 6) & 0x03030303u) | ((C >> 4) & 0x04040404u);
+        s[5] = ((B >> 3) & 0x18181818u) | ((C >> 2) & 0x20202020u);
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+                R[j][a] = s[slot_of(j, a)];
+    }
+};
+
+template <>
+struct StreamFormat<8, 64> {
+    static constexpr int kSteps = 2, kWords = 8, kSets = 1, kShift = 0;
+    __host__ __device__ static constexpr int set_of(int) { return 0; }
+    __device__ static void pack(const uint32_t (&c)[2][8], uint32_t (&w)[kWords])
+    {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+                w[j * 4 + a] = c[a & 1][2 * j + (a >> 1)];
+    }
+    __device__ static __forceinline__ void expand(const uint8_t *unit, int lane, uint32_t (&R)[kSteps][4])
+    {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(unit + j * 512 + lane * 16);
+            R[j][0] = v.x;
+            R[j][1] = v.y;
+            R[j][2] = v.z;
+            R[j][3] = v.w;
+        }
+    }
+};
 
 // ------------------------------------------------------------------------------------------ load-time re-layout
 // planes [Q][N][K/32] (+ per-group fp16 scale / u8 zero point) -> stream layout.  One thread per (tile, unit, lane).
-template <int Q>
+template <int Q, int UW>
 __global__ void __launch_bounds__(256) prepare_stream_kernel(const uint32_t *__restrict__ planes, const __half *__restrict__ w_scale,
                                                              const uint8_t *__restrict__ w_zero, uint8_t *__restrict__ out, int N, int K, int w_signed,
-                                                             int grouped, int groups_per_scale, int scale_groups)
+                                                             int grouped, int units_per_scale, int scale_groups)
 {
-    using F = StreamFormat<Q>;
-    const int units = K >> 7, KW = K >> 5;
+    using F = StreamFormat<Q, UW>;
+    const int units = K / UW, KW = K >> 5;
     const int tiles = (N + 15) >> 4;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)tiles * units * 32)
@@ -279,23 +405,28 @@ __global__ void __launch_bounds__(256) prepare_stream_kernel(const uint32_t *__r
     const int lane = (int)(idx & 31);
     const int u = (int)((idx >> 5) % units), r = (int)((idx >> 5) / units);
     const int g = lane >> 2, t = lane & 3;
-    const int unit_bytes = Q * 256 + (grouped ? 64 : 0);
+    const int unit_bytes = Q * 2 * UW + (grouped ? 64 : 0);
     uint8_t *unit = out + ((size_t)r * units + u) * unit_bytes;
     uint32_t c[2][8];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int row = r * 16 + g + 8 * h;
+        const int kw = UW == 128 ? u * 4 + t : u * 2 + (t >> 1); // the 32-feature run this lane's codes come from
         uint32_t p[Q];
 #pragma unroll
         for (int b = 0; b < Q; ++b)
-            p[b] = row < N ? planes[((size_t)b * N + row) * KW + u * 4 + t] : 0u;
-        planes_to_bytes<Q>(p, w_signed != 0 && row < N, c[h]); // two's complement -> offset codes: top plane flipped
+            p[b] = row < N ? planes[((size_t)b * N + row) * KW + kw] : 0u;
+        uint32_t full[8];
+        planes_to_bytes<Q>(p, w_signed != 0 && row < N, full); // two's complement -> offset codes: top plane flipped
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            c[h][i] = UW == 128 ? full[i] : full[(4 * (t & 1) + i) & 7]; // 64-feature units: registers 4 (t % 2) .. + 3 of the run
     }
     uint32_t w[F::kWords];
     F::pack(c, w);
 #pragma unroll
     for (int i = 0; i < F::kWords; ++i)
-        *reinterpret_cast<uint32_t *>(unit + stream_word_offset<Q>(lane, i)) = w[i];
+        *reinterpret_cast<uint32_t *>(unit + stream_word_offset<Q, UW>(lane, i)) = w[i];
     if (grouped && t == 0) {
         const int zoff = w_signed ? (1 << (Q - 1)) : 0;
 #pragma unroll
@@ -303,29 +434,40 @@ __global__ void __launch_bounds__(256) prepare_stream_kernel(const uint32_t *__r
             const int row = r * 16 + g + 8 * h;
             uint32_t pk = 0;
             if (row < N) {
-                const size_t si = (size_t)row * scale_groups + u / groups_per_scale;
+                const size_t si = (size_t)row * scale_groups + u / units_per_scale;
                 pk = __float_as_uint(__half2float(w_scale[si])) | (uint32_t)(zoff + (w_zero ? (int)w_zero[si] : 0));
             }
-            *reinterpret_cast<uint32_t *>(unit + Q * 256 + (2 * g + h) * 4) = pk;
+            *reinterpret_cast<uint32_t *>(unit + Q * 2 * UW + (2 * g + h) * 4) = pk;
         }
     }
 }
 
 // ------------------------------------------------------------------------------------------ activation records
-// Store one expanded item (token m, 32-feature run t of unit ul) and, from lane t == 0 of each group of four, the unit's code sum.
-__device__ __forceinline__ void stream_store_item(uint8_t *rec_base, int *sums, int MR, int ul, int m, int t, const uint32_t (&r)[8], int sum, bool mine)
+// Store one expanded item (token m, 32-feature run kwl of this CTA's K range; a unit is uw / 32 consecutive runs) and, from
+// the first lane of each unit, the unit's code sum.
+__device__ __forceinline__ void stream_store_item(uint8_t *rec_base, int *sums, int MR, int uw, int kwl, int m, const uint32_t (&r)[8], int sum, bool mine)
 {
-    // the four 32-feature runs of a unit sit in four consecutive lanes (the item count per token is a multiple of 4)
+    // the runs of a unit sit in consecutive lanes (the item count per token is a multiple of the runs per unit)
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int sum4 = sum + __shfl_xor_sync(0xffffffffu, sum, 2);
     if (!mine)
         return;
-    uint8_t *dst = rec_base + ((size_t)ul * MR + m) * 128 + t * 32;
-    const int swz = (m & 1) << 4;
-    *reinterpret_cast<uint4 *>(dst + swz) = make_uint4(r[0], r[1], r[2], r[3]);
-    *reinterpret_cast<uint4 *>(dst + (16 ^ swz)) = make_uint4(r[4], r[5], r[6], r[7]);
-    if (t == 0)
-        sums[ul * MR + m] = sum;
+    if (uw == 128) {
+        const int ul = kwl >> 2, t = kwl & 3;
+        uint8_t *dst = rec_base + ((size_t)ul * MR + m) * 128 + t * 32;
+        const int swz = (m & 1) << 4;
+        *reinterpret_cast<uint4 *>(dst + swz) = make_uint4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<uint4 *>(dst + (16 ^ swz)) = make_uint4(r[4], r[5], r[6], r[7]);
+        if (t == 0)
+            sums[ul * MR + m] = sum4;
+    } else { // 64-feature units: lanes 2 w and 2 w + 1 of the MMA quad read the two halves of run w
+        const int ul = kwl >> 1, w = kwl & 1;
+        uint8_t *dst = rec_base + ((size_t)ul * MR + m) * 64 + w * 32;
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(r[4], r[5], r[6], r[7]);
+        if (w == 0)
+            sums[ul * MR + m] = sum;
+    }
 }
 
 __device__ __forceinline__ int stream_code_sum(const uint32_t (&r)[8], bool x_signed)
@@ -353,136 +495,106 @@ __device__ __forceinline__ void prefetch_l2(const void *p)
 // threads of the CTA (index arithmetic by a multiply-high, no division), a thread first requests the plane words of all B
 // items of a batch and then expands them (one round trip to L2 per batch, not per item), and the code is instantiated
 // per activation width so that only the path taken is ever fetched.
-// It is preceded, BEFORE the wait on the previous kernel, by a pass over the same items (WARM) that touches no activation
-// value: it asks for the lines the build will read to be brought into L2 -- which also walks the page table for them, the
-// larger part of a first access after gigabytes of weights have gone through the TLBs -- and writes the zero padding
-// (token rows and units beyond the real ones), so that the build itself only handles real items.
-template <int P, int B, bool WARM>
-__device__ __forceinline__ void stream_records_planes(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR)
+// It is preceded, BEFORE the wait on the previous kernel, by a rehearsal (warm == true): the very same instructions run
+// over the same items with the loads of activation values switched off (zeros instead), which (a) brings this code into the
+// instruction cache -- a CTA's first pass through cold code costs more than the arithmetic in it -- (b) asks for the
+// lines the build will read to be brought into L2, walking the page table for them, and (c) writes the zero padding
+// (token rows and units beyond the real ones).  The build then overwrites the records of the real items.
+template <int P, int B>
+__device__ __forceinline__ void stream_records_planes(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR, bool warm)
 {
-    const int words = n_pad * 4;
+    const int wsh = a.uw == 128 ? 2 : 1; // log2 of the 32-feature runs per unit
+    const int words = n_pad << wsh;
     const int items = MR * words;
     const uint32_t magic = 0xffffffffu / (uint32_t)words + 1u; // idx / words == umulhi(idx, magic) for idx * words < 2^32
     const int KW = a.K >> 5;
+#ifdef ABQ_STREAM_TRACE
+#define ABQ_RTRACE(slot, dep) if (!warm && a.trace && threadIdx.x == 0 && base == 0) a.trace[16 + (size_t)(*(volatile unsigned *)&trace_slot_g) * 16 + slot] = globaltimer_ns() + ((dep) == 0x9e3779b9u ? 1 : 0)
+#else
+#define ABQ_RTRACE(slot, dep)
+#endif
     for (int base = 0; base < items; base += blockDim.x * B) { // every lane of a warp takes every trip (shuffles inside)
         uint32_t pl[B][P];
         int mm[B], kk[B];
         bool live[B];
+        ABQ_RTRACE(11, 0u);
 #pragma unroll
         for (int i = 0; i < B; ++i) {
             const int idx = base + i * (int)blockDim.x + (int)threadIdx.x;
             mm[i] = (int)__umulhi((uint32_t)idx, magic);
             kk[i] = idx - mm[i] * words;
-            live[i] = idx < items && mm[i] < a.M && (kk[i] >> 2) < n_units;
-            const uint32_t *src = a.X + (size_t)mm[i] * KW + u_first * 4 + kk[i];
-            if (WARM) {
-                if (live[i] && (kk[i] & 31) == 0) { // one request per 128-byte line of every plane row
-#pragma unroll
-                    for (int b = 0; b < P; ++b)
-                        prefetch_l2(src + b * a.x_plane_words);
-                }
-            } else {
+            live[i] = idx < items && mm[i] < a.M && (kk[i] >> wsh) < n_units;
+            const uint32_t *src = a.X + (size_t)mm[i] * KW + (u_first << wsh) + kk[i];
+            if (warm && live[i] && (kk[i] & 31) == 0) { // one request per 128-byte line of every plane row
 #pragma unroll
                 for (int b = 0; b < P; ++b)
-                    pl[i][b] = live[i] ? __ldg(src + b * a.x_plane_words) : 0u;
+                    prefetch_l2(src + b * a.x_plane_words);
             }
+#pragma unroll
+            for (int b = 0; b < P; ++b)
+                pl[i][b] = (live[i] && !warm) ? __ldg(src + b * a.x_plane_words) : 0u;
         }
-#ifdef ABQ_STREAM_TRACE
-        if (!WARM && a.trace && threadIdx.x == 0 && base == 0)
-            a.trace[16 + (size_t)(*(volatile unsigned *)&trace_slot_g) * 16 + 7] = globaltimer_ns() + (pl[0][P - 1] & 0u); // after the loads have landed
-#endif
+        ABQ_RTRACE(12, 0u);
+        ABQ_RTRACE(7, pl[0][P - 1]);
 #pragma unroll
         for (int i = 0; i < B; ++i) {
             const int idx = base + i * (int)blockDim.x + (int)threadIdx.x;
             uint32_t r[8];
-            int sum = 0;
-            if (WARM) {
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    r[s] = 0;
-                stream_store_item(rec_base, sums, MR, kk[i] >> 2, mm[i], kk[i] & 3, r, 0, idx < items && !live[i]);
-            } else {
-                if (live[i]) {
-                    x_bytes<P>(pl[i], a.x_signed != 0, r);
-                    sum = stream_code_sum(r, a.x_signed != 0);
-                } else {
-#pragma unroll
-                    for (int s = 0; s < 8; ++s)
-                        r[s] = 0;
-                }
-                stream_store_item(rec_base, sums, MR, kk[i] >> 2, mm[i], kk[i] & 3, r, sum, live[i]);
-            }
+            x_bytes<P>(pl[i], a.x_signed != 0, r); // (zeros in, zeros out: no branch around the arithmetic)
+            const int sum = stream_code_sum(r, a.x_signed != 0);
+            ABQ_RTRACE(13, (uint32_t)sum);
+            stream_store_item(rec_base, sums, MR, a.uw, kk[i], mm[i], r, sum, warm ? idx < items : live[i]);
         }
+        ABQ_RTRACE(14, 0u);
     }
+#undef ABQ_RTRACE
 }
 
-template <bool WARM>
-__device__ __forceinline__ void stream_records_half(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR)
+__device__ __forceinline__ void stream_records_half(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR, bool warm)
 {
-    const int words = n_pad * 4;
+    const int wsh = a.uw == 128 ? 2 : 1;
+    const int words = n_pad << wsh;
     const int items = MR * words;
     const uint32_t magic = 0xffffffffu / (uint32_t)words + 1u;
-    const __half hscale = WARM ? __half() : __float2half(__ldg(a.x_qscale));
+    if (warm && threadIdx.x == 0)
+        prefetch_l2(a.x_qscale);
+    const __half hscale = warm ? __half() : __float2half(__ldg(a.x_qscale));
     for (int base = 0; base < items; base += blockDim.x) {
         const int idx = base + (int)threadIdx.x;
         const int m = (int)__umulhi((uint32_t)idx, magic), kwl = idx - m * words;
-        const bool live = idx < items && m < a.M && (kwl >> 2) < n_units;
-        const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.X) + (size_t)m * a.K + (size_t)(u_first * 4 + kwl) * 32);
+        const bool live = idx < items && m < a.M && (kwl >> wsh) < n_units;
+        const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.X) + (size_t)m * a.K + (size_t)((u_first << wsh) + kwl) * 32);
         uint32_t r[8];
-        int sum = 0;
 #pragma unroll
         for (int s = 0; s < 8; ++s)
             r[s] = 0;
-        if (WARM) {
-            if (live && (kwl & 1) == 0)
-                prefetch_l2(src); // 64 bytes per item: one request per 128-byte line
-            if (live && idx == 0)
-                prefetch_l2(a.x_qscale);
-            stream_store_item(rec_base, sums, MR, kwl >> 2, m, kwl & 3, r, 0, idx < items && !live);
-        } else {
-            if (live) {
-                x_bytes_from_half(src, hscale, a.x_bits, r);
-                sum = stream_code_sum(r, true);
-            }
-            stream_store_item(rec_base, sums, MR, kwl >> 2, m, kwl & 3, r, sum, live);
-        }
+        if (warm && live && (kwl & 1) == 0)
+            prefetch_l2(src); // 64 bytes per item: one request per 128-byte line
+        if (live && !warm)
+            x_bytes_from_half(src, hscale, a.x_bits, r);
+        const int sum = stream_code_sum(r, true);
+        stream_store_item(rec_base, sums, MR, a.uw, kwl, m, r, sum, warm ? idx < items : live);
     }
 }
 
 // Records of units [u_first, u_first + n_units) of this CTA's K range, zero-padded to n_pad units and MR token rows:
 // rec[(ul * MR + m) * 128 + t * 32 + {0, 16} ^ ((m & 1) << 4)] = the lane-t halves (registers 0..3 and 4..7 of x_bytes)
-// of token m, and sums[ul * MR + m] = the sum of its 128 codes.  warm: the pass before the dependency wait (see above).
-// One copy of this code per compile unit.
+// of token m, and sums[ul * MR + m] = the sum of its 128 codes (64-feature units: see stream_store_item).
+// warm: the rehearsal before the dependency wait (see above).  One copy of this code per compile unit.
 static __device__ __noinline__ void stream_build_records(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR,
                                                          bool warm)
 {
     if (a.x_qscale) {
-        if (warm)
-            stream_records_half<true>(a, rec_base, sums, u_first, n_units, n_pad, MR);
-        else
-            stream_records_half<false>(a, rec_base, sums, u_first, n_units, n_pad, MR);
+        stream_records_half(a, rec_base, sums, u_first, n_units, n_pad, MR, warm);
         return;
     }
-    if (warm) { // no arithmetic on activation values: one instantiation serves all widths
-        switch (a.x_bits) {
-        case 1: stream_records_planes<1, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        case 2: stream_records_planes<2, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        case 3: stream_records_planes<3, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        case 4: stream_records_planes<4, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        case 5: stream_records_planes<5, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        case 6: stream_records_planes<6, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        case 7: stream_records_planes<7, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        default: stream_records_planes<8, 4, true>(a, rec_base, sums, u_first, n_units, n_pad, MR); break;
-        }
-        return;
-    }
-    const bool one = MR * n_pad * 4 <= (int)blockDim.x; // one item per thread at most: no batching needed
+    const bool one = MR * n_pad * (a.uw / 32) <= (int)blockDim.x; // one item per thread at most: no batching needed
 #define ABQ_RECORDS_CASE(P)                                                                                      \
     case P:                                                                                                      \
         if (one)                                                                                                 \
-            stream_records_planes<P, 1, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);                  \
+            stream_records_planes<P, 1>(a, rec_base, sums, u_first, n_units, n_pad, MR, warm);                   \
         else                                                                                                     \
-            stream_records_planes<P, 4, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);                  \
+            stream_records_planes<P, 4>(a, rec_base, sums, u_first, n_units, n_pad, MR, warm);                   \
         break;
     switch (a.x_bits) {
         ABQ_RECORDS_CASE(1)
@@ -494,9 +606,9 @@ static __device__ __noinline__ void stream_build_records(const StreamArgs &a, ui
         ABQ_RECORDS_CASE(7)
     default:
         if (one)
-            stream_records_planes<8, 1, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);
+            stream_records_planes<8, 1>(a, rec_base, sums, u_first, n_units, n_pad, MR, warm);
         else
-            stream_records_planes<8, 4, false>(a, rec_base, sums, u_first, n_units, n_pad, MR);
+            stream_records_planes<8, 4>(a, rec_base, sums, u_first, n_units, n_pad, MR, warm);
     }
 #undef ABQ_RECORDS_CASE
 }
@@ -514,14 +626,14 @@ __device__ __forceinline__ void mma_u8s8_first(int (&d)[4], uint32_t a0, uint32_
 struct StreamSmem {
     size_t ring, rec, sums, zero, red, bars, total;
 };
-__host__ __device__ inline StreamSmem stream_smem_layout(int nw, int ring, int cu, int unit_bytes, int units_pad, int MR, int tiles_per_cta, int MT)
+__host__ __device__ inline StreamSmem stream_smem_layout(int nw, int ring, int cu, int unit_bytes, int units_pad, int MR, int tiles_per_cta, int MT, int uw)
 {
     StreamSmem L;
     size_t at = 0;
     L.ring = at;
     at += (size_t)nw * ring * cu * unit_bytes;
     L.rec = at;
-    at += (size_t)units_pad * MR * 128;
+    at += (size_t)units_pad * MR * uw;
     L.sums = at;
     at += ((size_t)units_pad * MR * 4 + 15) & ~(size_t)15;
     L.zero = at;
@@ -536,10 +648,12 @@ __host__ __device__ inline StreamSmem stream_smem_layout(int nw, int ring, int c
 
 // Q: weight bits.  MT: token tiles of 8 (2 for 9..16 tokens).  MP: token rows per column block (1, 2, 4, 8).
 // GS = 8 / MP units share one set of accumulators (GROUPED only).  GROUPED: per-group scale / zero point in the stream.
-template <int Q, int MT, int MP, bool GROUPED>
+template <int Q, int MT, int MP, bool GROUPED, int UW>
 __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const StreamArgs a)
 {
-    using F = StreamFormat<Q>;
+    using F = StreamFormat<Q, UW>;
+    constexpr int kCodeBytes = Q * 2 * UW; // of a unit; its 64 parameter bytes follow
+    static_assert(GROUPED || UW == 128, "64-feature units exist for scale groups of 64 only");
     constexpr int GS = GROUPED ? 8 / MP : 1;
     constexpr int MR = MT == 2 ? 16 : MP; // token rows of a record
     static_assert(MT == 1 || MP == 8, "two token tiles only with full column blocks");
@@ -563,8 +677,9 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     ABQ_TRACE(0);
     const int s = blockIdx.x / a.ctas_per_slice;
     const int cb = blockIdx.x - s * a.ctas_per_slice;
-    const int r_begin = (int)((long long)cb * a.tiles / a.ctas_per_slice);
-    const int r_end = (int)((long long)(cb + 1) * a.tiles / a.ctas_per_slice);
+    // (32-bit arithmetic: a launch has at most a few hundred CTAs per slice and the planner bounds tiles * CTAs below 2^31)
+    const int r_begin = (int)((unsigned)cb * (unsigned)a.tiles / (unsigned)a.ctas_per_slice);
+    const int r_end = (int)((unsigned)(cb + 1) * (unsigned)a.tiles / (unsigned)a.ctas_per_slice);
     const int T = r_end - r_begin;
     const int max_T = (a.tiles + a.ctas_per_slice - 1) / a.ctas_per_slice;
     const int u0 = s * a.units_per_slice;                        // first unit of this CTA's K range
@@ -574,7 +689,7 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     const int total_chunks = T * cpt;
     const int chunk_bytes = a.cu * a.unit_bytes;
 
-    const StreamSmem L = stream_smem_layout(nw, a.ring, a.cu, a.unit_bytes, units_pad, MR, max_T, MT);
+    const StreamSmem L = stream_smem_layout(nw, a.ring, a.cu, a.unit_bytes, units_pad, MR, max_T, MT, UW);
     uint8_t *ring_base = smem + L.ring;
     uint8_t *rec_base = smem + L.rec;
     int *sums = reinterpret_cast<int *>(smem + L.sums);
@@ -603,24 +718,24 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     uint8_t *my_ring = ring_base + (size_t)warp * a.ring * chunk_bytes;
 
     // request side (lane 0): cursor over the chunks in consumption order
-    int q_tile = 0, q_cit = 0, q_left = 0;
+    int q_cit = 0, q_left = 0;
+    const uint8_t *q_src = a.Wp; // where the next chunk starts: chunks of a tile follow one another in memory
     if (cpt > 0) {
-        q_tile = c_begin / cpt;
+        const int q_tile = c_begin / cpt;
         q_cit = c_begin - q_tile * cpt;
         q_left = c_end - c_begin;
+        q_src = a.Wp + ((size_t)(r_begin + q_tile) * a.units + u0 + (size_t)q_cit * a.cu) * a.unit_bytes;
     }
+    const uint32_t last_chunk_bytes = (uint32_t)(n_units - (cpt - 1) * a.cu) * a.unit_bytes;        // of a tile's K range
+    const size_t tile_gap = (size_t)(a.units - n_units) * a.unit_bytes;                               // K range of the other slices
     auto issue = [&](int slot) {
-        const int uf = q_cit * a.cu;
-        const int nu = min(a.cu, n_units - uf);
-        const uint32_t bytes = (uint32_t)nu * a.unit_bytes;
-        const uint8_t *src = a.Wp + ((size_t)(r_begin + q_tile) * a.units + u0 + uf) * a.unit_bytes;
+        const bool last = q_cit == cpt - 1;
+        const uint32_t bytes = last ? last_chunk_bytes : (uint32_t)chunk_bytes;
         mbar_arrive_expect_tx(&full[slot], bytes);
-        bulk_load(my_ring + (size_t)slot * chunk_bytes, src, bytes, &full[slot]);
+        bulk_load(my_ring + (size_t)slot * chunk_bytes, q_src, bytes, &full[slot]);
+        q_src += bytes + (last ? tile_gap : 0);
+        q_cit = last ? 0 : q_cit + 1;
         --q_left;
-        if (++q_cit == cpt) {
-            q_cit = 0;
-            ++q_tile;
-        }
     };
     if (lane == 0) {
         for (int slot = 0; slot < a.prefill && q_left > 0; ++slot)
@@ -644,9 +759,39 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     }
     const int per_tile = a.M * 16; // outputs of a tile; output idx of the CTA is tile idx / per_tile, token (idx % per_tile) / 16, row idx % 16
     const int first_tl = (int)threadIdx.x / per_tile, first_i = (int)threadIdx.x - first_tl * per_tile;
-    // Nothing of the previous kernel's output is touched yet: bring the activations' lines (and page-table entries) towards
-    // L2, write the records' zero padding, and ask for the lines this CTA will store its results to.
-    stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, true);
+    // The activation records.  Common case (plane input of 8 or 4 bits, at most kFast items per thread): everything about
+    // a thread's items that can be known now is computed now -- where the plane words come from, where the record goes --
+    // so that after the wait only loads, the bit shuffle and stores remain, in straight-line code.  Other cases run the
+    // general routine, rehearsed here with the loads switched off.  Either way: the records' zero padding is written, the
+    // lines to be read (and the lines this CTA will store its results to) are requested into L2, page-table walk included.
+    constexpr int kFast = 4;
+    const int rec_words = units_pad * (UW / 32), rec_items = MR * rec_words;
+    const int rec_batches = (rec_items + (int)blockDim.x - 1) / (int)blockDim.x;
+    const bool rec_fast = !a.x_qscale && (a.x_bits == 8 || a.x_bits == 4) && rec_batches <= kFast;
+    const uint32_t *it_src[kFast]; // plane 0 word of the item, or null: padding (already zero)
+    uint32_t it_dst[kFast];        // byte offset of the record from rec_base | 1: this lane also stores the unit's code sum
+    if (rec_fast) {
+        const uint32_t magic = 0xffffffffu / (uint32_t)rec_words + 1u; // idx / rec_words == umulhi(idx, magic) here
+#pragma unroll
+        for (int i = 0; i < kFast; ++i) {
+            const int idx = i * (int)blockDim.x + (int)threadIdx.x;
+            const int m = (int)__umulhi((uint32_t)idx, magic), kwl = idx - m * rec_words;
+            const bool live = idx < rec_items && m < a.M && kwl / (UW / 32) < n_units;
+            it_src[i] = live ? a.X + (size_t)m * (a.K >> 5) + (size_t)u0 * (UW / 32) + kwl : nullptr;
+            const int ul = kwl / (UW / 32), part = kwl % (UW / 32);
+            it_dst[i] = (uint32_t)(((size_t)ul * MR + m) * UW + part * 32) | (part == 0 ? 1u : 0u) | ((uint32_t)(m & 1) << 1);
+            if (live && (kwl & 31) == 0)
+                for (int b = 0; b < a.x_bits; ++b)
+                    prefetch_l2(it_src[i] + b * a.x_plane_words);
+        }
+        // zero padding: the whole record area (real items are overwritten after the wait)
+        for (int i = threadIdx.x; i < (int)((size_t)units_pad * MR * UW / 16); i += blockDim.x)
+            reinterpret_cast<uint4 *>(rec_base)[i] = make_uint4(0, 0, 0, 0);
+        for (int i = threadIdx.x; i < units_pad * MR; i += blockDim.x)
+            sums[i] = 0;
+    } else {
+        stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, true);
+    }
     {
         const size_t esz = a.out_dtype == ABQ_OUT_INT32 ? 4 : 2;
         for (int i = threadIdx.x; i < a.M; i += blockDim.x)
@@ -661,9 +806,9 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
         uint32_t v, v2;
         const unsigned long long t0 = globaltimer_ns();
         asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(a.X) : "memory");
-        const unsigned long long t1 = globaltimer_ns() + (v & 0u);
-        asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v2) : "l"(a.Wp + (size_t)blockIdx.x * 8192 + 4096 + (t1 & 0u)) : "memory");
-        const unsigned long long t2 = globaltimer_ns() + (v2 & 0u);
+        const unsigned long long t1 = globaltimer_ns() + (v == 0x9e3779b9u ? 1 : 0);
+        asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v2) : "l"(a.Wp + (size_t)blockIdx.x * 8192 + 4096 + (t1 & 3u) * 0) : "memory");
+        const unsigned long long t2 = globaltimer_ns() + (v2 == 0x9e3779b9u ? 1 : 0);
         a.trace[16 + (size_t)trace_slot * 16 + 9] = t1 - t0;
         a.trace[16 + (size_t)trace_slot * 16 + 10] = t2 - t1;
     }
@@ -675,7 +820,43 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     __shared__ uint32_t ar_epoch;
     if (a.ar.world > 1 && threadIdx.x == 0) // (only the last CTA of a launch advances the counter, after all have read it)
         ar_epoch = *reinterpret_cast<volatile uint32_t *>(a.ar.counter) + 1u;
-    stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, false);
+    if (rec_fast) {
+        auto build = [&](auto width_tag) {
+            constexpr int P = decltype(width_tag)::value;
+            uint32_t pl[kFast][P];
+#pragma unroll
+            for (int i = 0; i < kFast; ++i) {
+#pragma unroll
+                for (int b = 0; b < P; ++b)
+                    pl[i][b] = (i < rec_batches && it_src[i]) ? __ldg(it_src[i] + b * a.x_plane_words) : 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < kFast; ++i) {
+                if (i < rec_batches) { // the same for every thread of the CTA: the shuffles below see whole warps
+                    uint32_t r[8];
+                    x_bytes<P>(pl[i], a.x_signed != 0, r);
+                    int sum = stream_code_sum(r, a.x_signed != 0);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1); // the runs of a unit sit in consecutive lanes
+                    if (UW == 128)
+                        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    if (it_src[i]) {
+                        uint8_t *dst = rec_base + (it_dst[i] & ~3u);
+                        const int swz = UW == 128 ? (int)(it_dst[i] & 2u) << 3 : 0; // odd token rows swap their 16-byte halves
+                        *reinterpret_cast<uint4 *>(dst + swz) = make_uint4(r[0], r[1], r[2], r[3]);
+                        *reinterpret_cast<uint4 *>(dst + (16 ^ swz)) = make_uint4(r[4], r[5], r[6], r[7]);
+                        if (it_dst[i] & 1u)
+                            sums[(it_dst[i] & ~3u) / UW] = sum;
+                    }
+                }
+            }
+        };
+        if (a.x_bits == 8)
+            build(std::integral_constant<int, 8>{});
+        else
+            build(std::integral_constant<int, 4>{});
+    } else {
+        stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, false);
+    }
     ABQ_TRACE(8);
     __syncthreads();
     ABQ_TRACE(3);
@@ -683,7 +864,7 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
     // lane constants of the B fragment fetch: column c = g holds token (g % MP) of unit (g / MP) of a block
     const int my_m = g & (MP - 1);
     const int my_slot = GS > 1 ? g / MP : 0;
-    const int rec_lane = my_m * 128 + t * 32;
+    const int rec_lane = UW == 128 ? my_m * 128 + t * 32 : my_m * 64 + t * 16;
     const int swz = (my_m & 1) << 4;
     const int zoff = a.w_signed ? (1 << (Q - 1)) : 0;
 
@@ -710,7 +891,7 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
 
     // |acc0 + acc1 / 2^kShift - (zero + offset) * sum(x)| of one 128-feature group stays below 2^22 for the narrow widths:
     // int -> float by the 1.5 * 2^23 trick (two plain ALU/FMA operations) instead of a conversion instruction
-    constexpr long long kBound = 128LL * 128 * (((1 << Q) - 1) + ((1 << Q) - 1) + (1 << (Q - 1)));
+    constexpr long long kBound = (long long)UW * 128 * (((1 << Q) - 1) + ((1 << Q) - 1) + (1 << (Q - 1)));
     constexpr bool kMagic = kBound < (1LL << 22);
 
     for (int ci = c_begin; ci < c_end && ok; ++ci) {
@@ -720,59 +901,70 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
         const uint8_t *stage = my_ring + (size_t)slot * chunk_bytes;
         const int uf = cit * a.cu;              // first unit of the chunk within this CTA's K range
         const int nu = min(a.cu, n_units - uf); // units in the chunk
-        // (two blocks per trip: with accumulators of its own, a block's MMAs can run under the fold of the block before it)
-#pragma unroll 2
+        // The loops over blocks and over the units of a block stay rolled (two units per trip): a warp only sees a few dozen
+        // units per launch, and straight-line code that long is fetched from the instruction cache about as often as it
+        // is executed -- measured, instruction fetch and not arithmetic was what this loop waited for when it was unrolled.
+#pragma unroll 1
         for (int ub = 0; ub < nu; ub += GS) {
             const uint8_t *blk = stage + (size_t)ub * a.unit_bytes;
             const int left = nu - ub; // units of this block that exist
-            int acc_block[F::kSets][MT][4]; // GROUPED: the block's own accumulators (its first MMA step overwrites them)
-            int(&acc)[F::kSets][MT][4] = GROUPED ? acc_block : acc_run;
-            // A whole block runs without a branch between its units, so that the compiler overlaps the loads of one unit
-            // with the arithmetic of another; only the last block of a tile's K range may be short.
-            auto run_block = [&](auto whole_tag) {
-                constexpr bool kWhole = decltype(whole_tag)::value;
+            // GROUPED: the block's own accumulators; blocks of several units keep two sets, for even and odd units, so that a
+            // unit's MMAs do not queue behind those of the unit before it
+            constexpr int kPar = GROUPED && GS >= 2 ? 2 : 1;
+            int acc_block[kPar][F::kSets][MT][4];
+            if (GROUPED && GS >= 2) {
 #pragma unroll
-                for (int ui = 0; ui < GS; ++ui) {
-                    if (kWhole || ui < left) {
-                        const uint8_t *unit = blk + ui * a.unit_bytes;
-                        uint32_t R[4][4];
-                        F::expand(unit, lane, R);
-                        const uint8_t *rec = rec_base + (size_t)(uf + ub + ui) * MR * 128;
+                for (int i = 0; i < kPar * F::kSets * MT * 4; ++i)
+                    (&acc_block[0][0][0][0])[i] = 0;
+            }
+            auto run_unit = [&](int ui, auto par_tag) { // ui: unit of the block; par_tag: which accumulator set (compile time)
+                constexpr int kP = decltype(par_tag)::value;
+                const uint8_t *unit = blk + ui * a.unit_bytes;
+                uint32_t R[F::kSteps][4];
+                F::expand(unit, lane, R);
+                const uint8_t *rec = rec_base + (size_t)(uf + ub + ui) * MR * UW;
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
-                            const uint8_t *bp = (GS == 1 || my_slot == ui) ? rec + mt * 1024 + rec_lane : zero_base;
-                            const uint4 blo = *reinterpret_cast<const uint4 *>(bp + swz);
-                            const uint4 bhi = *reinterpret_cast<const uint4 *>(bp + (16 ^ swz));
-                            const uint32_t b[8] = { blo.x, blo.y, blo.z, blo.w, bhi.x, bhi.y, bhi.z, bhi.w };
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint8_t *bp = (GS == 1 || my_slot == ui) ? rec + mt * 8 * UW + rec_lane : zero_base;
+                    uint32_t bf[2 * F::kSteps];
+                    if (UW == 128) {
+                        const uint4 blo = *reinterpret_cast<const uint4 *>(bp + swz);
+                        const uint4 bhi = *reinterpret_cast<const uint4 *>(bp + (16 ^ swz));
+                        bf[0] = blo.x, bf[1] = blo.y, bf[2] = blo.z, bf[3] = blo.w;
+                        bf[4 % (2 * F::kSteps)] = bhi.x, bf[5 % (2 * F::kSteps)] = bhi.y, bf[6 % (2 * F::kSteps)] = bhi.z, bf[7 % (2 * F::kSteps)] = bhi.w;
+                    } else {
+                        const uint4 bq = *reinterpret_cast<const uint4 *>(bp);
+                        bf[0] = bq.x, bf[1] = bq.y, bf[2] = bq.z, bf[3] = bq.w;
+                    }
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                // GROUPED: the first step of every set in a block starts from zero
-                                const bool first = GROUPED && ui == 0 && stream_first_in_set<F>(j);
-                                if (first)
-                                    mma_u8s8_first(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
-                                else
-                                    mma_u8<false>(acc[F::set_of(j)][mt], R[j][0], R[j][1], R[j][2], R[j][3], b[2 * j], b[2 * j + 1]);
-                            }
-                        }
-                        if (!GROUPED) {
+                    for (int j = 0; j < F::kSteps; ++j) {
+                        int(&acc)[4] = GROUPED ? acc_block[kP][F::set_of(j)][mt] : acc_run[F::set_of(j)][mt];
+                        // a single-unit block starts its sets from zero with the MMA itself
+                        if (GROUPED && GS == 1 && stream_first_in_set<F>(j))
+                            mma_u8s8_first(acc, R[j][0], R[j][1], R[j][2], R[j][3], bf[2 * j], bf[2 * j + 1]);
+                        else
+                            mma_u8<false>(acc, R[j][0], R[j][1], R[j][2], R[j][3], bf[2 * j], bf[2 * j + 1]);
+                    }
+                }
+                if (!GROUPED) {
 #pragma unroll
-                            for (int mt = 0; mt < MT; ++mt) {
-                                const int2 sv = *reinterpret_cast<const int2 *>(sums + (uf + ub + ui) * MR + 8 * mt + 2 * t);
-                                xs[mt][0] += sv.x;
-                                xs[mt][1] += sv.y;
-                            }
-                        }
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int2 sv = *reinterpret_cast<const int2 *>(sums + (uf + ub + ui) * MR + 8 * mt + 2 * t);
+                        xs[mt][0] += sv.x;
+                        xs[mt][1] += sv.y;
                     }
                 }
             };
-#ifdef ABQ_STREAM_BRANCHY // development builds only: every unit behind its own branch, for comparison
-            run_block(std::false_type{});
-#else
-            if (GS == 1 || left >= GS)
-                run_block(std::true_type{});
-            else
-                run_block(std::false_type{});
-#endif
+            if (GS == 1) {
+                run_unit(0, std::integral_constant<int, 0>{});
+            } else {
+#pragma unroll 1
+                for (int ui = 0; ui < GS && ui < left; ui += 2) {
+                    run_unit(ui, std::integral_constant<int, 0>{});
+                    if (ui + 1 < left)
+                        run_unit(ui + 1, std::integral_constant<int, kPar - 1>{});
+                }
+            }
             if (GROUPED) {
                 // fold the block: column 2 t + j of the accumulators is token (col % MP) of unit ub + col / MP
                 const int ul = uf + ub; // first unit of the block within the CTA's K range (a multiple of GS)
@@ -781,14 +973,14 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
                     uint2 pk[2]; // [column of the pair] -> (row g, row g + 8)
                     int xv[2];
                     if (MP == 1) {
-                        pk[0] = (2 * t < left) ? *reinterpret_cast<const uint2 *>(blk + (2 * t) * a.unit_bytes + Q * 256 + 8 * g) : make_uint2(0, 0);
-                        pk[1] = (2 * t + 1 < left) ? *reinterpret_cast<const uint2 *>(blk + (2 * t + 1) * a.unit_bytes + Q * 256 + 8 * g) : make_uint2(0, 0);
+                        pk[0] = (2 * t < left) ? *reinterpret_cast<const uint2 *>(blk + (2 * t) * a.unit_bytes + kCodeBytes + 8 * g) : make_uint2(0, 0);
+                        pk[1] = (2 * t + 1 < left) ? *reinterpret_cast<const uint2 *>(blk + (2 * t + 1) * a.unit_bytes + kCodeBytes + 8 * g) : make_uint2(0, 0);
                         const int2 sv = *reinterpret_cast<const int2 *>(sums + ul + 2 * t);
                         xv[0] = sv.x;
                         xv[1] = sv.y;
                     } else {
                         const int sl = (2 * t) / MP; // both columns of the pair belong to the same unit
-                        pk[0] = (GS == 1 || sl < left) ? *reinterpret_cast<const uint2 *>(blk + sl * a.unit_bytes + Q * 256 + 8 * g) : make_uint2(0, 0);
+                        pk[0] = (GS == 1 || sl < left) ? *reinterpret_cast<const uint2 *>(blk + sl * a.unit_bytes + kCodeBytes + 8 * g) : make_uint2(0, 0);
                         pk[1] = pk[0];
                         const int2 sv = *reinterpret_cast<const int2 *>(sums + (ul + sl) * MR + 8 * mt + ((2 * t) & (MP - 1)));
                         xv[0] = sv.x;
@@ -799,9 +991,15 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
                         const uint32_t p = (e >> 1) ? pk[e & 1].y : pk[e & 1].x;
                         const float sc_w = __uint_as_float(p & ~kZeroMask);
                         const int z = (int)(p & kZeroMask);
-                        int v = acc[0][mt][e];
-                        if (F::kSets == 2)
-                            v += acc[F::kSets - 1][mt][e] >> F::kShift; // exact: every term of that set is a multiple of 2^kShift
+                        int v = acc_block[0][0][mt][e];
+                        if (kPar == 2)
+                            v += acc_block[kPar - 1][0][mt][e];
+                        if (F::kSets == 2) { // exact: every term of that set is a multiple of 2^kShift
+                            int hi = acc_block[0][F::kSets - 1][mt][e];
+                            if (kPar == 2)
+                                hi += acc_block[kPar - 1][F::kSets - 1][mt][e];
+                            v += hi >> F::kShift;
+                        }
                         v -= z * xv[e & 1];
                         const float fv = kMagic ? __int_as_float(v + 0x4b400000) - 12582912.0f : (float)v;
                         facc[mt][e] = fmaf(fv, sc_w, facc[mt][e]);
@@ -1031,10 +1229,10 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
 }
 
 // ------------------------------------------------------------------------------------------- host side
-template <int Q, int MT, int MP, bool GROUPED>
+template <int Q, int MT, int MP, bool GROUPED, int UW = 128>
 static cudaError_t stream_launch_variant(const abq_gemm_state *st, const StreamArgs &args, cudaStream_t stream)
 {
-    auto kern = stream_kernel<Q, MT, MP, GROUPED>;
+    auto kern = stream_kernel<Q, MT, MP, GROUPED, UW>;
     static thread_local SmemOptIn opted;
     cudaError_t e = opted.ensure(kern, st->shared_mem_size);
     if (e != cudaSuccess)
@@ -1056,28 +1254,37 @@ static cudaError_t stream_launch_variant(const abq_gemm_state *st, const StreamA
     return cudaLaunchKernelEx(&cfg, kern, args);
 }
 
+template <int Q, int UW>
+static cudaError_t stream_launch_grouped(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, cudaStream_t stream)
+{
+    if (MT == 2)
+        return stream_launch_variant<Q, 2, 8, true, UW>(st, args, stream);
+    switch (MP) {
+    case 1: return stream_launch_variant<Q, 1, 1, true, UW>(st, args, stream);
+    case 2: return stream_launch_variant<Q, 1, 2, true, UW>(st, args, stream);
+    case 4: return stream_launch_variant<Q, 1, 4, true, UW>(st, args, stream);
+    default: return stream_launch_variant<Q, 1, 8, true, UW>(st, args, stream);
+    }
+}
+
 template <int Q>
 static cudaError_t stream_launch_q(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, bool grouped, cudaStream_t stream)
 {
     if (!grouped)
         return MT == 2 ? stream_launch_variant<Q, 2, 8, false>(st, args, stream) : stream_launch_variant<Q, 1, 8, false>(st, args, stream);
-    if (MT == 2)
-        return stream_launch_variant<Q, 2, 8, true>(st, args, stream);
-    switch (MP) {
-    case 1: return stream_launch_variant<Q, 1, 1, true>(st, args, stream);
-    case 2: return stream_launch_variant<Q, 1, 2, true>(st, args, stream);
-    case 4: return stream_launch_variant<Q, 1, 4, true>(st, args, stream);
-    default: return stream_launch_variant<Q, 1, 8, true>(st, args, stream);
-    }
+    return args.uw == 64 ? stream_launch_grouped<Q, 64>(st, args, MT, MP, stream) : stream_launch_grouped<Q, 128>(st, args, MT, MP, stream);
 }
 
 template <int Q>
 static cudaError_t stream_prepare_q(const uint32_t *planes, const __half *w_scale, const uint8_t *w_zero, uint8_t *out, int N, int K, int w_signed,
-                                    int grouped, int groups_per_scale, int scale_groups, cudaStream_t stream)
+                                    int grouped, int uw, int units_per_scale, int scale_groups, cudaStream_t stream)
 {
-    const long long threads = (long long)((N + 15) / 16) * (K / 128) * 32;
-    prepare_stream_kernel<Q><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(planes, w_scale, w_zero, out, N, K, w_signed, grouped,
-                                                                                   groups_per_scale, scale_groups);
+    const long long threads = (long long)((N + 15) / 16) * (K / uw) * 32;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (uw == 64)
+        prepare_stream_kernel<Q, 64><<<blocks, 256, 0, stream>>>(planes, w_scale, w_zero, out, N, K, w_signed, grouped, units_per_scale, scale_groups);
+    else
+        prepare_stream_kernel<Q, 128><<<blocks, 256, 0, stream>>>(planes, w_scale, w_zero, out, N, K, w_signed, grouped, units_per_scale, scale_groups);
     return cudaGetLastError();
 }
 
@@ -1088,14 +1295,14 @@ static cudaError_t stream_prepare_q(const uint32_t *planes, const __half *w_scal
         return stream_launch_q<Q>(st, args, MT, MP, grouped, stream);                                                                           \
     }                                                                                                                                           \
     cudaError_t stream_prepare_w##Q(const uint32_t *planes, const __half *w_scale, const uint8_t *w_zero, uint8_t *out, int N, int K,          \
-                                    int w_signed, int grouped, int groups_per_scale, int scale_groups, cudaStream_t stream)                    \
+                                    int w_signed, int grouped, int uw, int units_per_scale, int scale_groups, cudaStream_t stream)             \
     {                                                                                                                                           \
-        return stream_prepare_q<Q>(planes, w_scale, w_zero, out, N, K, w_signed, grouped, groups_per_scale, scale_groups, stream);              \
+        return stream_prepare_q<Q>(planes, w_scale, w_zero, out, N, K, w_signed, grouped, uw, units_per_scale, scale_groups, stream);           \
     }
 #define ABQ_STREAM_DECLARE(Q)                                                                                                                   \
     cudaError_t stream_launch_w##Q(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, bool grouped, cudaStream_t stream);       \
     cudaError_t stream_prepare_w##Q(const uint32_t *planes, const __half *w_scale, const uint8_t *w_zero, uint8_t *out, int N, int K,          \
-                                    int w_signed, int grouped, int groups_per_scale, int scale_groups, cudaStream_t stream);
+                                    int w_signed, int grouped, int uw, int units_per_scale, int scale_groups, cudaStream_t stream);
 ABQ_STREAM_DECLARE(2)
 ABQ_STREAM_DECLARE(3)
 ABQ_STREAM_DECLARE(4)

@@ -32,7 +32,8 @@ def build(force: bool = False) -> None:
     """Compile the C restatement (and the reference library when its sources are mounted)."""
     if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < (_HERE / "abq_oracle.c").stat().st_mtime:
         subprocess.run(["make", "-C", str(_HERE), "all"], check=True, capture_output=True)
-    ref_root = os.environ.get("ABQ_REFERENCE_ROOT", "/root/reference")
+    # the reference checkout: ABQ_REFERENCE_ROOT, else a directory named "reference" beside this repository
+    ref_root = os.environ.get("ABQ_REFERENCE_ROOT", str(_HERE.parent.parent / "reference"))
     if os.path.isdir(os.path.join(ref_root, "engine")) and (force or not _REF_PATH.exists()):
         subprocess.run(["make", "-C", str(_HERE), "ref", f"REF={ref_root}"], check=True, capture_output=True)
     if os.path.isdir(os.path.join(ref_root, "engine")) and (force or not _REF_GPU_PATH.exists()):

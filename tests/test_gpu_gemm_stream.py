@@ -13,6 +13,13 @@ from test_gpu_gemm_fp16 import check_close
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def heuristic_plans(monkeypatch):
+    """The tuning table sends some shapes to the kernel that reads the planes; these tests are about the prepared-weights
+    kernel, so they plan with the heuristic alone (one test below checks that a table entry is honoured)."""
+    monkeypatch.setenv("ABQ_TUNE_IGNORE", "1")
+
+
 def run_prepared(abq, xp, wp, M, N, K, *, x_bits, w_bits, x_signed, w_signed, out_fp16=False, scale_mode=0, group_size=0, C=None,
                  w_scale=None, w_zero=None, x_scale=None, flags=0, x_quant_scale=None, calls=1):
     from abq_llm_b200 import binding as B
@@ -97,6 +104,24 @@ def test_per_group(abq, oracle, cuda, M, N, K, q, group, w_signed):
     check_close(got, oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), xs, group))
 
 
+@pytest.mark.parametrize("M,N,K,q,group", [(1, 4096, 4096, 2, 64), (2, 512, 1024, 3, 64), (4, 320, 2176, 4, 64), (8, 136, 640, 8, 64), (16, 1024, 4096, 2, 64),
+                                           (33, 96, 1280, 3, 64), (5, 200, 1152, 4, 192), (16, 5120, 5120, 2, 64), (16, 5120, 13824, 2, 64),
+                                           (1, 13824, 5120, 2, 64), (3, 15360, 5120, 2, 64)])
+@pytest.mark.parametrize("w_signed", [False, True])
+def test_scale_groups_of_64(abq, oracle, cuda, M, N, K, q, group, w_signed):
+    """Scale groups that are an odd multiple of 64 features wide (the LLaMA-2-13B W2A8 g64 configuration: hidden 5120, FFN 13824):
+    the prepared layout then uses 64-feature units."""
+    rng = np.random.default_rng(N + K + q + group + M)
+    x = np.clip(np.rint(rng.normal(0, 30, size=(M, K))), -128, 127).astype(np.int32)
+    w = rand_codes(rng, N, K, q, w_signed)
+    G = K // group
+    ws = rng.uniform(0.001, 0.02, size=(N, G)).astype(np.float16)
+    wz = rng.integers(0, 1 << q, size=(N, G)).astype(np.uint8)
+    got, st = run_prepared(abq, planes_dev(oracle, x, 8), planes_dev(oracle, w, q), M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=w_signed,
+                           out_fp16=True, scale_mode=abq.SCALE_GROUP, group_size=group, w_scale=dev(ws), w_zero=dev(wz), calls=2)
+    check_close(got, oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), None, group))
+
+
 @pytest.mark.parametrize("M,N,K,q", [(1, 4096, 4096, 2), (4, 1024, 4096, 3), (16, 512, 11008, 4), (7, 200, 1152, 4), (1, 64, 128, 8)])
 @pytest.mark.parametrize("with_zero", [False, True])
 def test_per_channel_and_tensor_compat(abq, oracle, cuda, M, N, K, q, with_zero):
@@ -168,3 +193,34 @@ def test_full_size_sweep_shapes(abq, oracle, cuda, N, K, q):
         check_close(got, oracle.dequant_gemm(x, w, ws, wz.astype(np.int32), None, 128))
         acc, _ = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False)
         assert np.array_equal(acc, oracle.gemm_values_blas(x, w)), f"M={M}"
+
+
+def test_tuning_table_entry_is_honoured(abq, oracle, cuda, monkeypatch, tmp_path):
+    """A table line for the problem changes the launch shape (here: sixteen warps, one CTA per SM, 74 CTAs) and nothing else."""
+    M, N, K, q = 4, 2048, 1024, 4
+    rng = np.random.default_rng(7)
+    x, w = rand_codes(rng, M, K, 8, True), rand_codes(rng, N, K, q, False)
+    xp, wp = planes_dev(oracle, x, 8), planes_dev(oracle, w, q)
+    base, st0 = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False)
+    # the table is read once per process: this test can only check a process that has not planned yet, so it runs a child
+    import subprocess, sys, textwrap
+    table = tmp_path / "table.txt"
+    table.write_text(f"{q} 8 4 {N} {K} 0 0 : 0 0 0 16 1 74 0 0 0\n")
+    code = textwrap.dedent(f"""
+        import sys, ctypes
+        sys.path.insert(0, {str(__import__('pathlib').Path(__file__).resolve().parent)!r}); sys.path.insert(0, {str(__import__('pathlib').Path(__file__).resolve().parent.parent)!r})
+        from conftest import load_package
+        abq = load_package()
+        from abq_llm_b200 import binding as B
+        p = B.GemmParams(); p.M, p.N, p.K = {M}, {N}, {K}; p.X = p.W = p.D = 4096; p.x_bits, p.w_bits, p.x_signed = 8, {q}, 1
+        p.route = 2; p.flags = abq.FLAG_WEIGHTS_PREPARED; p.w_prepared = 4096
+        st = B.GemmState(); assert abq.lib().abq_gemm_init(ctypes.byref(p), ctypes.byref(st)) == 0
+        print(st.grid[0], st.block[0])
+    """)
+    env = dict(__import__("os").environ, ABQ_TUNE_TABLE=str(table))
+    env.pop("ABQ_TUNE_IGNORE", None)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
+    assert out.returncode == 0, out.stderr[-1500:]
+    assert out.stdout.split() == ["74", "512"], out.stdout
+    assert (st0.grid[0], st0.block[0]) != (74, 512)
+    assert np.array_equal(base, oracle.gemm_values_blas(x, w))
