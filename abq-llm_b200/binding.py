@@ -180,6 +180,13 @@ def gemm_prepared_weight_bytes(params: GemmParams) -> int:
     return int(lib().abq_gemm_prepared_weight_bytes(ctypes.byref(params)))
 
 
+def state_kernel(state: GemmState) -> str:
+    """Name of the GEMM kernel a plan launches (for reports): the route, and on the decode route which of its two kernels."""
+    if state.route == ROUTE_I8_MMA:
+        return "stream_kernel" if (state.tmap[1][0] & 0xffffffff) == 0x5354524d else "decode_kernel"
+    return {ROUTE_B1_MMA: "b1_kernel", ROUTE_I8_UMMA: "umma_kernel"}.get(state.route, "?")
+
+
 def gemm_init(params: GemmParams) -> GemmState:
     st = GemmState()
     _check(lib().abq_gemm_init(ctypes.byref(params), ctypes.byref(st)), "abq_gemm_init")

@@ -158,12 +158,12 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
     const StreamHints H = hints_for(p);
     if (H.planes > 0 && !p.allreduce)
         return false;
-    int MP = P->MT == 2 || !grouped ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
-    while (MP < 8 && (8 / MP) * P->unit_bytes > 5120)
+    int MP = P->MT == 2 ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
+    while (grouped && MP < 8 && (8 / MP) * P->unit_bytes > 5120)
         MP *= 2;
-    if (H.mp > 0 && P->MT == 1 && grouped)
+    if (H.mp > 0 && P->MT == 1)
         MP = H.mp;
-    if ((MP != 1 && MP != 2 && MP != 4 && MP != 8) || MP < (rows > 8 ? 8 : rows) || ((P->MT == 2 || !grouped) && MP != 8))
+    if ((MP != 1 && MP != 2 && MP != 4 && MP != 8) || MP < (rows > 8 ? 8 : rows) || (P->MT == 2 && MP != 8))
         return false;
     P->MP = MP;
     const int GS = grouped && P->MT == 1 ? 8 / P->MP : 1;

@@ -949,9 +949,15 @@ __global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const S
                 if (!GROUPED) {
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const int2 sv = *reinterpret_cast<const int2 *>(sums + (uf + ub + ui) * MR + 8 * mt + 2 * t);
-                        xs[mt][0] += sv.x;
-                        xs[mt][1] += sv.y;
+                        if (MP == 1) { // one token: every column is that token
+                            const int sv = sums[uf + ub + ui];
+                            xs[mt][0] += sv;
+                            xs[mt][1] += sv;
+                        } else {       // columns 2 t, 2 t + 1 are tokens (2 t) % MP, + 1 (columns beyond MP repeat tokens and are ignored)
+                            const int2 sv = *reinterpret_cast<const int2 *>(sums + (uf + ub + ui) * MR + 8 * mt + ((2 * t) & (MP - 1)));
+                            xs[mt][0] += sv.x;
+                            xs[mt][1] += sv.y;
+                        }
                     }
                 }
             };
@@ -1270,8 +1276,16 @@ static cudaError_t stream_launch_grouped(const abq_gemm_state *st, const StreamA
 template <int Q>
 static cudaError_t stream_launch_q(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, bool grouped, cudaStream_t stream)
 {
-    if (!grouped)
-        return MT == 2 ? stream_launch_variant<Q, 2, 8, false>(st, args, stream) : stream_launch_variant<Q, 1, 8, false>(st, args, stream);
+    if (!grouped) {
+        if (MT == 2)
+            return stream_launch_variant<Q, 2, 8, false>(st, args, stream);
+        switch (MP) { // without group parameters the column blocks only make the activation records smaller
+        case 1: return stream_launch_variant<Q, 1, 1, false>(st, args, stream);
+        case 2: return stream_launch_variant<Q, 1, 2, false>(st, args, stream);
+        case 4: return stream_launch_variant<Q, 1, 4, false>(st, args, stream);
+        default: return stream_launch_variant<Q, 1, 8, false>(st, args, stream);
+        }
+    }
     return args.uw == 64 ? stream_launch_grouped<Q, 64>(st, args, MT, MP, stream) : stream_launch_grouped<Q, 128>(st, args, MT, MP, stream);
 }
 

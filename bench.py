@@ -726,7 +726,7 @@ def run_tp_decode(args, rank, world, local):
                 "ms_per_step": best["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
                 "data": "synthetic", "config": {"workload": res["workload"] + f"; tensor parallel {world}, batch 1 (value); batches 8 and 32 in `batches`"},
                 "tp_decode": res}
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -756,7 +756,7 @@ def run_reference(args, rank, world):
     gpu_rows = reference_gpu_kernels()  # context only: the arm's value stays the reference's CPU implementation
     if gpu_rows:
         line["reference_gpu_kernels"] = gpu_rows
-    print(json.dumps(line))
+    emit(line)
 
 
 def main():
@@ -780,6 +780,12 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="profiling aid: launch kernel by kernel instead of one CUDA graph per step")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="profiling aid: skip the host-side reference timing")
     args = ap.parse_args()
+    # stdout carries the one JSON line and nothing else: whatever libraries print there meanwhile (NCCL's version banner) goes
+    # to stderr; the descriptor is put back for the final print
+    global REAL_STDOUT
+    sys.stdout.flush()
+    REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -837,9 +843,13 @@ def main():
     d2h = gemms[0]["e2e"]["out_host"].numel() * 2 * passes
     peak, peak_kind = measured_peaks()
     per_gpu = bytes_per_step * args.steps / (ms * 1e-3) / 1e9
-    stream_launches = sum(1 for g in gemms if g["prepared"] is not None) if headline == "prepared" else 0
-    kernel = "stream_kernel" if stream_launches == n_gemm else ("decode_kernel" if stream_launches == 0 else "stream_kernel / decode_kernel")
+    # which kernel each GEMM of the pass launches (the tuning table sends some shapes to the kernel that reads the planes);
+    # the roofline object describes the one that takes the larger share of the launches
+    kernels = [abq.state_kernel(g["states"][headline]) for g in gemms]
+    counts = {k: kernels.count(k) for k in sorted(set(kernels))}
+    kernel = max(counts, key=counts.get)
     ratio = DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE.get(kernel)
+    dom_bytes = sum(g["bytes"] for g, k in zip(gemms, kernels) if k == kernel) / counts[kernel]
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
@@ -859,11 +869,11 @@ def main():
                 "frac_of_hbm": value_other / world / peak},
         "gpu_launches": n_gemm * passes * args.steps,  # one kernel of this library per GEMM
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": f"{kernel} ({n_gemm} launches per pass, all shapes)", "achieved": per_gpu, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": f"{kernel} ({counts[kernel]} of the {n_gemm} launches per pass; all: {counts})", "achieved": per_gpu, "peak": peak,
                      "unit": "GB/s", "frac": per_gpu / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
                      "bytes_per_launch": bytes_per_pass / max(1, n_gemm), "us_per_launch": ms * 1e3 / args.steps / passes / max(1, n_gemm),
-                     "traffic": None if ratio is None else ratio * bytes_per_pass / max(1, n_gemm),
-                     "traffic_source": "ncu dram bytes of a sweep-sized single-shape capture, scaled by algorithmic bytes to the mean launch of the sweep"},
+                     "traffic": None if ratio is None else ratio * dom_bytes,
+                     "traffic_source": f"ncu dram bytes of a sweep-sized single-shape capture of {kernel}, scaled by algorithmic bytes to its mean launch in the sweep"},
         "wall_ms_per_step": wall_ms / args.steps,
     }
     if args.shape:
@@ -887,9 +897,18 @@ def main():
         torch.cuda.empty_cache()
         line["tp_decode"] = tp_decode_measure(args, torch, dist, abq, rank, world)  # every rank takes part; rank 0 reports
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
+
+
+REAL_STDOUT = 1
+
+
+def emit(line):
+    """The JSON line, on the process's real stdout."""
+    sys.stdout.flush()
+    os.write(REAL_STDOUT, (json.dumps(line) + "\n").encode())
 
 
 if __name__ == "__main__":

@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <map>
 
 #include "abq_b200.h"
 
@@ -225,6 +226,7 @@ private:
     int x_bits_;
     int w_bits_;
     bool signed_;
+    std::map<const int *, void *> prepared_; // weight planes -> their prepared copy (extension, see prepare_weights)
 
 public:
     ABQGEMMWrapper(int X_BITS, int W_BITS, bool SIGNED): x_bits_(X_BITS), w_bits_(W_BITS), signed_(SIGNED) {}
@@ -238,6 +240,53 @@ public:
     {
         report(abq_quantize_pack_half(in_data, scale, packed_data, M, K, BIT, 0, stream), "pack");
     }
+    // Extension (no counterpart in the reference): bytes of, and the one-time set-up of, the prepared copy of a weight for
+    // decode-shape calls.  Call once per weight where the planes are loaded (LlamaDecoderLayerWeight::loadModel), with a
+    // device buffer of prepared_weight_bytes(N, K) bytes that lives as long as the planes; gemm() calls with these planes
+    // and up to 32 tokens then read the prepared copy.  Waits for the re-ordering to finish.
+    size_t prepared_weight_bytes(int N, int K) const
+    {
+        abq_gemm_params p = {};
+        p.M = 1;
+        p.N = N;
+        p.K = K;
+        p.x_bits = x_bits_;
+        p.w_bits = w_bits_;
+        p.x_signed = p.w_signed = signed_;
+        p.out_dtype = ABQ_OUT_FP16;
+        p.scale_mode = ABQ_SCALE_TENSOR_COMPAT;
+        return abq_gemm_prepared_weight_bytes(&p);
+    }
+    bool prepare_weights(const int *B, int N, int K, void *prepared, cudaStream_t stream)
+    {
+        abq_gemm_params p = {};
+        p.M = 1;
+        p.N = N;
+        p.K = K;
+        p.X = B; // (planning needs a non-null, aligned pointer; the activations are not touched here)
+        p.W = B;
+        p.C = B;
+        p.D = prepared;
+        p.x_bits = x_bits_;
+        p.w_bits = w_bits_;
+        p.x_signed = p.w_signed = signed_;
+        p.out_dtype = ABQ_OUT_FP16;
+        p.scale_mode = ABQ_SCALE_TENSOR_COMPAT;
+        p.route = ABQ_ROUTE_I8_MMA;
+        p.flags = ABQ_FLAG_WEIGHTS_PREPARED;
+        p.w_prepared = prepared;
+        abq_gemm_state st;
+        abq_status s = abq_gemm_init(&p, &st);
+        if (s == ABQ_OK)
+            s = abq_gemm_prepare_weights(&st, stream);
+        if (s != ABQ_OK || cudaStreamSynchronize(stream) != cudaSuccess) {
+            report(s == ABQ_OK ? ABQ_ERR_CUDA : s, "prepare_weights");
+            return false;
+        }
+        prepared_[B] = prepared;
+        return true;
+    }
+
     void gemm(const int M, const int N, const int K, const half *A, const int *B, const half *C, half *D, const float *scale,
               const float *scale_inter, const float *scale_out, bool bias, char *abq_gemm_workspace, size_t abq_gemm_ws_bytes,
               cudaStream_t stream)
@@ -274,7 +323,13 @@ public:
         p.x_signed = p.w_signed = signed_;
         p.out_dtype = ABQ_OUT_FP16;
         p.scale_mode = ABQ_SCALE_TENSOR_COMPAT;
-        const size_t need = abq_gemm_workspace_bytes(M, N, K, x_bits_, w_bits_, ABQ_ROUTE_AUTO);
+        const auto prep = prepared_.find(B);
+        if (prep != prepared_.end() && M <= 32) { // a prepared copy of these planes exists: the decode kernel that reads it
+            p.w_prepared = prep->second;
+            p.flags |= ABQ_FLAG_WEIGHTS_PREPARED;
+            p.route = ABQ_ROUTE_I8_MMA;
+        }
+        const size_t need = abq_gemm_workspace_bytes(M, N, K, x_bits_, w_bits_, p.route);
         abq_status s;
         const size_t used = fused ? 0 : plane_bytes; // the fused call leaves the whole workspace to the GEMM
         if (abq_gemm_ws_bytes >= used + need) { // a caller that sized the workspace with room for the scratch

@@ -8,6 +8,7 @@
 //     wrapper    ABQGEMMWrapper(8, 2, true).gemm on fp16 activations with the workspace FasterTransformer allocates
 //                (8 * tokens * K / 8 bytes, layers/FfnLayer.cc:670-673), fp16 out; scale_out is a float re-read as fp16
 //     wrapper_u  the same with SIGNED = false (activations go through the planes in the caller's workspace)
+//     wrapper_p  as wrapper, after ABQGEMMWrapper::prepare_weights (the library's extension: weights re-ordered once at load)
 // Reads <dir>/x.bin, <dir>/w.bin (and scale.bin, scale_out.bin for the wrapper), writes <dir>/d.bin.  Exit code 0 = ran.
 #include <cstdio>
 #include <cstdlib>
@@ -62,7 +63,7 @@ static void dump(const std::string &path, const void *dev, size_t bytes)
 int main(int argc, char **argv)
 {
     if (argc != 6) {
-        std::fprintf(stderr, "usage: compat_driver <initexec|wmma_any|wrapper|wrapper_u> <dir> M N K\n");
+        std::fprintf(stderr, "usage: compat_driver <initexec|wmma_any|wrapper|wrapper_u|wrapper_p> <dir> M N K\n");
         return 1;
     }
     const std::string what = argv[1], dir = argv[2];
@@ -107,8 +108,8 @@ int main(int argc, char **argv)
         if (err != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess)
             return 6;
         dump(dir + "/d.bin", D, (size_t)M * N * 4);
-    } else if (what == "wrapper" || what == "wrapper_u") {
-        const bool is_signed = what == "wrapper";
+    } else if (what == "wrapper" || what == "wrapper_u" || what == "wrapper_p") {
+        const bool is_signed = what != "wrapper_u";
         void *scale = to_device(slurp(dir + "/scale.bin"));         // float: activation quantiser scale
         void *scale_out = to_device(slurp(dir + "/scale_out.bin")); // float whose first two bytes are the fp16 output scale
         half *D = nullptr;
@@ -118,6 +119,13 @@ int main(int argc, char **argv)
         char *ws = nullptr;
         cudaMalloc(&ws, ws_bytes);
         ABQGEMMWrapper wrapper(8, 2, is_signed);
+        if (what == "wrapper_p") {
+            void *prepared = nullptr;
+            const size_t nbytes = wrapper.prepared_weight_bytes(N, K);
+            if (nbytes == 0 || cudaMalloc(&prepared, nbytes) != cudaSuccess ||
+                !wrapper.prepare_weights(reinterpret_cast<const int *>(w), N, K, prepared, stream))
+                return 9;
+        }
         wrapper.gemm(M, N, K, reinterpret_cast<const half *>(x), reinterpret_cast<const int *>(w), nullptr, D,
                      reinterpret_cast<const float *>(scale), nullptr, reinterpret_cast<const float *>(scale_out), false, ws, ws_bytes, stream);
         if (cudaStreamSynchronize(stream) != cudaSuccess)

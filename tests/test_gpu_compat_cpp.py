@@ -84,12 +84,12 @@ def _wrapper_expected(oracle, x, w, scale, out_scale, signed):
     return planes, oracle.dequant_tensor_compat(oracle.gemm_values_blas(vals, wv), out_scale)
 
 
-@pytest.mark.parametrize("what", ["wrapper", "wrapper_u"])
+@pytest.mark.parametrize("what", ["wrapper", "wrapper_u", "wrapper_p"])
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (7, 640, 1152), (40, 768, 2048)])
 def test_ft_wrapper_class(abq, oracle, cuda, tmp_path, what, M, N, K):
     rng = np.random.default_rng(M + K)
     x, w, scale, out_scale, scale_out = _wrapper_inputs(rng, M, N, K)
-    signed = what == "wrapper"
+    signed = what != "wrapper_u"
     run_driver(abq, what, tmp_path, M, N, K, {"x.bin": x, "w.bin": oracle.pack(w, 2), "scale.bin": scale, "scale_out.bin": scale_out})
     planes, want = _wrapper_expected(oracle, x, w, scale, out_scale, signed)
     got = np.fromfile(tmp_path / "d.bin", dtype=np.float16).reshape(M, N)

@@ -62,8 +62,9 @@ def main():
     print(f"rank {rank} FUSED_EQUALS_NCCL {ok}", flush=True)
 
     # ... and against the unsharded block computed by the CPU oracle (one rank, numpy stand-in for the GEMMs): what the
-    # two ranks produce together is the model's result, not merely the same thing twice.  Tolerance of the one-GPU test:
-    # chained GEMMs with fp16 intermediates, where one rounding difference moves a quantised code.
+    # two ranks produce together is the model's result, not merely the same thing twice.  Tolerance: twice that of the
+    # one-GPU test (chained GEMMs with fp16 intermediates, where one rounding difference moves a quantised code): here every
+    # row-parallel output is in addition the fp16 sum of two fp16 partials.
     import numpy as np
     from test_tp_linear_gloo import NumpyBackend
     host_w = [(c.cpu().numpy(), s.cpu().numpy(), z.cpu().numpy()) for c, s, z in weights]
@@ -75,7 +76,10 @@ def main():
         ref = whole.forward(x.cpu().numpy()).astype(np.float64)
         got = outs[("fused", M)].cpu().numpy().astype(np.float64)
         err = np.abs(got - ref)
-        close = close and bool(np.all(err <= 2.0 ** -6 * np.abs(ref) + 2.0 ** -7 * np.abs(ref).max()))
+        bound = 2.0 ** -5 * np.abs(ref) + 2.0 ** -6 * np.abs(ref).max()
+        if rank == 0:
+            print(f"M={M}: max |err| {err.max():.4g}, max |ref| {np.abs(ref).max():.4g}, worst err/bound {np.max(err / bound):.3f}", flush=True)
+        close = close and bool(np.all(err <= bound))
     print(f"rank {rank} MATCHES_UNSHARDED_ORACLE {close}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
