@@ -94,6 +94,8 @@ def lib() -> ctypes.CDLL:
                                              ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         L.abq_quantize_weights_half.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        L.abq_swiglu_half.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        L.abq_add_half.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_long, ctypes.c_void_p]
         L.abq_unpack_int8.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_void_p]
         _lib = L
@@ -240,6 +242,15 @@ def quantize_weights_half(w_half, planes, scale, zero, N: int, K: int, bits: int
     """fp16 weights [N][K] -> bit-planes + fp16 scale + u8 zero point (min/max calibration of the reference's quantiser)."""
     _check(lib().abq_quantize_weights_half(_ptr(w_half), N, K, bits, group_size, int(symmetric), _ptr(planes), _ptr(scale), _ptr(zero), _stream(stream)),
            "abq_quantize_weights_half")
+
+
+def swiglu_half(gate_up, out, M: int, F: int, stream=None) -> None:
+    """out[m][f] = silu(gate_up[m][f]) * gate_up[m][F + f]: one launch, in the GEMMs' dependent-launch chain."""
+    _check(lib().abq_swiglu_half(_ptr(gate_up), _ptr(out), M, F, _stream(stream)), "abq_swiglu_half")
+
+
+def add_half(a, b, out, n: int, stream=None) -> None:
+    _check(lib().abq_add_half(_ptr(a), _ptr(b), _ptr(out), n, _stream(stream)), "abq_add_half")
 
 
 def unpack_int8(planes, out_i8, rows: int, K: int, bits: int, signed: bool, stream=None) -> None:

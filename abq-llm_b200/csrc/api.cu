@@ -178,8 +178,7 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
                 return ABQ_ERR_INVALID_ARG;
         if (params->out_dtype != ABQ_OUT_FP16)
             return ABQ_ERR_INVALID_ARG;
-        state->ar = ar;
-        state->p.allreduce = nullptr; // the copy in the state is what the launch uses
+        state->ar = ar; // the copy in the state is what the launch uses (the pointer is dropped once the plan is made)
     }
     int route = params->route;
     if (route == ABQ_ROUTE_AUTO) {
@@ -205,6 +204,7 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
     if (s != ABQ_OK)
         return s;
     state->route = route;
+    state->p.allreduce = nullptr;
     if (state->ar.world > 0 && !(route == ABQ_ROUTE_I8_MMA && stream_planned(state) && state->cluster == 1))
         return ABQ_ERR_UNSUPPORTED; // the fused all-reduce lives in the epilogue of the prepared-weights decode kernel
     state->init_success = 1;

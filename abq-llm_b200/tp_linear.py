@@ -281,7 +281,17 @@ class AbqBackend:
         return out
 
     def glue_residual(self, a, b, out=None):
+        if out is None:
+            out = self.torch.empty_like(a)
+        if a.numel() % 8 == 0 and a.is_contiguous() and b.is_contiguous():
+            self.abq.add_half(a, b, out, a.numel())   # one launch, chained to the GEMMs around it
+            return out
         return self.torch.add(a, b, out=out)
 
     def glue_swiglu(self, gu, fl, out=None):
+        if out is None:
+            out = self.torch.empty((gu.shape[0], fl), dtype=gu.dtype, device=gu.device)
+        if fl % 8 == 0 and gu.is_contiguous() and gu.shape[1] == 2 * fl:
+            self.abq.swiglu_half(gu, out, gu.shape[0], fl)
+            return out
         return self.torch.mul(self.torch.nn.functional.silu(gu[:, :fl]), gu[:, fl:], out=out)

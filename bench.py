@@ -709,6 +709,94 @@ def tp_decode_measure(args, torch, dist, abq, rank, world):
             "hbm_bound_tokens_per_s_batch1": world * measured_peaks()[0] * 1e9 / wbytes}
 
 
+def reference_gpu_best():
+    """The reference's "time every configuration, keep the best" on this GPU: a sample of 24 of its own decode-tile
+    instantiations per width (W2A8, W3A8, W4A8; oracle/_ref/libabq_ref_gpu_sampled.so, compiled from its headers) on the four
+    sweep shapes at M = 1, signed operands, int32 output, weight copies rotating so that no launch finds its planes in L2.
+    A configuration counts only if its output equals this library's bit for bit; beside the best one: this library's time
+    for the very same GEMM (int32 output, prepared weights)."""
+    from oracle import oracle as O
+    try:
+        import torch
+    except ImportError:
+        return None
+    if not (O.ref_sampled_available() and torch.cuda.is_available()):
+        return None
+    abq = load_package()
+    B = abq.binding
+    L = O.ref_sampled()
+    configs = O.ref_sampled_configs()
+    rng = np.random.default_rng(5)
+    rows = []
+    side = torch.cuda.Stream()
+
+    def time_graph(launch, copies):
+        with torch.cuda.stream(side):
+            launch(0)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for c in range(copies):
+                    launch(c)
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (2 * copies)
+
+    for q in (2, 3, 4):
+        for (N, K) in SHAPES:
+            M, p = 1, 8
+            x = rng.integers(-128, 128, size=(M, K), dtype=np.int32)
+            w = rng.integers(-(1 << (q - 1)), 1 << (q - 1), size=(N, K), dtype=np.int32)
+            xp = torch.from_numpy(O.pack(x, p).view(np.int32)).cuda()
+            base = torch.from_numpy(O.pack(w, q).view(np.int32)).cuda()
+            copies = int(260e6 // (q * N * K // 8)) + 2
+            ws = [base] + [base.clone() for _ in range(copies - 1)]
+            out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+            ours = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+            work = torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, p, q)), dtype=torch.uint8, device="cuda")
+            prm = B.make_params(M, N, K, xp, base, ours, x_bits=p, w_bits=q, x_signed=True, w_signed=True, route=abq.ROUTE_I8_MMA,
+                                flags=abq.FLAG_PDL | abq.FLAG_WEIGHTS_PREPARED, workspace=work)
+            preps = [torch.empty(abq.gemm_prepared_weight_bytes(prm), dtype=torch.uint8, device="cuda")]
+            prm.w_prepared = preps[0].data_ptr()
+            st0 = abq.gemm_init(prm)
+            abq.gemm_prepare_weights(st0)
+            torch.cuda.synchronize()
+            preps += [preps[0].clone() for _ in range(copies - 1)]
+            states = []
+            for pr in preps:
+                prm.w_prepared = pr.data_ptr()
+                states.append(abq.gemm_init(prm))
+            abq.gemm_exec(st0)
+            torch.cuda.synchronize()
+            us_ours = time_graph(lambda c: abq.gemm_exec(states[c], side), copies)
+            best, passed, tried = None, 0, 0
+            for (i, xb, wb, name) in configs:
+                if wb != q:
+                    continue
+                tried += 1
+                out.zero_()
+                rc = L.abq_ref_sampled_gemm(i, xp.data_ptr(), base.data_ptr(), M, N, K, out.data_ptr(), 1, torch.cuda.current_stream().cuda_stream)
+                torch.cuda.synchronize()
+                if rc != 0 or not torch.equal(out, ours):
+                    continue
+                passed += 1
+                us = time_graph(lambda c, i=i: L.abq_ref_sampled_gemm(i, xp.data_ptr(), ws[c].data_ptr(), M, N, K, out.data_ptr(), 1, side.cuda_stream), copies)
+                if best is None or us < best[0]:
+                    best = (us, name)
+            rows.append({"wxay": f"W{q}A{p}", "M": M, "N": N, "K": K, "reference_best_us": None if best is None else round(best[0], 2),
+                         "reference_best_config": None if best is None else best[1], "configs_tried": tried, "configs_passed": passed,
+                         "this_library_us": round(us_ours, 2), "ratio": None if best is None else round(best[0] / us_ours, 2)})
+            del ws, preps, states, base
+    return rows
+
+
 def run_tp_decode(args, rank, world, local):
     """`--workload tp_decode` by itself: the tensor-parallel linear stack as the headline of its own JSON line."""
     import torch
@@ -756,6 +844,9 @@ def run_reference(args, rank, world):
     gpu_rows = reference_gpu_kernels()  # context only: the arm's value stays the reference's CPU implementation
     if gpu_rows:
         line["reference_gpu_kernels"] = gpu_rows
+    best_rows = reference_gpu_best()  # the reference's own search, on its own GPU kernels, on this GPU: context as well
+    if best_rows:
+        line["reference_gpu_best"] = best_rows
     emit(line)
 
 

@@ -266,6 +266,15 @@ ABQ_API abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint32_t
                                            int signal_offset, void *out, long n_halves, uint32_t *counter, int *status_word,
                                            abq_stream_t stream);
 
+/*
+ * The fp16 elementwise steps between the GEMMs of a decoder block, as single launches that join the programmatic-dependent-
+ * launch chain: out[m][f] = SiLU(gate_up[m][f]) * gate_up[m][F + f] over a fused gate+up output [M][2F] (the reference's
+ * FasterTransformer fork: genericActivation after the gate and up GEMMs, layers/FfnLayer.cc:407-421; SiLU in fp32, rounded to
+ * fp16 before the product) and out = a + b (its residual adds).  F and n multiples of 8, pointers 16-byte aligned.
+ */
+ABQ_API abq_status abq_swiglu_half(const void *gate_up, void *out, int M, int F, abq_stream_t stream);
+ABQ_API abq_status abq_add_half(const void *a, const void *b, void *out, long n, abq_stream_t stream);
+
 /* Bit-planes -> int8 codes, row-major [rows][K] (two's complement for signed; unsigned 8-bit codes are
  * stored as uint8).  Used by route B; exported because weight planes can be expanded once and cached. */
 ABQ_API abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, int K, int bits, int is_signed,

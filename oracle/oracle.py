@@ -20,6 +20,7 @@ _HERE = Path(__file__).resolve().parent
 _LIB_PATH = _HERE / "_build" / "libabq_oracle.so"
 _REF_PATH = _HERE / "_ref" / "libabq_ref.so"
 _REF_GPU_PATH = _HERE / "_ref" / "libabq_ref_gpu.so"
+_REF_SAMPLED_PATH = _HERE / "_ref" / "libabq_ref_gpu_sampled.so"
 
 _i32p = ctypes.POINTER(ctypes.c_int32)
 _u32p = ctypes.POINTER(ctypes.c_uint32)
@@ -38,6 +39,8 @@ def build(force: bool = False) -> None:
         subprocess.run(["make", "-C", str(_HERE), "ref", f"REF={ref_root}"], check=True, capture_output=True)
     if os.path.isdir(os.path.join(ref_root, "engine")) and (force or not _REF_GPU_PATH.exists()):
         subprocess.run(["make", "-C", str(_HERE), "refgpu", f"REF={ref_root}"], check=True, capture_output=True)
+    if os.path.isdir(os.path.join(ref_root, "engine")) and (force or not _REF_SAMPLED_PATH.exists()):
+        subprocess.run(["make", "-C", str(_HERE), "refsampled", f"REF={ref_root}"], check=True, capture_output=True)
 
 
 _lib = None
@@ -101,6 +104,37 @@ def ref_gpu() -> ctypes.CDLL:
         L.abq_ref_gpu_config.restype = ctypes.c_int
         _ref_gpu = L
     return _ref_gpu
+
+
+_ref_sampled = None
+
+
+def ref_sampled_available() -> bool:
+    return _REF_SAMPLED_PATH.exists()
+
+
+def ref_sampled() -> ctypes.CDLL:
+    """A sample of the reference's own W2A8 / W3A8 / W4A8 decode-tile instantiations (source generated from its lists)."""
+    global _ref_sampled
+    if _ref_sampled is None:
+        L = ctypes.CDLL(str(_REF_SAMPLED_PATH))
+        L.abq_ref_sampled_count.restype = ctypes.c_int
+        L.abq_ref_sampled_info.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.c_char_p, ctypes.c_int]
+        L.abq_ref_sampled_gemm.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                           ctypes.c_int, ctypes.c_void_p]
+        _ref_sampled = L
+    return _ref_sampled
+
+
+def ref_sampled_configs():
+    """[(index, x_bits, w_bits, name)] of the sampled reference configurations (all signed, one token row per tile)."""
+    L = ref_sampled()
+    out = []
+    for i in range(L.abq_ref_sampled_count()):
+        a, b, name = ctypes.c_int(), ctypes.c_int(), ctypes.create_string_buffer(96)
+        L.abq_ref_sampled_info(i, ctypes.byref(a), ctypes.byref(b), name, 96)
+        out.append((i, a.value, b.value, name.value.decode()))
+    return out
 
 
 def ref_gpu_config(cfg: int):

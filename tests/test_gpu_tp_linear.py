@@ -25,3 +25,25 @@ def test_block_linears_match_the_oracle_backend(abq, oracle, cuda, group, M):
     # two chained GEMMs with fp16 intermediates: a rounding difference of one intermediate moves a quantised code
     err = np.abs(got - ref)
     assert np.all(err <= 2.0 ** -6 * np.abs(ref) + 2.0 ** -7 * np.abs(ref).max()), f"max abs err {err.max():.4g} of {np.abs(ref).max():.4g}"
+
+
+@pytest.mark.parametrize("M,F", [(1, 11008), (8, 5504), (32, 1376), (5, 64)])
+def test_glue_kernels_match_torch(abq, cuda, M, F):
+    """The library's SiLU(gate) * up and residual-add launches against the torch elementwise kernels they replace in the block
+    (fp16; the SiLU uses the fast exponential: at most one fp16 step off before the product)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(M + F)
+    gu = (torch.randn((M, 2 * F), device="cuda", generator=g) * 2).half()
+    out = torch.empty((M, F), dtype=torch.float16, device="cuda")
+    abq.swiglu_half(gu, out, M, F)
+    want = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    torch.cuda.synchronize()
+    err = (out.float() - want.float()).abs()
+    assert bool((err <= 2.0 ** -9 * want.float().abs() + 1e-4).all()), float(err.max())
+    a, b = gu[:, :F].contiguous(), gu[:, F:].contiguous()
+    s = torch.empty_like(a)
+    abq.add_half(a, b, s, a.numel())
+    torch.cuda.synchronize()
+    assert torch.equal(s, a + b)
+    with pytest.raises(abq.AbqError):
+        abq.swiglu_half(gu, out, M, F + 4)
