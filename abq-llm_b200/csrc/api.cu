@@ -252,20 +252,58 @@ abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_stream_t st
     return ABQ_OK;
 }
 
+// Plans of the one-shot entry, kept per host thread: a caller that launches the same GEMM again (a wrapper class called once
+// per layer and token step) skips validation, planning and the driver's tensor-map encoding.  A plan depends on nothing but the
+// parameter block and the device, so equal bytes mean an equal plan; differing padding bytes only cost a miss.
+namespace {
+struct CachedPlan {
+    abq_gemm_params key;
+    int device;
+    bool used;
+    abq_gemm_state state;
+};
+constexpr int kPlanCacheEntries = 32;
+thread_local CachedPlan g_plan_cache[kPlanCacheEntries];
+thread_local int g_plan_cache_next = 0;
+} // namespace
+
 abq_status abq_gemm(const abq_gemm_params *params, abq_stream_t stream)
 {
-    abq_gemm_state st;
-    abq_status s = plan_gemm(params, &st, false); // one-shot: everything, the counter reset included, goes on the stream
-    if (s != ABQ_OK)
-        return s;
-    if (st.route == ABQ_ROUTE_I8_MMA) {
-        cudaError_t e = decode_clear_counters(&st, reinterpret_cast<cudaStream_t>(stream));
+    if (!params)
+        return ABQ_ERR_INVALID_ARG;
+    const abq_gemm_state *plan = nullptr;
+    abq_gemm_state fresh;
+    int device = -1;
+    const bool cacheable = params->allreduce == nullptr && cudaGetDevice(&device) == cudaSuccess; // a pointed-to block may change
+    if (cacheable)
+        for (int i = 0; i < kPlanCacheEntries && !plan; ++i) {
+            const CachedPlan &c = g_plan_cache[i];
+            if (c.used && c.device == device && std::memcmp(&c.key, params, sizeof(*params)) == 0)
+                plan = &c.state;
+        }
+    if (!plan) {
+        abq_status s = plan_gemm(params, &fresh, false); // one-shot: everything, the counter reset included, goes on the stream
+        if (s != ABQ_OK)
+            return s;
+        plan = &fresh;
+        if (cacheable) {
+            CachedPlan &c = g_plan_cache[g_plan_cache_next];
+            g_plan_cache_next = (g_plan_cache_next + 1) % kPlanCacheEntries;
+            c.key = *params;
+            c.device = device;
+            c.state = fresh;
+            c.used = true;
+            plan = &c.state;
+        }
+    }
+    if (plan->route == ABQ_ROUTE_I8_MMA) {
+        cudaError_t e = decode_clear_counters(plan, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) {
             set_last_cuda_error(e);
             return ABQ_ERR_CUDA;
         }
     }
-    return abq_gemm_exec(&st, stream);
+    return abq_gemm_exec(plan, stream);
 }
 
 static abq_status check_pack_args(const void *in, const void *planes, int rows, int K, int bits)

@@ -224,9 +224,10 @@ class AbqBackend:
         self.x_bits, self.x_scale, self.max_tokens = x_bits, x_scale, max_tokens
         import os
         several = dist is not None and dist.get_world_size() > 1
-        # how the row-parallel partials are summed: "fused" (inside the GEMM, default), "peer" (the library's one-shot
-        # all-reduce kernel after the GEMM) or "nccl" (torch.distributed)
-        self.reduce_kind = os.environ.get("ABQ_TP_REDUCE", "nccl" if os.environ.get("ABQ_TP_NCCL", "0") == "1" else "fused") if several else "none"
+        # how the row-parallel partials are summed: "peer" (the library's one-shot all-reduce kernel after the GEMM, default),
+        # "fused" (inside the GEMM's epilogue: same time at batch 1, slower from batch 8 up, where it ties the layer to the
+        # prepared-weights kernel although the plane-reading one is the faster for 9..16 rows) or "nccl" (torch.distributed)
+        self.reduce_kind = os.environ.get("ABQ_TP_REDUCE", "nccl" if os.environ.get("ABQ_TP_NCCL", "0") == "1" else "peer") if several else "none"
         if self.reduce_kind not in ("none", "fused", "peer", "nccl"):
             raise ValueError(f"ABQ_TP_REDUCE={self.reduce_kind}")
         self.peer_reduce = self.reduce_kind in ("fused", "peer")  # no NCCL call on the data path: the step can be one CUDA graph

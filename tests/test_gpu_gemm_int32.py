@@ -79,3 +79,31 @@ def test_split_k_counters_on_dirty_workspace(abq, oracle, cuda, one_shot):
             torch.cuda.synchronize()
             assert np.array_equal(out.cpu().numpy(), want)
     assert int(status.item()) == 0
+
+
+def test_one_shot_plan_reuse(abq, oracle, cuda):
+    """The one-shot entry keeps its plans per host thread.  The same parameter block again must give the same result, a block
+    that differs only in its pointers must get its own plan, and more distinct blocks than the cache holds must still all be
+    right (entries are replaced in turn)."""
+    import torch
+    from abq_llm_b200 import binding as B
+    p, q, K, N = 8, 4, 1024, 72
+    rng = np.random.default_rng(2024)
+    cases = []
+    for i in range(40):
+        M = 1 + i % 5
+        x = rand_codes(rng, M, K, p, True)
+        w = rand_codes(rng, N, K, q, False)
+        out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+        ws = torch.zeros(max(256, abq.gemm_workspace_bytes(M, N, K, p, q, abq.ROUTE_I8_MMA)), dtype=torch.uint8, device="cuda")
+        xp, wp = planes_dev(oracle, x, p), planes_dev(oracle, w, q)
+        prm = B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=True, w_signed=False, route=abq.ROUTE_I8_MMA, workspace=ws)
+        cases.append((prm, out, oracle.gemm_values_blas(x, w), (xp, wp, ws)))
+    for rounds in range(3):
+        for prm, out, want, _ in cases:
+            out.fill_(-1)
+            abq.gemm(prm)
+            abq.gemm(prm)
+        torch.cuda.synchronize()
+        for prm, out, want, _ in cases:
+            assert np.array_equal(out.cpu().numpy(), want)
