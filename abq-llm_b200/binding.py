@@ -96,6 +96,7 @@ def lib() -> ctypes.CDLL:
                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         L.abq_swiglu_half.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         L.abq_add_half.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_long, ctypes.c_void_p]
+        L.abq_rmsnorm_quantize_pack_half.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_float] + [ctypes.c_void_p] * 4 + [ctypes.c_int] * 4 + [ctypes.c_void_p]
         L.abq_unpack_int8.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_void_p]
         _lib = L
@@ -236,6 +237,14 @@ def pack_int4(nibbles, planes, rows: int, K: int, bits: int = 4, stream=None) ->
 def quantize_pack_half(x_half, scale, planes, rows: int, K: int, bits: int, mode: int = 0, stream=None) -> None:
     _check(lib().abq_quantize_pack_half(_ptr(x_half), _ptr(scale), _ptr(planes), rows, K, bits, mode, _stream(stream)),
            "abq_quantize_pack_half")
+
+
+def rmsnorm_quantize_pack_half(x_half, gamma, eps: float, rows: int, K: int, bits: int, mode: int, *, residual=None, sum_out=None, scale=None,
+                               row_scale_out=None, planes=None, y_out=None, stream=None) -> None:
+    """(residual add ->) RMSNorm -> quantiser -> planes in one launch; see abq_rmsnorm_quantize_pack_half in the header."""
+    _check(lib().abq_rmsnorm_quantize_pack_half(_ptr(x_half), _ptr(residual), _ptr(sum_out), _ptr(gamma), ctypes.c_float(eps), _ptr(scale),
+                                                _ptr(row_scale_out), _ptr(planes), _ptr(y_out), rows, K, bits, mode, _stream(stream)),
+           "abq_rmsnorm_quantize_pack_half")
 
 
 def quantize_weights_half(w_half, planes, scale, zero, N: int, K: int, bits: int, group_size: int = 0, symmetric: bool = False, stream=None) -> None:

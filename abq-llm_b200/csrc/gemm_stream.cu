@@ -186,8 +186,8 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
         static const int kShapes1[][2] = { { 1, 8 }, { 0, 16 }, { 0, 8 }, { 1, 4 }, { 0, 4 }, { 0, 2 } };
         static const int kShapes2[][2] = { { 0, 16 }, { 1, 8 }, { 0, 8 }, { 1, 4 }, { 0, 4 }, { 0, 2 } };
         for (const auto &shape : (P->MT == 2 ? kShapes2 : kShapes1)) {
-            if ((force_full && shape[0]) || (!force_warps && (shape[1] >= 8) != (pass == 0)))
-                continue;
+            if ((force_full == 1 && shape[0]) || (force_full == 2 && !shape[0]) || (!force_warps && (shape[1] >= 8) != (pass == 0)))
+                continue; // full: 1 = a CTA that fills the SM, 2 = one that leaves room for a second
             const size_t budget = shape[0] ? 112 * 1024 : 226 * 1024;
             {
                 const int nw = force_warps ? force_warps : shape[1];

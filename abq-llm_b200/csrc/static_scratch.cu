@@ -48,9 +48,11 @@ extern "C" abq_status abq_gemm_static_scratch(const abq_gemm_params *params, abq
 {
     if (!params)
         return ABQ_ERR_INVALID_ARG;
-    // "Prepared" weights are an expansion that an earlier call left in the plan's own workspace.  On the shared array
-    // the last call may have been any other GEMM, so whatever sits there is not this problem's weights: refuse.
-    if (params->flags & ABQ_FLAG_WEIGHTS_PREPARED)
+    // "Prepared" weights of the tensor-core route are an expansion that an earlier call left in the plan's own workspace.
+    // On the shared array the last call may have been any other GEMM, so whatever sits there is not this problem's
+    // weights: refuse.  The decode route keeps its prepared copy in the caller's own buffer (w_prepared) and uses the
+    // workspace for split-K partial sums only, so that combination, asked for by name, is served.
+    if ((params->flags & ABQ_FLAG_WEIGHTS_PREPARED) && !(params->route == ABQ_ROUTE_I8_MMA && params->w_prepared))
         return ABQ_ERR_INVALID_ARG;
     const size_t need = abq_gemm_workspace_bytes(params->M, params->N, params->K, params->x_bits, params->w_bits, params->route);
     if (need > (size_t)ABQ_STATIC_SCRATCH_BYTES)

@@ -124,7 +124,7 @@ class AbqLinear:
     done inside the GEMM (``fused_reduce``: abq_fused_allreduce over symmetric memory)."""
 
     def __init__(self, abq, torch, codes, scale, zero, w_bits: int, group: int, x_bits: int = 8, x_scale: float = 16.0,
-                 max_tokens: int = 64, make_out=None, fused_reduce=None, status=None):
+                 max_tokens: int = 64, make_out=None, fused_reduce=None, status=None, fused_rows: int = 1 << 30):
         self.abq, self.torch = abq, torch
         self.make_out = make_out  # row-parallel layers: output buffers that the other ranks can read
         self.out_features, self.in_features = codes.shape
@@ -143,6 +143,8 @@ class AbqLinear:
         self.prepared = None
         self.prepared_done = False
         self.fused = None
+        self.fused_rows = fused_rows  # token counts up to this use the fused sum (where there is one), larger ones make_out
+        self.on_fused_output = None   # told the output buffer of every plan whose GEMM already delivers the sum
         if fused_reduce is not None:  # (dist, world, rank): receive buffers + flags of all ranks in one symmetric allocation
             import torch.distributed._symmetric_memory as symm
             dist, world, rank = fused_reduce
@@ -165,7 +167,8 @@ class AbqLinear:
         key = M
         if key not in self.plans:
             B = self.abq.binding
-            out = (self.make_out(M, self.out_features) if self.make_out else
+            fused = self.fused if M <= self.fused_rows else None
+            out = (self.make_out(M, self.out_features) if (self.make_out and fused is None) else
                    self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda"))
             x_view = self.torch.empty((M, self.in_features), dtype=self.torch.float16, device="cuda")  # the GEMM reads fp16 here
             flags = self.abq.FLAG_PDL | self.abq.FLAG_X_HALF
@@ -182,19 +185,21 @@ class AbqLinear:
                 try:
                     st = self.abq.gemm_init(B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out,
                                                           flags=flags | self.abq.FLAG_WEIGHTS_PREPARED, route=self.abq.ROUTE_I8_MMA,
-                                                          w_prepared=self.prepared, allreduce=None if self.fused is None else self.fused["desc"], **kw))
+                                                          w_prepared=self.prepared, allreduce=None if fused is None else fused["desc"], **kw))
                 except self.abq.AbqError:
                     st = None
-                    if self.fused is not None:
+                    if fused is not None:
                         raise
                 if st is not None and not self.prepared_done:
                     self.abq.gemm_prepare_weights(st)
                     self.torch.cuda.synchronize()  # a PDL GEMM must not be launched behind the kernel that writes its weights
                     self.prepared_done = True
             if st is None:
-                if self.fused is not None:
+                if fused is not None:
                     raise RuntimeError("the fused all-reduce needs the prepared-weights decode kernel")
                 st = self.abq.gemm_init(probe)
+            if fused is not None and self.on_fused_output is not None:
+                self.on_fused_output(out)
             self.plans[key] = (st, x_view, out)
         return self.plans[key]
 
@@ -224,31 +229,29 @@ class AbqBackend:
         self.x_bits, self.x_scale, self.max_tokens = x_bits, x_scale, max_tokens
         import os
         several = dist is not None and dist.get_world_size() > 1
-        # how the row-parallel partials are summed: "peer" (the library's one-shot all-reduce kernel after the GEMM, default),
-        # "fused" (inside the GEMM's epilogue: same time at batch 1, slower from batch 8 up, where it ties the layer to the
-        # prepared-weights kernel although the plane-reading one is the faster for 9..16 rows) or "nccl" (torch.distributed)
-        self.reduce_kind = os.environ.get("ABQ_TP_REDUCE", "nccl" if os.environ.get("ABQ_TP_NCCL", "0") == "1" else "peer") if several else "none"
-        if self.reduce_kind not in ("none", "fused", "peer", "nccl"):
+        # how the row-parallel partials are summed: "peer" (the library's one-shot all-reduce kernel after the GEMM), "fused"
+        # (inside the GEMM's epilogue), "nccl" (torch.distributed), or "auto" (default) = whichever of the first two measured
+        # faster: fused for up to 8 tokens on 4 or more ranks (the one-shot kernel reads world x the bytes and needs a closing
+        # round), peer otherwise (the fused form ties the layer to the prepared-weights kernel, and for 9..16 rows the
+        # plane-reading kernel is the faster one; on 2 ranks the two are level at batch 1)
+        self.reduce_kind = os.environ.get("ABQ_TP_REDUCE", "nccl" if os.environ.get("ABQ_TP_NCCL", "0") == "1" else "auto") if several else "none"
+        if self.reduce_kind not in ("none", "auto", "fused", "peer", "nccl"):
             raise ValueError(f"ABQ_TP_REDUCE={self.reduce_kind}")
-        self.peer_reduce = self.reduce_kind in ("fused", "peer")  # no NCCL call on the data path: the step can be one CUDA graph
+        self.fused_rows = {"fused": 1 << 30, "auto": 8 if several and dist.get_world_size() >= 4 else 0}.get(self.reduce_kind, 0)
+        if self.reduce_kind == "auto" and "ABQ_TP_FUSED_ROWS" in os.environ:
+            self.fused_rows = int(os.environ["ABQ_TP_FUSED_ROWS"])
+        self.peer_reduce = self.reduce_kind in ("auto", "fused", "peer")  # no NCCL call on the data path: the step can be one CUDA graph
         self._reduced = {}
         self._fused_outputs = set()
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
 
     def make_linear(self, codes, scale, zero, w_bits, group, reduce_output=False):
-        make_out = self._peer_visible_output if (reduce_output and self.reduce_kind == "peer") else None
-        fused = (self.dist, self.dist.get_world_size(), self.dist.get_rank()) if (reduce_output and self.reduce_kind == "fused") else None
+        make_out = self._peer_visible_output if (reduce_output and self.reduce_kind in ("auto", "peer")) else None
+        fused = (self.dist, self.dist.get_world_size(), self.dist.get_rank()) if (reduce_output and self.fused_rows > 0) else None
         layer = AbqLinear(self.abq, self.torch, codes, scale, zero, w_bits, group, self.x_bits, self.x_scale, self.max_tokens, make_out,
-                          fused_reduce=fused, status=self.status)
-        if fused is not None:
-            layer.owner = self
-            plan = layer._plan
-
-            def plan_and_note(M, _plan=plan):
-                res = _plan(M)
-                self._fused_outputs.add(res[2].data_ptr())  # all_reduce() leaves these alone: the GEMM already summed them
-                return res
-            layer._plan = plan_and_note
+                          fused_reduce=fused, status=self.status, fused_rows=self.fused_rows)
+        # all_reduce() leaves the outputs of fused plans alone: the GEMM already summed them
+        layer.on_fused_output = lambda out: self._fused_outputs.add(out.data_ptr())
         return layer
 
     # ---- all-reduce of the row-parallel partials.  Several ranks on one node: the partial buffers live in symmetric

@@ -48,7 +48,7 @@ def rows_class(M):
     return 1 if rows == 1 else 2 if rows == 2 else 4 if rows <= 4 else 8 if rows <= 8 else 16
 
 
-def candidates(M, group, quick):
+def candidates(M, group, quick, K=0):
     rc = rows_class(M)
     mps = [m for m in (1, 2, 4, 8) if m >= rc] if (group and rc <= 8) else [0]
     if quick:
@@ -57,9 +57,11 @@ def candidates(M, group, quick):
     for mp in mps:
         gs = 8 // mp if mp else 1
         for cu in sorted({gs, 2 * gs, 4 * gs} & set(range(1, 9))):
-            for full, warps in ((0, 8), (1, 8), (1, 16)):
-                for ctas in ((148, 296) if not full else (148,)):
-                    for slices in ((0, 2, 3) if rc == 16 else (0,)):
+            for full, warps in ((0, 8), (1, 8), (1, 16)) + (((2, 8),) if rc == 16 else ()):
+                for ctas in ((148, 296) if full != 1 else (148,)):
+                    for slices in ((0, 2, 3, 4, 8) if rc == 16 else (0, 2, 4) if K >= 8192 else (0,)):
+                        if full == 2 and slices == 0:
+                            continue
                         yield dict(mp=mp, cu=cu, ring=0, warps=warps, full=full, ctas=ctas, slices=slices, prefill=0, planes=0)
 
 
@@ -68,6 +70,8 @@ def main():
     ap.add_argument("--out", default=str(PKG / "abq_tune_table.txt"))
     ap.add_argument("--problems", default="sweep,tp")
     ap.add_argument("--quick", action="store_true", help="fewer candidates per problem")
+    ap.add_argument("--rows", type=int, default=0, help="only the problems with this many token rows")
+    ap.add_argument("--min-k", type=int, default=0, help="only the problems with at least this many features")
     args = ap.parse_args()
     import torch
     if not torch.cuda.is_available():
@@ -88,6 +92,8 @@ def main():
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     lines = ["# w_bits x_bits rows_class N K grouped group_size : mp cu ring warps full ctas slices prefill planes   (us best, us heuristic)"]
     for (q, p, M, N, K, group) in problems:
+        if (args.rows and M != args.rows) or K < args.min_k:
+            continue
         codes = torch.randint(0, 1 << q, (N, K), dtype=torch.int32, device="cuda", generator=gen)
         planes = torch.empty((q, N, K // 32), dtype=torch.int32, device="cuda")
         abq.pack_int32(codes, planes, N, K, q)
@@ -120,6 +126,8 @@ def main():
                     os.environ[v] = str(hints[k])
             try:
                 states = [abq.gemm_init(params(c)) for c in clones]
+                if hints and not hints.get("planes") and abq.state_kernel(states[0]) != "stream_kernel":
+                    return None  # no launch shape with these hints: the plan fell back to the kernel that reads the planes
             except abq.AbqError:
                 return None
             finally:
@@ -148,13 +156,22 @@ def main():
 
         base = time_plan(None)
         best, best_h = base, None
-        for h in candidates(M, group, args.quick):
+        tried = planned = 0
+        runner_up = (None, None)  # the best candidate on the prepared-weights kernel, whoever wins
+        for h in candidates(M, group, args.quick, K):
             us = time_plan(h)
-            if us is not None and us < best * 0.98:  # a candidate has to win by more than the noise to replace the heuristic
+            tried += 1
+            if us is None:
+                continue
+            planned += 1
+            if not h["planes"] and (runner_up[0] is None or us < runner_up[0]):
+                runner_up = (us, h)
+            if us < best * 0.98:  # a candidate has to win by more than the noise to replace the heuristic
                 best, best_h = us, h
         if int(status.item()) != 0:
             raise SystemExit(f"device status word {int(status.item())}: a bounded wait expired")
-        print(f"W{q}A{p} M={M} {N}x{K} g{group}: heuristic {base:.2f} us, best {best:.2f} us {best_h}", file=sys.stderr, flush=True)
+        print(f"W{q}A{p} M={M} {N}x{K} g{group}: heuristic {base:.2f} us, best {best:.2f} us {best_h}; {planned} of {tried} candidates planned, "
+              f"best on prepared weights {runner_up[0] and round(runner_up[0], 2)} us {runner_up[1]}", file=sys.stderr, flush=True)
         if best_h is not None:
             lines.append(f"{q} {p} {rows_class(M)} {N} {K} {1 if group else 0} {group} : " + " ".join(str(best_h[f]) for f in FIELDS) + f"   # {best:.2f} {base:.2f}")
         del clones, prep, planes, codes

@@ -133,7 +133,7 @@ def _params(abq, g, xbuf, obuf, kind, status):
         flags |= abq.FLAG_WEIGHTS_PREPARED
         prepared = g["prepared"]
     return B.make_params(g["M"], g["N"], g["K"], xbuf, g["planes"], obuf, x_bits=XBITS, w_bits=g["q"], x_signed=True, w_signed=False,
-                         out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP, group_size=GROUP, w_scale=g["w_scale"], w_zero=g["w_zero"],
+                         out_dtype=abq.OUT_FP16, scale_mode=abq.SCALE_GROUP, group_size=g.get("group", GROUP), w_scale=g["w_scale"], w_zero=g["w_zero"],
                          flags=flags, workspace=g["work"], status_word=status, w_prepared=prepared)
 
 
@@ -396,6 +396,36 @@ def prefill_leg(torch, abq, reps=10):
             "peak_source": "2 x MEASURED_PEAKS.json bf16_tflops" if peak else None,
             "library_int8_TOPS": None if lib_rate is None else round(lib_rate, 1), "library_int8_source": "torch._int_mm 8192^3, best of 10, this run",
             "cases": rows}
+
+
+def g64_leg(torch, abq, status, hbm_peak):
+    """Scale groups of 64 (the W2A8 g64 configuration, LLaMA-2-13B shapes): decode GEMMs on prepared weights (64-feature
+    units), timed like the rows of `detail`."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(64)
+    q, group = 2, 64
+    gemms = []
+    for (M, N, K) in ((1, 5120, 5120), (1, 13824, 5120), (1, 5120, 13824), (16, 13824, 5120)):
+        codes = torch.randint(0, 1 << q, (N, K), dtype=torch.int32, device="cuda", generator=gen)
+        planes = torch.empty((q, N, K // 32), dtype=torch.int32, device="cuda")
+        abq.pack_int32(codes, planes, N, K, q)
+        x = torch.randint(-128, 128, (M, K), dtype=torch.int32, device="cuda", generator=gen)
+        dev_x = torch.empty((XBITS, M, K // 32), dtype=torch.int32, device="cuda")
+        abq.pack_int32(x, dev_x, M, K, XBITS)
+        g = dict(q=q, M=M, N=N, K=K, group=group, planes=planes, dev_x=dev_x,
+                 w_scale=(torch.rand((N, K // group), device="cuda", generator=gen) * 0.019 + 0.001).to(torch.float16),
+                 w_zero=torch.randint(0, 1 << q, (N, K // group), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8),
+                 work=torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, XBITS, q)), dtype=torch.uint8, device="cuda"),
+                 out=torch.empty((M, N), dtype=torch.float16, device="cuda"), bytes=algorithmic_bytes(M, N, K, XBITS, q, group), ops=2 * M * N * K)
+        nbytes = abq.gemm_prepared_weight_bytes(_params(abq, g, dev_x, g["out"], "planes", status))
+        g["prepared"] = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        abq.gemm_prepare_weights(abq.gemm_init(_params(abq, g, dev_x, g["out"], "prepared", status)))
+        gemms.append(g)
+    torch.cuda.synchronize()
+    rows = per_config_detail(torch, abq, gemms, status, hbm_peak, "prepared")
+    for r in rows:
+        r["group_size"] = group
+    return rows
 
 
 def config0_leg(torch, abq, hbm_peak):
@@ -695,7 +725,8 @@ def tp_decode_measure(args, torch, dist, abq, rank, world):
         fn = (lambda i: graph.replay()) if graph is not None else ((lambda i: step_pieces()) if pieces else (lambda i: step()))
         n = args.tp_steps
         ms, _ = timed(torch, dist, fn, n, 3)
-        results.append({"batch": M, "steps": n, "ms_per_step": ms / n, "tokens_per_s": M * n / (ms * 1e-3), "cuda_graph": "whole step" if graph is not None else ("between the all-reduces" if pieces else "no")})
+        kind = "none" if world == 1 else ({"auto": "fused" if M <= backend.fused_rows else "peer"}.get(backend.reduce_kind, backend.reduce_kind))
+        results.append({"batch": M, "steps": n, "ms_per_step": ms / n, "tokens_per_s": M * n / (ms * 1e-3), "all_reduce": kind, "cuda_graph": "whole step" if graph is not None else ("between the all-reduces" if pieces else "no")})
     if int(backend.status.item()) != 0:
         raise SystemExit(f"tp_decode: device status word {int(backend.status.item())} (a bounded wait expired): the numbers are void")
     wbytes = layers * sum(sp.out_features * sp.in_features for sp in tp.llama_block_specs(hidden, ffn)) * q // 8
@@ -979,6 +1010,7 @@ def main():
         base = cpu_baseline_sample("reference")
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if extras and not args.no_prefill:
+        line["g64"] = g64_leg(torch, abq, status, peak)
         line["config0"] = config0_leg(torch, abq, peak)
         line["prefill"] = prefill_leg(torch, abq)
         line["routes"] = routes_leg(torch, abq)

@@ -275,6 +275,24 @@ ABQ_API abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint32_t
 ABQ_API abq_status abq_swiglu_half(const void *gate_up, void *out, int M, int F, abq_stream_t stream);
 ABQ_API abq_status abq_add_half(const void *a, const void *b, void *out, long n, abq_stream_t stream);
 
+/*
+ * (Residual add ->) RMSNorm -> activation quantiser -> bit-planes in one launch, one read of the row.  Replaces the chain
+ * the reference's FasterTransformer fork runs in front of every quantized GEMM: invokeGeneralAddBiasResidualPreLayerNorm /
+ * invokeGeneralT5LayerNorm (fp16 output) followed by ABQGEMMWrapper::pack (kernels/abqgemm/abq_gemm_wrapper.cu:79-98).
+ *   s = x (+ residual, fp16 add; written to sum_out_half when that is given)
+ *   y = half((float(s) * rsqrt(mean(s^2) + eps)) * float(gamma))        gamma: fp16 [K]; written to y_out_half when given
+ *   planes[bits][rows][K/32] = codes of y:  mode 0  (int)(y * half(scale[0]))              the wrapper's quantiser
+ *                                           mode 1  clamp(rint(float(y) / scale[row]))     given per-token scales
+ *                                           mode 2  as mode 1 with scale[row] = max|y| / (2^(bits-1) - 1), chosen here and
+ *                                                   written to row_scale_out[rows] (the GEMM epilogue's x_scale)
+ * The planes equal abq_quantize_pack_half applied to y bit for bit.  planes may be NULL (normalisation only).
+ * K a multiple of 128, at most 16384; fp16 pointers 16-byte aligned.  Joins a programmatic-dependent-launch chain (gamma
+ * must be complete before the preceding kernel starts).
+ */
+ABQ_API abq_status abq_rmsnorm_quantize_pack_half(const void *x_half, const void *residual_half, void *sum_out_half, const void *gamma_half,
+                                                  float eps, const float *scale, float *row_scale_out, void *planes, void *y_out_half,
+                                                  int rows, int K, int bits, int mode, abq_stream_t stream);
+
 /* Bit-planes -> int8 codes, row-major [rows][K] (two's complement for signed; unsigned 8-bit codes are
  * stored as uint8).  Used by route B; exported because weight planes can be expanded once and cached. */
 ABQ_API abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, int K, int bits, int is_signed,
@@ -284,8 +302,10 @@ ABQ_API abq_status abq_unpack_int8(const void *planes, void *out_i8, int rows, i
  * abq_gemm for callers that cannot supply scratch memory.  No counterpart in the reference.
  *
  * Same contract as abq_gemm, except that params->workspace / workspace_bytes are ignored and that
- * ABQ_FLAG_WEIGHTS_PREPARED is refused (ABQ_ERR_INVALID_ARG: prepared weights live in a workspace of their own, and
- * the shared array holds whatever the last call left).  The scratch the chosen route needs is taken from one array
+ * ABQ_FLAG_WEIGHTS_PREPARED is refused (ABQ_ERR_INVALID_ARG) wherever the prepared weights would live in the workspace
+ * (the shared array holds whatever the last call left): it is accepted only with route == ABQ_ROUTE_I8_MMA and a
+ * w_prepared buffer, where the prepared copy is the caller's own and the scratch holds split-K partial sums only.
+ * The scratch the chosen route needs is taken from one array
  * of ABQ_STATIC_SCRATCH_BYTES bytes in the library's device code: a GPU holds it from the moment the CUDA runtime
  * loads that code on it (with lazy loading: the first call on that GPU) until the process exits.  The call allocates nothing (no cudaMalloc, no
  * cudaFree, no allocating library routine), which is what a caller needs that runs inside a stream-ordered forward

@@ -112,3 +112,18 @@ def test_missing_library_fails_loudly(abq, monkeypatch, tmp_path):
     monkeypatch.setattr(B, "lib_path", lambda: tmp_path / "nope.so")
     with pytest.raises(FileNotFoundError):
         B.lib()
+
+
+def test_torch_operators_are_registered_and_refuse_cpu_tensors(abq):
+    """abq_b200::gemm_planes / linear_half exist after importing the operator module, have shape functions (a traced graph
+    can hold them) and have no CPU kernel: a CPU tensor is an error, not a silent fallback."""
+    import importlib
+    import torch
+    importlib.import_module("abq_llm_b200.torch_ops")
+    assert hasattr(torch.ops.abq_b200, "gemm_planes") and hasattr(torch.ops.abq_b200, "linear_half")
+    x = torch.zeros((8, 1, 4), dtype=torch.int32)
+    w = torch.zeros((2, 16, 4), dtype=torch.int32)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.abq_b200.gemm_planes(x, w, 8, 2, True)
+    meta = torch.ops.abq_b200.gemm_planes(x.to("meta"), w.to("meta"), 8, 2, True)
+    assert tuple(meta.shape) == (1, 16) and meta.dtype == torch.int32

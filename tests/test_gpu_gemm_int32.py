@@ -107,3 +107,17 @@ def test_one_shot_plan_reuse(abq, oracle, cuda):
         torch.cuda.synchronize()
         for prm, out, want, _ in cases:
             assert np.array_equal(out.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("M,N,K,p,q,signed", [(1, 40, 128, 8, 2, True), (3, 96, 1152, 3, 5, False), (16, 72, 4096, 8, 2, True), (37, 64, 2176, 8, 8, True),
+                                              (5, 200, 11008, 4, 4, False), (64, 48, 640, 2, 2, False), (9, 33, 1024, 7, 3, True), (130, 32, 256, 1, 1, False),
+                                              (2, 4096, 4096, 8, 2, True), (20, 256, 1280, 6, 6, True)])
+def test_plane_stacked_b1_route(abq, oracle, cuda, M, N, K, p, q, signed):
+    """The 1-bit route with the planes stacked along the rows of both operands: widths that do not divide a tile of eight
+    stacked rows (tokens straddling tiles), more tokens than one CTA takes, weight rows that do not fill the last CTA, a K
+    that is not a whole number of 1024-feature stages."""
+    rng = np.random.default_rng(M * 131 + N + K + p * 7 + q)
+    x, w = rand_codes(rng, M, K, p, signed), rand_codes(rng, N, K, q, signed)
+    got, _ = run_gemm(abq, planes_dev(oracle, x, p), planes_dev(oracle, w, q), M, N, K, x_bits=p, w_bits=q, x_signed=signed, w_signed=signed,
+                      route=abq.ROUTE_B1_MMA)
+    assert np.array_equal(got, oracle.gemm_values_blas(x, w))

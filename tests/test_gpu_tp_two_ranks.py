@@ -25,4 +25,5 @@ def test_peer_all_reduce_equals_nccl(cuda):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert res.stdout.count("PEER_EQUALS_NCCL True") == 2, res.stdout[-2000:]
     assert res.stdout.count("FUSED_EQUALS_NCCL True") == 2, res.stdout[-2000:]
+    assert res.stdout.count("AUTO_EQUALS_NCCL True") == 2, res.stdout[-2000:]
     assert res.stdout.count("MATCHES_UNSHARDED_ORACLE True") == 2, res.stdout[-2000:]

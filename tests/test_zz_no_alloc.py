@@ -89,3 +89,26 @@ def test_static_scratch_refuses_prepared_weights(abq, cuda):
     with pytest.raises(abq.AbqError) as err:
         abq.gemm_static_scratch(p)
     assert err.value.status == 1  # ABQ_ERR_INVALID_ARG
+
+
+def test_static_scratch_serves_decode_route_with_callers_prepared_copy(abq, oracle, cuda):
+    """The one prepared-weights combination the shared array can serve: the decode route with the prepared copy in the
+    caller's own w_prepared buffer (the scratch then only holds split-K partial sums, here 16 tokens with K = 11008)."""
+    from abq_llm_b200 import binding as B
+    M, N, K, p, q = 16, 512, 11008, 8, 4
+    rng = np.random.default_rng(29)
+    x, w = rand_codes(rng, M, K, p, True), rand_codes(rng, N, K, q, False)
+    xp, wp = planes_dev(oracle, x, p), planes_dev(oracle, w, q)
+    out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    ws = torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, p, q, abq.ROUTE_I8_MMA)), dtype=torch.uint8, device="cuda")
+    kw = dict(x_bits=p, w_bits=q, x_signed=True, w_signed=False, route=abq.ROUTE_I8_MMA, flags=abq.FLAG_WEIGHTS_PREPARED)
+    nbytes = abq.gemm_prepared_weight_bytes(B.make_params(M, N, K, xp, wp, out, **kw))
+    assert nbytes > 0
+    prep = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    abq.gemm_prepare_weights(abq.gemm_init(B.make_params(M, N, K, xp, wp, out, workspace=ws, w_prepared=prep, **kw)))
+    torch.cuda.synchronize()
+    for _ in range(2):
+        out.fill_(-1)
+        abq.gemm_static_scratch(B.make_params(M, N, K, xp, wp, out, w_prepared=prep, **kw))
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), oracle.gemm_values_blas(x, w))

@@ -34,10 +34,12 @@ def main():
         zero = torch.randint(0, 1 << q, (sp.out_features,), dtype=torch.int32, device="cuda", generator=gen).to(torch.uint8)
         weights.append((codes, scale, zero))
     outs = {}
-    for mode in ("fused", "peer", "nccl"):
+    os.environ["ABQ_TP_FUSED_ROWS"] = "8"   # "auto" on two ranks would never pick the fused form by itself: make it mix the two
+    for mode in ("fused", "peer", "nccl", "auto"):
         os.environ["ABQ_TP_REDUCE"] = mode
         be = tp.AbqBackend(abq, torch, dist, x_bits=8, x_scale=8.0, max_tokens=32)
         assert be.reduce_kind == mode and be.peer_reduce == (mode != "nccl")
+        assert be.fused_rows == {"fused": 1 << 30, "auto": 8}.get(mode, 0)
         block = tp.TensorParallelBlockLinears(be, hidden, ffn, rank, world, weights, q, 0)
         for M in (1, 8, 32):
             gen.manual_seed(M)
@@ -60,6 +62,8 @@ def main():
     print(f"rank {rank} PEER_EQUALS_NCCL {ok}", flush=True)
     ok = all(torch.equal(outs[("fused", M)], outs[("nccl", M)]) for M in keys)
     print(f"rank {rank} FUSED_EQUALS_NCCL {ok}", flush=True)
+    ok = all(torch.equal(outs[("auto", M)], outs[("nccl", M)]) for M in keys)
+    print(f"rank {rank} AUTO_EQUALS_NCCL {ok}", flush=True)
 
     # ... and against the unsharded block computed by the CPU oracle (one rank, numpy stand-in for the GEMMs): what the
     # two ranks produce together is the model's result, not merely the same thing twice.  Tolerance: twice that of the
