@@ -39,7 +39,7 @@ struct UmmaArgs {
     const uint8_t *w_zero;
     const float *x_scale;
     const int *xsum; // per-token code sums (only with per-channel zero points)
-    int kb_per_group;  // ABQ_SCALE_GROUP: 128-byte K blocks per scale group
+    int kb_per_group;  // ABQ_SCALE_GROUP: 128-byte K blocks per scale group; 0: groups of 64 features, two per K block
     int scale_groups;  // ABQ_SCALE_GROUP: scale groups per weight row
     int out_dtype, scale_mode;
     uint32_t idesc;
@@ -674,6 +674,36 @@ __global__ void __launch_bounds__(kGroupThreads, 1) umma_group_kernel(const __gr
             int kc = 0, gc = 0; // K blocks and scale groups issued so far, over all tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (a.kb_per_group == 0) {
+                    // scale groups of 64 features: a K block holds two groups; its first two MMAs start one accumulator, its
+                    // last two the next
+                    for (int kb = 0; kb < k_blocks && ok; ++kb, ++kc) {
+                        const int s = kc % a.stages;
+                        ok = mbar_wait_bounded(&full[s], (kc / a.stages) & 1, a.status, STATUS_TIMEOUT_TMA);
+                        if (!ok)
+                            break;
+                        tmem_fence_after();
+                        const uint32_t sa = smem_u32(smem + (size_t)s * kStageBytes), sb = sa + kABytes;
+                        const uint64_t da = make_smem_desc_sw128(sa), db = make_smem_desc_sw128(sb);
+                        for (int h = 0; h < 2 && ok; ++h, ++gc) {
+                            const int b = gc % kAccs;
+                            if (gc >= kAccs) {
+                                ok = mbar_wait_bounded(&acc_empty[b], ((gc / kAccs) - 1) & 1, a.status, STATUS_TIMEOUT_PIPE);
+                                if (!ok)
+                                    break;
+                                tmem_fence_after();
+                            }
+                            const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
+#pragma unroll
+                            for (int k = 0; k < 2; ++k)
+                                umma_i8(tmem_d, da + (uint64_t)((2 * h + k) * 32 >> 4), db + (uint64_t)((2 * h + k) * 32 >> 4), a.idesc, k != 0);
+                            umma_commit(&acc_full[b]);
+                        }
+                        if (ok)
+                            umma_commit(&empty[s]);
+                    }
+                    continue;
+                }
                 for (int g = 0; g < G && ok; ++g, ++gc) {
                     const int b = gc % kAccs;
                     if (gc >= kAccs) { // the epilogue has drained this accumulator's previous group
@@ -864,8 +894,8 @@ abq_status umma_plan(abq_gemm_state *st)
     if (grouped) {
         // drained per scale group (umma_group_kernel): groups of whole K blocks; zero points are folded into the int8
         // weight codes, which needs w - z to fit: unsigned weights of at most 7 bits
-        if (p.group_size % kUmmaBK != 0 || p.out_dtype != ABQ_OUT_FP16)
-            return ABQ_ERR_UNSUPPORTED;
+        if ((p.group_size % kUmmaBK != 0 && p.group_size != kUmmaBK / 2) || p.out_dtype != ABQ_OUT_FP16)
+            return ABQ_ERR_UNSUPPORTED; // (groups of 64: two per K block, see the MMA warp of umma_group_kernel)
         if (p.w_zero && (p.w_signed || p.w_bits > 7))
             return ABQ_ERR_UNSUPPORTED;
         if ((size_t)scale_groups * kGroupBN * 4 + 3 * (size_t)(kUmmaBM + kGroupBN) * kUmmaBK > 216 * 1024)
@@ -1075,7 +1105,7 @@ cudaError_t umma_launch(const abq_gemm_state *st, cudaStream_t stream)
     }
     if (st->tile[2]) {
         // |acc of a group| < 2^22 with signed activations (|x| <= 128), |w - z| <= 255 and one K block per group
-        const bool magic = p.x_signed && a.kb_per_group == 1;
+        const bool magic = p.x_signed && a.kb_per_group <= 1;
         return magic ? launch_group<true>(st, a, stream) : launch_group<false>(st, a, stream);
     }
     switch (BN) {

@@ -52,7 +52,8 @@ def test_int32_full_size_per_width(abq, oracle, cuda, case):
     assert st.route == abq.ROUTE_I8_UMMA
     want = oracle.gemm_values_blas(x, w)
     assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} of {got.size} differ"
-    scale = rng.uniform(0.001, 0.02, size=N).astype(np.float16)
+    # channel scales that keep every product inside the fp16 range whatever the widths (6-bit x 6-bit sums reach 1.6e7)
+    scale = (rng.uniform(0.5, 1.0, size=N) * (30000.0 / max(1.0, float(np.abs(want).max())))).astype(np.float16)
     got16, _ = run_gemm(abq, xp, wp, M, N, K, x_bits=p, w_bits=q, x_signed=signed, w_signed=signed, out_fp16=True,
                         scale_mode=abq.SCALE_CHANNEL, w_scale=dev(scale))
     check_close(got16, want.astype(np.float64) * scale.astype(np.float64)[None, :])
@@ -180,6 +181,12 @@ GROUP_CASES = [
     (2048, 2048, 512, 8, True, 4, False, 128, True, "umma"),      # several tiles per CTA
     (100, 512, 4096, 8, True, 8, False, 128, True, "mma"),        # w - z does not fit int8: 16 rows per launch instead
     (33, 96, 1280, 8, True, 3, False, 640, True, "umma"),
+    # scale groups of 64 features (two per K block): the W2A8 g64 configuration at LLaMA-2-13B widths, ragged tiles, 4-bit
+    (40, 320, 1024, 8, True, 2, False, 64, True, "umma"),
+    (300, 1000, 1152, 8, True, 4, False, 64, True, "umma"),
+    (512, 5120, 5120, 8, True, 2, False, 64, True, "umma"),
+    (256, 640, 13824, 8, True, 2, False, 64, True, "umma"),
+    (200, 520, 1536, 4, False, 4, False, 64, False, "umma"),
 ]
 
 
