@@ -18,6 +18,7 @@ namespace {
 struct StreamPlan {
     int magic;
     int uw, nw, cu, ring, prefill, slices, units_per_slice, ctas_per_slice, MT, MP, grouped, unit_bytes, max_tiles_per_cta;
+    int rows_per_launch; // 16, or 32 (MT == 4) for problems of more than 16 token rows
 };
 constexpr int kStreamMagic = 0x5354524d;
 
@@ -47,8 +48,7 @@ struct TuneEntry {
 
 int rows_class_of(int M)
 {
-    const int rows = M < 16 ? M : 16;
-    return rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : rows <= 8 ? 8 : 16;
+    return M == 1 ? 1 : M == 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : M <= 16 ? 16 : 32;
 }
 
 // Table file: text, one entry per line, '#' starts a comment:
@@ -89,13 +89,13 @@ const std::vector<TuneEntry> &tune_table()
     return table;
 }
 
-StreamHints hints_for(const abq_gemm_params &p)
+StreamHints hints_for(const abq_gemm_params &p, int rows)
 {
     StreamHints h = {};
     if (!env_int("ABQ_TUNE_IGNORE", 0)) {
         const int grouped = p.scale_mode == ABQ_SCALE_GROUP;
         for (const TuneEntry &t : tune_table()) {
-            if (t.w_bits == p.w_bits && t.x_bits == p.x_bits && t.rows_class == rows_class_of(p.M) && t.N == p.N && t.K == p.K && t.grouped == grouped &&
+            if (t.w_bits == p.w_bits && t.x_bits == p.x_bits && t.rows_class == rows_class_of(rows) && t.N == p.N && t.K == p.K && t.grouped == grouped &&
                 (!grouped || t.group_size == p.group_size)) {
                 h = t.h;
                 break;
@@ -144,30 +144,29 @@ size_t stream_prepared_bytes(const abq_gemm_params &p)
 // Launch shape.  Preference: a CTA small enough for two to share an SM (so that the next GEMM's CTAs move in and fetch
 // their first weights while this one computes), K split over CTAs only when the activation records of the whole K
 // range do not fit, chunks of about 4 KB, as deep a ring as the shared memory left over allows.
-static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_bytes)
+static bool make_plan_rows(const abq_gemm_params &p, int rows, StreamPlan *P, size_t *smem_bytes)
 {
-    const int rows = p.M < 16 ? p.M : 16;
     const bool grouped = p.scale_mode == ABQ_SCALE_GROUP;
     P->magic = kStreamMagic;
     P->grouped = grouped;
-    P->MT = rows > 8 ? 2 : 1;
+    P->MT = rows > 16 ? 4 : rows > 8 ? 2 : 1;
     P->unit_bytes = unit_bytes_of(p);
     P->uw = unit_width_of(p);
     // token rows per column block: the fewest that hold the tokens, but more (fewer units per fold) while a block of
     // 8 / MP units would be too large a chunk for the ring
-    const StreamHints H = hints_for(p);
+    const StreamHints H = hints_for(p, rows);
     if (H.planes > 0 && !p.allreduce)
         return false;
-    int MP = P->MT == 2 ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
+    int MP = P->MT >= 2 ? 8 : (rows == 1 ? 1 : rows == 2 ? 2 : rows <= 4 ? 4 : 8);
     while (grouped && MP < 8 && (8 / MP) * P->unit_bytes > 5120)
         MP *= 2;
     if (H.mp > 0 && P->MT == 1)
         MP = H.mp;
-    if ((MP != 1 && MP != 2 && MP != 4 && MP != 8) || MP < (rows > 8 ? 8 : rows) || (P->MT == 2 && MP != 8))
+    if ((MP != 1 && MP != 2 && MP != 4 && MP != 8) || MP < (rows > 8 ? 8 : rows) || (P->MT >= 2 && MP != 8))
         return false;
     P->MP = MP;
     const int GS = grouped && P->MT == 1 ? 8 / P->MP : 1;
-    const int MR = P->MT == 2 ? 16 : P->MP;
+    const int MR = P->MT >= 2 ? 8 * P->MT : P->MP;
     const int units = p.K / P->uw;
     const int tiles = (p.N + 15) / 16;
     const int sms = device_sms();
@@ -185,8 +184,12 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
         // (9 to 16 tokens: sixteen warps first -- twice the activation records to expand, twice the MMAs per unit)
         static const int kShapes1[][2] = { { 1, 8 }, { 0, 16 }, { 0, 8 }, { 1, 4 }, { 0, 4 }, { 0, 2 } };
         static const int kShapes2[][2] = { { 0, 16 }, { 1, 8 }, { 0, 8 }, { 1, 4 }, { 0, 4 }, { 0, 2 } };
-        for (const auto &shape : (P->MT == 2 ? kShapes2 : kShapes1)) {
-            if ((force_full == 1 && shape[0]) || (force_full == 2 && !shape[0]) || (!force_warps && (shape[1] >= 8) != (pass == 0)))
+        static const int kShapes4[][2] = { { 0, 8 }, { 0, 4 } }; // 17..32 tokens: the kernel is built for at most eight warps
+        const auto *shapes = P->MT == 4 ? kShapes4 : (P->MT == 2 ? kShapes2 : kShapes1);
+        const int n_shapes = P->MT == 4 ? 2 : 6;
+        for (int si = 0; si < n_shapes; ++si) {
+            const int *shape = shapes[si];
+            if ((P->MT == 4 && force_warps > 8) || (force_full == 1 && shape[0]) || (force_full == 2 && !shape[0]) || (!force_warps && (shape[1] >= 8) != (pass == 0)))
                 continue; // full: 1 = a CTA that fills the SM, 2 = one that leaves room for a second
             const size_t budget = shape[0] ? 112 * 1024 : 226 * 1024;
             {
@@ -238,6 +241,26 @@ static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_byte
             break;
     }
     return false;
+}
+
+// More than 16 token rows: launches of 16 rows.  Launches of 32 rows (the weights are then read once per 32 rows) exist
+// and are tested, but are opt-in (ABQ_STREAM_ROWS32=1): every CTA expands the activation records of all 32 rows, and with
+// eight warps and one CTA per SM that costs more than the second read of the weights saves (LLaMA-7B W4A4 linear stack at
+// batch 32: 5.43 ms per step against 4.23 ms with two 16-row launches per GEMM).
+static bool make_plan(const abq_gemm_params &p, StreamPlan *P, size_t *smem_bytes)
+{
+    if (p.M > 16 && env_int("ABQ_STREAM_ROWS32", 0) != 0 && make_plan_rows(p, p.M < 32 ? p.M : 32, P, smem_bytes)) {
+        // a K split parks 32-row partial tiles in the workspace, which callers size for 16-row launches: take it only if they fit
+        size_t off_partials, total;
+        decode_workspace_layout(p.M, p.N, &off_partials, &total);
+        const size_t need = off_partials + (size_t)P->slices * ((p.N + 15) / 16) * 32 * 16 * 4;
+        if (P->slices == 1 || (p.workspace && p.workspace_bytes >= need)) {
+            P->rows_per_launch = 32;
+            return true;
+        }
+    }
+    P->rows_per_launch = 16;
+    return make_plan_rows(p, p.M < 16 ? p.M : 16, P, smem_bytes);
 }
 
 abq_status stream_plan(abq_gemm_state *st, bool clear_counters)
@@ -354,8 +377,9 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
     }
 #endif
     const size_t out_row_bytes = (size_t)p.N * (p.out_dtype == ABQ_OUT_INT32 ? 4 : 2);
-    for (int m0 = 0; m0 < p.M; m0 += 16) { // taller problems: 16 rows per launch, in stream order (they share the workspace)
-        a.M = p.M - m0 < 16 ? p.M - m0 : 16;
+    const int step = P.rows_per_launch;
+    for (int m0 = 0; m0 < p.M; m0 += step) { // taller problems: 16 or 32 rows per launch, in stream order (they share the workspace)
+        a.M = p.M - m0 < step ? p.M - m0 : step;
         a.X = (p.flags & ABQ_FLAG_X_HALF) ? reinterpret_cast<const uint32_t *>(reinterpret_cast<const __half *>(p.X) + (size_t)m0 * p.K)
                                           : reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
         a.D = reinterpret_cast<uint8_t *>(p.D) + (size_t)m0 * out_row_bytes;

@@ -646,17 +646,19 @@ __host__ __device__ inline StreamSmem stream_smem_layout(int nw, int ring, int c
     return L;
 }
 
-// Q: weight bits.  MT: token tiles of 8 (2 for 9..16 tokens).  MP: token rows per column block (1, 2, 4, 8).
+// Q: weight bits.  MT: token tiles of 8 (2 for 9..16 tokens, 4 for 17..32: at most eight warps then, so that a thread may
+// use up to 255 registers).  MP: token rows per column block (1, 2, 4, 8).
 // GS = 8 / MP units share one set of accumulators (GROUPED only).  GROUPED: per-group scale / zero point in the stream.
 template <int Q, int MT, int MP, bool GROUPED, int UW>
-__global__ void __launch_bounds__(kStreamMaxWarps * 32, 1) stream_kernel(const StreamArgs a)
+__global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) stream_kernel(const StreamArgs a)
 {
     using F = StreamFormat<Q, UW>;
     constexpr int kCodeBytes = Q * 2 * UW; // of a unit; its 64 parameter bytes follow
     static_assert(GROUPED || UW == 128, "64-feature units exist for scale groups of 64 only");
     constexpr int GS = GROUPED ? 8 / MP : 1;
-    constexpr int MR = MT == 2 ? 16 : MP; // token rows of a record
-    static_assert(MT == 1 || MP == 8, "two token tiles only with full column blocks");
+    constexpr int MR = MT >= 2 ? 8 * MT : MP; // token rows of a record
+    static_assert(MT == 1 || MP == 8, "several token tiles only with full column blocks");
+    static_assert(MT == 1 || MT == 2 || MT == 4, "8, 16 or 32 token rows per launch");
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
 
@@ -1263,6 +1265,8 @@ static cudaError_t stream_launch_variant(const abq_gemm_state *st, const StreamA
 template <int Q, int UW>
 static cudaError_t stream_launch_grouped(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, cudaStream_t stream)
 {
+    if (MT == 4)
+        return stream_launch_variant<Q, 4, 8, true, UW>(st, args, stream);
     if (MT == 2)
         return stream_launch_variant<Q, 2, 8, true, UW>(st, args, stream);
     switch (MP) {
@@ -1277,6 +1281,8 @@ template <int Q>
 static cudaError_t stream_launch_q(const abq_gemm_state *st, const StreamArgs &args, int MT, int MP, bool grouped, cudaStream_t stream)
 {
     if (!grouped) {
+        if (MT == 4)
+            return stream_launch_variant<Q, 4, 8, false>(st, args, stream);
         if (MT == 2)
             return stream_launch_variant<Q, 2, 8, false>(st, args, stream);
         switch (MP) { // without group parameters the column blocks only make the activation records smaller

@@ -44,8 +44,7 @@ def tp_problems():
 
 
 def rows_class(M):
-    rows = min(M, 16)
-    return 1 if rows == 1 else 2 if rows == 2 else 4 if rows <= 4 else 8 if rows <= 8 else 16
+    return 1 if M == 1 else 2 if M == 2 else 4 if M <= 4 else 8 if M <= 8 else 16 if M <= 16 else 32
 
 
 def candidates(M, group, quick, K=0):

@@ -224,3 +224,51 @@ def test_tuning_table_entry_is_honoured(abq, oracle, cuda, monkeypatch, tmp_path
     assert out.stdout.split() == ["74", "512"], out.stdout
     assert (st0.grid[0], st0.block[0]) != (74, 512)
     assert np.array_equal(base, oracle.gemm_values_blas(x, w))
+
+
+TALL_CASES = [
+    # M, N, K, w_bits, group (0: int32 output, no scales)   -- 17..32 token rows go through one launch of the 32-row variant
+    (17, 520, 1152, 4, 0), (32, 4096, 4096, 4, 0), (24, 200, 4096, 2, 0), (32, 1024, 11008, 3, 0), (33, 320, 1280, 8, 0), (64, 136, 2048, 2, 0),
+    (40, 512, 4096, 4, 0), (17, 264, 640, 3, 128), (32, 4096, 4096, 4, 128), (32, 512, 11008, 2, 128), (25, 1000, 2048, 8, 128), (48, 320, 1536, 2, 64),
+    (32, 5120, 5120, 2, 64),
+]
+
+
+@pytest.mark.parametrize("rows32", ["0", "1"], ids=["launches_of_16", "launches_of_32"])
+@pytest.mark.parametrize("M,N,K,q,group", TALL_CASES)
+def test_more_than_16_token_rows(abq, oracle, cuda, monkeypatch, M, N, K, q, group, rows32):
+    """More than 16 token rows on prepared weights, as launches of 16 rows (default) and as launches of 32 rows (opt-in: one
+    read of the weights per 32 rows): a ragged last launch, K ranges that must be split over CTAs, per-group scales and
+    zero points, scale groups of 64."""
+    monkeypatch.setenv("ABQ_STREAM_ROWS32", rows32)
+    rng = np.random.default_rng(M * 17 + N + K + q + group)
+    x, w = rand_codes(rng, M, K, 8, True), rand_codes(rng, N, K, q, False)
+    xp, wp = planes_dev(oracle, x, 8), planes_dev(oracle, w, q)
+    if not group:
+        got, st = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, calls=2)
+        assert abq.state_kernel(st) == "stream_kernel"
+        assert np.array_equal(got, oracle.gemm_values_blas(x, w))
+        return
+    G = K // group
+    scale = rng.uniform(0.001, 0.02, size=(N, G)).astype(np.float16)
+    zero = rng.integers(0, 1 << q, size=(N, G)).astype(np.uint8)
+    tok = rng.uniform(0.5, 2.0, size=M).astype(np.float32)
+    got, st = run_prepared(abq, xp, wp, M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_fp16=True, scale_mode=abq.SCALE_GROUP,
+                           group_size=group, w_scale=dev(scale), w_zero=dev(zero), x_scale=dev(tok), calls=2)
+    assert abq.state_kernel(st) == "stream_kernel"
+    check_close(got, oracle.dequant_gemm(x, w, scale, zero.astype(np.int32), tok, group))
+
+
+def test_fp16_activations_32_rows(abq, oracle, cuda, monkeypatch):
+    """ABQ_FLAG_X_HALF with 32 token rows in one launch: the record builder quantises 32 rows of fp16 activations."""
+    monkeypatch.setenv("ABQ_STREAM_ROWS32", "1")
+    M, N, K, q = 32, 512, 4096, 4
+    rng = np.random.default_rng(321)
+    x = rng.normal(0, 2.0, size=(M, K)).astype(np.float16)
+    w = rand_codes(rng, N, K, q, False)
+    qs = torch.full((1,), 13.0, dtype=torch.float32, device="cuda")
+    got, _ = run_prepared(abq, torch.from_numpy(x).cuda(), planes_dev(oracle, w, q), M, N, K, x_bits=8, w_bits=q, x_signed=True, w_signed=False,
+                          flags=abq.FLAG_X_HALF, x_quant_scale=qs)
+    _, codes = oracle.quantize_half_compat(x, 13.0, 8)
+    codes = ((codes + 128) % 256) - 128
+    assert np.array_equal(got, oracle.gemm_values_blas(codes, w))
