@@ -66,6 +66,7 @@ void decode_workspace_layout(int M, int N, size_t *off_partials, size_t *total);
 
 // ---- gemm_stream.cu (route ABQ_ROUTE_I8_MMA over prepared weights, ABQ_FLAG_WEIGHTS_PREPARED + w_prepared)
 bool stream_supported(const abq_gemm_params &p);
+void decode_table_hints(const abq_gemm_params &p, int *warps, int *slices, int *ring, int *split); // tuned shape of the plane-reading kernel
 size_t stream_prepared_bytes(const abq_gemm_params &p);
 abq_status stream_plan(abq_gemm_state *st, bool clear_counters);
 bool stream_planned(const abq_gemm_state *st);

@@ -50,11 +50,13 @@ static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
     const int rec = decode_record_bytes(L->MT);
     (void)rows;
     const size_t budget = 226 * 1024;
-    const int forced_slices = env_int("ABQ_DECODE_SLICES", 0);
+    int t_warps, t_slices, t_ring, t_split; // from the tuning table (0: heuristic); environment variables outrank it
+    decode_table_hints(p, &t_warps, &t_slices, &t_ring, &t_split);
+    const int forced_slices = env_int("ABQ_DECODE_SLICES", t_slices);
     // 16 warps per CTA when two ring stages per warp fit, else 8 (wide weights); the smallest K split that fits
     int NW = 0, slices = 0, sps = 0, ring = 0;
     size_t fixed = 0;
-    for (int nw = env_int("ABQ_DECODE_WARPS", kMaxWarps); nw >= 8 && !NW; nw -= 8) {
+    for (int nw = env_int("ABQ_DECODE_WARPS", t_warps == 8 || t_warps == 16 ? t_warps : kMaxWarps); nw >= 8 && !NW; nw -= 8) {
         fixed = 1024 + (size_t)nw * 4 * L->MT * 32 * 4 + ((size_t)nw * kMaxRing + 2 * nw) * 8;
         for (int sl = forced_slices > 0 ? forced_slices : 1; sl <= kDecodeMaxSlices && sl <= total_stages; ++sl) {
             const int st = (total_stages + sl - 1) / sl;
@@ -75,7 +77,7 @@ static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
         return false;
     slices = (total_stages + sps - 1) / sps; // drop slices that would be empty
     ring = ring > kMaxRing ? kMaxRing : ring;
-    ring = env_int("ABQ_DECODE_RING", ring);
+    ring = env_int("ABQ_DECODE_RING", t_ring > 0 && t_ring <= ring ? t_ring : ring);
     if (ring < 1 || ring > kMaxRing)
         return false;
     int cps = sms / slices;
@@ -95,7 +97,7 @@ static bool make_layout(const abq_gemm_params &p, DecodeLayout *L)
             best_split = sp;
         }
     }
-    best_split = env_int("ABQ_DECODE_SPLIT", best_split);
+    best_split = env_int("ABQ_DECODE_SPLIT", t_split > 0 && t_split <= NW && t_split <= sps ? t_split : best_split);
     if (best_split < 1 || best_split > NW)
         return false;
     L->NW = NW;

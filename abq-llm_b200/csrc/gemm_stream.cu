@@ -123,6 +123,29 @@ int unit_bytes_of(const abq_gemm_params &p) { return p.w_bits * 2 * unit_width_o
 
 } // namespace
 
+// The tuning table's launch shape for the kernel that reads the planes (entries with planes = 1 reuse four columns:
+// warps, slices, ring, and cu = the number of warps that share a tile along K); zeros where it leaves the heuristic alone.
+void decode_table_hints(const abq_gemm_params &p, int *warps, int *slices, int *ring, int *split)
+{
+    *warps = *slices = *ring = *split = 0;
+    if (env_int("ABQ_TUNE_IGNORE", 0))
+        return;
+    const int grouped = p.scale_mode == ABQ_SCALE_GROUP;
+    const int rows = p.M < 16 ? p.M : 16;
+    for (const TuneEntry &t : tune_table()) {
+        if (t.w_bits == p.w_bits && t.x_bits == p.x_bits && t.rows_class == rows_class_of(rows) && t.N == p.N && t.K == p.K && t.grouped == grouped &&
+            (!grouped || t.group_size == p.group_size)) {
+            if (t.h.planes > 0) {
+                *warps = t.h.warps;
+                *slices = t.h.slices;
+                *ring = t.h.ring;
+                *split = t.h.cu;
+            }
+            return;
+        }
+    }
+}
+
 bool stream_supported(const abq_gemm_params &p)
 {
     if (!width_supported(p.w_bits))

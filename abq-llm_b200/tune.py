@@ -23,6 +23,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 ENV = {"mp": "ABQ_STREAM_MP", "cu": "ABQ_STREAM_CU", "ring": "ABQ_STREAM_RING", "warps": "ABQ_STREAM_WARPS", "full": "ABQ_STREAM_FULL",
        "ctas": "ABQ_STREAM_CTAS", "slices": "ABQ_STREAM_SLICES", "prefill": "ABQ_STREAM_PREFILL", "planes": "ABQ_STREAM_PLANES"}
+PLANE_ENV = {"warps": "ABQ_DECODE_WARPS", "slices": "ABQ_DECODE_SLICES", "ring": "ABQ_DECODE_RING", "cu": "ABQ_DECODE_SPLIT"}
 FIELDS = ["mp", "cu", "ring", "warps", "full", "ctas", "slices", "prefill", "planes"]
 
 
@@ -52,7 +53,14 @@ def candidates(M, group, quick, K=0):
     mps = [m for m in (1, 2, 4, 8) if m >= rc] if (group and rc <= 8) else [0]
     if quick:
         mps = mps[:2]
-    yield dict(mp=0, cu=0, ring=0, warps=0, full=0, ctas=0, slices=0, prefill=0, planes=1)  # the kernel that reads the planes themselves
+    # the kernel that reads the planes themselves: its heuristic shape, then warps x K slices x warps sharing a tile (in `cu`)
+    yield dict(mp=0, cu=0, ring=0, warps=0, full=0, ctas=0, slices=0, prefill=0, planes=1)
+    if not quick:
+        for warps in (0, 8):
+            for slices in (0, 2, 4):
+                for split in (0, 1, 2, 4, 8, 16):
+                    if (warps, slices, split) != (0, 0, 0) and split <= (warps or 16):
+                        yield dict(mp=0, cu=split, ring=0, warps=warps, full=0, ctas=0, slices=slices, prefill=0, planes=1)
     for mp in mps:
         gs = 8 // mp if mp else 1
         for cu in sorted({gs, 2 * gs, 4 * gs} & set(range(1, 9))):
@@ -118,11 +126,19 @@ def main():
         clones = [prep] + [prep.clone() for _ in range(copies - 1)]
 
         def time_plan(hints):
-            saved = {k: os.environ.get(v) for k, v in ENV.items()}
-            for k, v in ENV.items():
+            names = list(ENV.values()) + list(PLANE_ENV.values())
+            saved = {v: os.environ.get(v) for v in names}
+            for v in names:
                 os.environ.pop(v, None)
-                if hints and hints.get(k):
-                    os.environ[v] = str(hints[k])
+            if hints and hints.get("planes"):  # the plane-reading kernel takes its shape from its own variables
+                os.environ[ENV["planes"]] = "1"
+                for k, v in PLANE_ENV.items():
+                    if hints.get(k):
+                        os.environ[v] = str(hints[k])
+            elif hints:
+                for k, v in ENV.items():
+                    if hints.get(k):
+                        os.environ[v] = str(hints[k])
             try:
                 states = [abq.gemm_init(params(c)) for c in clones]
                 if hints and not hints.get("planes") and abq.state_kernel(states[0]) != "stream_kernel":
@@ -130,10 +146,10 @@ def main():
             except abq.AbqError:
                 return None
             finally:
-                for k, v in ENV.items():
+                for v in names:
                     os.environ.pop(v, None)
-                    if saved[k] is not None:
-                        os.environ[v] = saved[k]
+                    if saved[v] is not None:
+                        os.environ[v] = saved[v]
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
                 abq.gemm_exec(states[0])

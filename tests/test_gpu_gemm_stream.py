@@ -226,6 +226,38 @@ def test_tuning_table_entry_is_honoured(abq, oracle, cuda, monkeypatch, tmp_path
     assert np.array_equal(base, oracle.gemm_values_blas(x, w))
 
 
+def test_tuning_table_shapes_the_plane_kernel_too(abq, oracle, cuda, tmp_path):
+    """A table line with planes = 1 sends the problem to the kernel that reads the planes and may give it a launch shape: here
+    K split over four CTAs and eight warps, against the heuristic's unsplit sixteen."""
+    import subprocess, sys, textwrap
+    M, N, K, q = 16, 512, 4096, 2
+    table = tmp_path / "table.txt"
+    table.write_text(f"{q} 8 16 {N} {K} 0 0 : 0 2 0 8 0 0 4 0 1\n")
+    code = textwrap.dedent(f"""
+        import sys, ctypes
+        sys.path.insert(0, {str(__import__('pathlib').Path(__file__).resolve().parent)!r}); sys.path.insert(0, {str(__import__('pathlib').Path(__file__).resolve().parent.parent)!r})
+        import torch
+        from conftest import load_package
+        abq = load_package()
+        from abq_llm_b200 import binding as B
+        buf = torch.zeros(16 << 20, dtype=torch.uint8, device="cuda")
+        p = B.GemmParams(); p.M, p.N, p.K = {M}, {N}, {K}; p.X = p.W = p.D = p.workspace = buf.data_ptr(); p.workspace_bytes = 16 << 20
+        p.x_bits, p.w_bits, p.x_signed = 8, {q}, 1
+        p.route = 2; p.flags = abq.FLAG_WEIGHTS_PREPARED; p.w_prepared = buf.data_ptr()
+        st = B.GemmState(); assert abq.lib().abq_gemm_init(ctypes.byref(p), ctypes.byref(st)) == 0
+        print(abq.state_kernel(st), st.cluster, st.block[0])
+    """)
+    env = dict(__import__("os").environ, ABQ_TUNE_TABLE=str(table))
+    env.pop("ABQ_TUNE_IGNORE", None)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr[-1500:]
+    assert out.stdout.split() == ["decode_kernel", "4", "256"], out.stdout
+    env["ABQ_TUNE_IGNORE"] = "1"
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr[-1500:]
+    assert out.stdout.split()[0] == "stream_kernel", out.stdout
+
+
 TALL_CASES = [
     # M, N, K, w_bits, group (0: int32 output, no scales)   -- 17..32 token rows go through one launch of the 32-row variant
     (17, 520, 1152, 4, 0), (32, 4096, 4096, 4, 0), (24, 200, 4096, 2, 0), (32, 1024, 11008, 3, 0), (33, 320, 1280, 8, 0), (64, 136, 2048, 2, 0),
