@@ -393,12 +393,6 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
         a.ar.recv[r] = reinterpret_cast<__half *>(st->ar.recv[r]);
         a.ar.flags[r] = st->ar.flags[r];
     }
-#ifdef ABQ_STREAM_TRACE
-    {
-        const char *tp = std::getenv("ABQ_TRACE_PTR");
-        a.trace = tp ? reinterpret_cast<unsigned long long *>(std::strtoull(tp, nullptr, 0)) : nullptr;
-    }
-#endif
     const size_t out_row_bytes = (size_t)p.N * (p.out_dtype == ABQ_OUT_INT32 ? 4 : 2);
     const int step = P.rows_per_launch;
     for (int m0 = 0; m0 < p.M; m0 += step) { // taller problems: 16 or 32 rows per launch, in stream order (they share the workspace)

@@ -76,22 +76,8 @@ struct StreamArgs {
     int out_dtype, scale_mode, w_signed;
     int *status;
     StreamAllreduce ar; // world <= 1: none
-#ifdef ABQ_STREAM_TRACE
-    unsigned long long *trace; // development builds only: per-CTA time stamps (see trace_mark)
-#endif
 };
 
-#ifdef ABQ_STREAM_TRACE
-__shared__ unsigned trace_slot_g;
-#define ABQ_TRACE(i) trace_mark(a, trace_slot, i)
-__device__ __forceinline__ void trace_mark(const StreamArgs &a, unsigned slot, int i)
-{
-    if (a.trace && threadIdx.x == 0)
-        a.trace[16 + (size_t)slot * 16 + i] = globaltimer_ns();
-}
-#else
-#define ABQ_TRACE(i)
-#endif
 
 // ------------------------------------------------------------------------------------------ formats
 // StreamFormat<Q>: how the codes of one lane (rows g and g + 8, 32 features each) are packed, and how they come back.
@@ -508,16 +494,10 @@ __device__ __forceinline__ void stream_records_planes(const StreamArgs &a, uint8
     const int items = MR * words;
     const uint32_t magic = 0xffffffffu / (uint32_t)words + 1u; // idx / words == umulhi(idx, magic) for idx * words < 2^32
     const int KW = a.K >> 5;
-#ifdef ABQ_STREAM_TRACE
-#define ABQ_RTRACE(slot, dep) if (!warm && a.trace && threadIdx.x == 0 && base == 0) a.trace[16 + (size_t)(*(volatile unsigned *)&trace_slot_g) * 16 + slot] = globaltimer_ns() + ((dep) == 0x9e3779b9u ? 1 : 0)
-#else
-#define ABQ_RTRACE(slot, dep)
-#endif
     for (int base = 0; base < items; base += blockDim.x * B) { // every lane of a warp takes every trip (shuffles inside)
         uint32_t pl[B][P];
         int mm[B], kk[B];
         bool live[B];
-        ABQ_RTRACE(11, 0u);
 #pragma unroll
         for (int i = 0; i < B; ++i) {
             const int idx = base + i * (int)blockDim.x + (int)threadIdx.x;
@@ -534,20 +514,15 @@ __device__ __forceinline__ void stream_records_planes(const StreamArgs &a, uint8
             for (int b = 0; b < P; ++b)
                 pl[i][b] = (live[i] && !warm) ? __ldg(src + b * a.x_plane_words) : 0u;
         }
-        ABQ_RTRACE(12, 0u);
-        ABQ_RTRACE(7, pl[0][P - 1]);
 #pragma unroll
         for (int i = 0; i < B; ++i) {
             const int idx = base + i * (int)blockDim.x + (int)threadIdx.x;
             uint32_t r[8];
             x_bytes<P>(pl[i], a.x_signed != 0, r); // (zeros in, zeros out: no branch around the arithmetic)
             const int sum = stream_code_sum(r, a.x_signed != 0);
-            ABQ_RTRACE(13, (uint32_t)sum);
             stream_store_item(rec_base, sums, MR, a.uw, kk[i], mm[i], r, sum, warm ? idx < items : live[i]);
         }
-        ABQ_RTRACE(14, 0u);
     }
-#undef ABQ_RTRACE
 }
 
 __device__ __forceinline__ void stream_records_half(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR, bool warm)
@@ -665,18 +640,6 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int nw = a.nw;
-#ifdef ABQ_STREAM_TRACE
-    __shared__ unsigned trace_slot_s;
-    if (a.trace && threadIdx.x == 0) {
-        trace_slot_s = (unsigned)atomicAdd(a.trace, 1ull);
-        trace_slot_g = trace_slot_s;
-        unsigned smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        a.trace[16 + (size_t)trace_slot_s * 16 + 15] = ((unsigned long long)smid << 32) | blockIdx.x;
-    }
-    const unsigned trace_slot = a.trace && threadIdx.x == 0 ? trace_slot_s : 0;
-#endif
-    ABQ_TRACE(0);
     const int s = blockIdx.x / a.ctas_per_slice;
     const int cb = blockIdx.x - s * a.ctas_per_slice;
     // (32-bit arithmetic: a launch has at most a few hundred CTAs per slice and the planner bounds tiles * CTAs below 2^31)
@@ -800,21 +763,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
             prefetch_l2(reinterpret_cast<const uint8_t *>(a.D) + ((size_t)i * a.N + (size_t)r_begin * 16) * esz);
     }
     // ---- activations: everything below may depend on the kernel launched just before
-    ABQ_TRACE(1);
     pdl_wait_prior_grid();
-    ABQ_TRACE(2);
-#ifdef ABQ_STREAM_TRACE
-    if (a.trace && threadIdx.x == 0) { // latency of one load right after the wait: a line every CTA reads, then a line only this CTA reads
-        uint32_t v, v2;
-        const unsigned long long t0 = globaltimer_ns();
-        asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(a.X) : "memory");
-        const unsigned long long t1 = globaltimer_ns() + (v == 0x9e3779b9u ? 1 : 0);
-        asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v2) : "l"(a.Wp + (size_t)blockIdx.x * 8192 + 4096 + (t1 & 3u) * 0) : "memory");
-        const unsigned long long t2 = globaltimer_ns() + (v2 == 0x9e3779b9u ? 1 : 0);
-        a.trace[16 + (size_t)trace_slot * 16 + 9] = t1 - t0;
-        a.trace[16 + (size_t)trace_slot * 16 + 10] = t2 - t1;
-    }
-#endif
     if (lane == 0) {
         for (int slot = a.prefill; slot < a.ring && q_left > 0; ++slot)
             issue(slot);
@@ -859,9 +808,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     } else {
         stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, false);
     }
-    ABQ_TRACE(8);
     __syncthreads();
-    ABQ_TRACE(3);
 
     // lane constants of the B fragment fetch: column c = g holds token (g % MP) of unit (g / MP) of a block
     const int my_m = g & (MP - 1);
@@ -1082,9 +1029,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
         for (int i = 0; i < a.ring; ++i)
             mbar_wait_bounded(&full[i], 0, nullptr, 0);
     }
-    ABQ_TRACE(4);
     __syncthreads();
-    ABQ_TRACE(5);
 
     // ---- the CTA's tiles: add the warps' partial sums in warp order, finish, store.  Thread per (tile, token, row).
     auto tile_sum = [&](int tl, int m, int row) -> int {
@@ -1190,7 +1135,6 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
                 a.ar.counter[0] = epoch;
             }
         }
-        ABQ_TRACE(6);
         return;
     }
     if (a.slices == 1) {
@@ -1198,7 +1142,6 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
             const int tl = idx == (int)threadIdx.x ? first_tl : idx / per_tile, i = idx == (int)threadIdx.x ? first_i : idx - tl * per_tile;
             finish(r_begin + tl, i >> 4, i & 15, tile_sum(tl, i >> 4, i & 15));
         }
-        ABQ_TRACE(6);
         return;
     }
     // ---- K split over CTAs as well: a workspace slot per slice, the CTA arriving last at a tile's counter adds the

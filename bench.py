@@ -548,6 +548,30 @@ def config0_leg(torch, abq, hbm_peak):
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (3 * copies)
+    # the same with the weights expanded once beforehand (ABQ_FLAG_WEIGHTS_PREPARED: each plan keeps its expansion in a
+    # workspace of its own; the call then expands the activations only)
+    works = [torch.empty(abq.gemm_workspace_bytes(M, N, K, p, q), dtype=torch.uint8, device="cuda") for _ in wps]
+    prepared = [abq.gemm_init(B.make_params(M, N, K, xp, wp, out, x_bits=p, w_bits=q, x_signed=False, w_signed=False, workspace=wk,
+                                            flags=abq.FLAG_WEIGHTS_PREPARED)) for wp, wk in zip(wps, works)]
+    for st in prepared:
+        abq.gemm_prepare_weights(st)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        abq.gemm_exec(prepared[0])
+        side.synchronize()
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2, stream=side):
+            for st in prepared:
+                abq.gemm_exec(st)
+    torch.cuda.synchronize()
+    graph2.replay()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(3):
+        graph2.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us_prepared = e0.elapsed_time(e1) * 1e3 / (3 * copies)
     nbytes = q * N * K // 8 + p * M * K // 8 + 4 * M * N
     peak = None
     f = ROOT / "MEASURED_PEAKS.json"
@@ -556,7 +580,8 @@ def config0_leg(torch, abq, hbm_peak):
     tops = 2.0 * M * N * K / us / 1e6
     return {"workload": "W4A4 unsigned, M=128, N=4096, K=4096, int32 out", "route": {2: "I8_MMA", 3: "I8_UMMA"}.get(states[0].route),
             "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm_peak, 3), "TOPS": round(tops, 1),
-            "frac_of_2x_bf16": round(tops / peak, 3) if peak else None}
+            "frac_of_2x_bf16": round(tops / peak, 3) if peak else None, "us_weights_prepared": round(us_prepared, 2),
+            "TOPS_weights_prepared": round(2.0 * M * N * K / us_prepared / 1e6, 1)}
 
 
 def _time_calls(torch, fn, reps=10, warm=3):
