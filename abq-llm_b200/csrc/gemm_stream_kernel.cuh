@@ -472,6 +472,14 @@ __device__ __forceinline__ int stream_code_sum(const uint32_t (&r)[8], bool x_si
     return (int)usum;
 }
 
+// what the activation-record builders read of a launch
+struct StreamRecArgs {
+    const uint32_t *X;
+    size_t x_plane_words;
+    const float *x_qscale;
+    int M, K, x_bits, x_signed, uw;
+};
+
 __device__ __forceinline__ void prefetch_l2(const void *p)
 {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
@@ -487,7 +495,7 @@ __device__ __forceinline__ void prefetch_l2(const void *p)
 // lines the build will read to be brought into L2, walking the page table for them, and (c) writes the zero padding
 // (token rows and units beyond the real ones).  The build then overwrites the records of the real items.
 template <int P, int B>
-__device__ __forceinline__ void stream_records_planes(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR, bool warm)
+__device__ __forceinline__ void stream_records_planes(const StreamRecArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR, bool warm)
 {
     const int wsh = a.uw == 128 ? 2 : 1; // log2 of the 32-feature runs per unit
     const int words = n_pad << wsh;
@@ -525,7 +533,7 @@ __device__ __forceinline__ void stream_records_planes(const StreamArgs &a, uint8
     }
 }
 
-__device__ __forceinline__ void stream_records_half(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR, bool warm)
+__device__ __forceinline__ void stream_records_half(const StreamRecArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR, bool warm)
 {
     const int wsh = a.uw == 128 ? 2 : 1;
     const int words = n_pad << wsh;
@@ -556,9 +564,13 @@ __device__ __forceinline__ void stream_records_half(const StreamArgs &a, uint8_t
 // rec[(ul * MR + m) * 128 + t * 32 + {0, 16} ^ ((m & 1) << 4)] = the lane-t halves (registers 0..3 and 4..7 of x_bytes)
 // of token m, and sums[ul * MR + m] = the sum of its 128 codes (64-feature units: see stream_store_item).
 // warm: the rehearsal before the dependency wait (see above).  One copy of this code per compile unit.
-static __device__ __noinline__ void stream_build_records(const StreamArgs &a, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad, int MR,
-                                                         bool warm)
+static __device__ __noinline__ void stream_build_records(const uint32_t *X, size_t x_plane_words, const float *x_qscale, int M, int K, int x_bits,
+                                                         int x_signed, int uw, uint8_t *rec_base, int *sums, int u_first, int n_units, int n_pad,
+                                                         int MR, bool warm)
 {
+    // (scalars, not a reference to the kernel's parameter block: a reference handed to a function that is not inlined would
+    // make every thread copy the whole block to its stack first)
+    const StreamRecArgs a = { X, x_plane_words, x_qscale, M, K, x_bits, x_signed, uw };
     if (a.x_qscale) {
         stream_records_half(a, rec_base, sums, u_first, n_units, n_pad, MR, warm);
         return;
@@ -755,7 +767,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
         for (int i = threadIdx.x; i < units_pad * MR; i += blockDim.x)
             sums[i] = 0;
     } else {
-        stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, true);
+        stream_build_records(a.X, a.x_plane_words, a.x_qscale, a.M, a.K, a.x_bits, a.x_signed, a.uw, rec_base, sums, u0, n_units, units_pad, MR, true);
     }
     {
         const size_t esz = a.out_dtype == ABQ_OUT_INT32 ? 4 : 2;
@@ -806,7 +818,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
         else
             build(std::integral_constant<int, 4>{});
     } else {
-        stream_build_records(a, rec_base, sums, u0, n_units, units_pad, MR, false);
+        stream_build_records(a.X, a.x_plane_words, a.x_qscale, a.M, a.K, a.x_bits, a.x_signed, a.uw, rec_base, sums, u0, n_units, units_pad, MR, false);
     }
     __syncthreads();
 
