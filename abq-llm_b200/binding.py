@@ -45,6 +45,7 @@ class GemmParams(ctypes.Structure):
         ("x_quant_scale", ctypes.c_void_p),
         ("w_prepared", ctypes.c_void_p),
         ("allreduce", ctypes.POINTER(FusedAllreduce)),
+        ("residual", ctypes.c_void_p),
     ]
 
 
@@ -147,7 +148,7 @@ def gemm_workspace_bytes(M: int, N: int, K: int, x_bits: int, w_bits: int, route
 
 def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dtype=OUT_INT32, scale_mode=SCALE_NONE,
                 group_size=0, C=None, w_scale=None, w_zero=None, x_scale=None, route=ROUTE_AUTO, flags=0, workspace=None,
-                status_word=None, x_quant_scale=None, w_prepared=None, allreduce=None) -> GemmParams:
+                status_word=None, x_quant_scale=None, w_prepared=None, allreduce=None, residual=None) -> GemmParams:
     p = GemmParams()
     p.M, p.N, p.K = M, N, K
     p.X, p.W, p.C, p.D = _ptr(X), _ptr(W), _ptr(C), _ptr(D)
@@ -161,6 +162,7 @@ def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dty
     p.status_word = _ptr(status_word)
     p.x_quant_scale = _ptr(x_quant_scale)
     p.w_prepared = _ptr(w_prepared)
+    p.residual = _ptr(residual)
     if allreduce is not None:
         p.allreduce = ctypes.pointer(allreduce)
         p._keep_allreduce = allreduce  # the struct must outlive the call that reads it
@@ -205,13 +207,13 @@ def gemm_prepare_weights(state: GemmState, stream=None) -> None:
 
 
 def peer_allreduce_half(bufs_dev: int, signals_dev: int, rank: int, world: int, signal_offset: int, out, n_halves: int, counter,
-                        status_word=None, stream=None) -> None:
-    """One-shot sum over the ranks' partial buffers (peer-mapped pointers, see abq_peer_allreduce_half)."""
+                        status_word=None, stream=None, residual=None) -> None:
+    """One-shot sum over the ranks' partial buffers (peer-mapped pointers, see abq_peer_allreduce_half), plus ``residual``."""
     f = lib().abq_peer_allreduce_half
     f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_long, ctypes.c_void_p,
-                  ctypes.c_void_p, ctypes.c_void_p]
-    _check(f(bufs_dev, signals_dev, rank, world, signal_offset, _ptr(out), n_halves, _ptr(counter), _ptr(status_word), _stream(stream)),
-           "abq_peer_allreduce_half")
+                  ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    _check(f(bufs_dev, signals_dev, rank, world, signal_offset, _ptr(out), n_halves, _ptr(counter), _ptr(status_word), _ptr(residual),
+             _stream(stream)), "abq_peer_allreduce_half")
 
 
 def gemm(params: GemmParams, stream=None) -> None:

@@ -23,7 +23,8 @@ namespace abq {
 constexpr int kAllreduceThreads = 1024;
 
 __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const __half *const *bufs, uint32_t *const *signals, int rank,
-                                                                           int world, int signal_offset, __half *out, long n, uint32_t *counter, int *status)
+                                                                           int world, int signal_offset, __half *out, long n, uint32_t *counter, int *status,
+                                                                           const __half *residual)
 {
     // counter[0]: calls completed; counter[1]: blocks of this call that have finished
     __shared__ uint32_t s_epoch;
@@ -71,6 +72,13 @@ __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const
 #pragma unroll
         for (int e = 0; e < 4; ++e)
             oh[e] = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
+        if (residual) { // the fp16 add of a residual kernel that would otherwise follow
+            const uint4 rv = *reinterpret_cast<const uint4 *>(residual + i);
+            const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                oh[e] = __hadd2(oh[e], rh[e]);
+        }
         *reinterpret_cast<uint4 *>(out + i) = o;
     }
     __syncthreads();
@@ -113,12 +121,13 @@ __global__ void __launch_bounds__(kAllreduceThreads) peer_allreduce_kernel(const
 }
 
 cudaError_t peer_allreduce(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world, int signal_offset, void *out,
-                           long n_halves, uint32_t *counter, int *status, cudaStream_t stream)
+                           long n_halves, uint32_t *counter, int *status, const void *residual, cudaStream_t stream)
 {
     long blocks = (n_halves / 8 + kAllreduceThreads - 1) / kAllreduceThreads; // one 16-byte piece per thread where that needs <= 32 blocks
     blocks = blocks < 1 ? 1 : (blocks > 32 ? 32 : blocks);
     peer_allreduce_kernel<<<(unsigned)blocks, kAllreduceThreads, 0, stream>>>(reinterpret_cast<const __half *const *>(bufs_dev), signals_dev, rank, world,
-                                                               signal_offset, reinterpret_cast<__half *>(out), n_halves, counter, status);
+                                                               signal_offset, reinterpret_cast<__half *>(out), n_halves, counter, status,
+                                                               reinterpret_cast<const __half *>(residual));
     return cudaGetLastError();
 }
 
@@ -126,12 +135,12 @@ cudaError_t peer_allreduce(const void *const *bufs_dev, uint32_t *const *signals
 
 extern "C" abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world,
                                               int signal_offset, void *out, long n_halves, uint32_t *counter, int *status_word,
-                                              abq_stream_t stream)
+                                              const void *residual, abq_stream_t stream)
 {
     if (!bufs_dev || !signals_dev || !out || !counter || world < 1 || world > 32 || rank < 0 || rank >= world || n_halves <= 0 ||
-        n_halves % 8 != 0 || signal_offset < 0 || (reinterpret_cast<uintptr_t>(out) & 15))
+        n_halves % 8 != 0 || signal_offset < 0 || ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 15))
         return ABQ_ERR_INVALID_ARG;
-    cudaError_t e = abq::peer_allreduce(bufs_dev, signals_dev, rank, world, signal_offset, out, n_halves, counter, status_word,
+    cudaError_t e = abq::peer_allreduce(bufs_dev, signals_dev, rank, world, signal_offset, out, n_halves, counter, status_word, residual,
                                         reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) {
         abq::set_last_cuda_error(e);

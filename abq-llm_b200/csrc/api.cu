@@ -106,6 +106,8 @@ static abq_status validate(const abq_gemm_params &p)
     // the kernels move operands and results in 16-byte pieces: a misaligned pointer would fault on the device
     if ((reinterpret_cast<uintptr_t>(p.X) | reinterpret_cast<uintptr_t>(p.W) | reinterpret_cast<uintptr_t>(p.D)) & 15)
         return ABQ_ERR_INVALID_ARG;
+    if (p.residual && (p.out_dtype != ABQ_OUT_FP16 || (reinterpret_cast<uintptr_t>(p.residual) & 1)))
+        return ABQ_ERR_INVALID_ARG;
     if (p.flags & ABQ_FLAG_X_HALF) {
         if (!p.x_quant_scale || !p.x_signed)
             return ABQ_ERR_INVALID_ARG;
@@ -203,6 +205,8 @@ static abq_status plan_gemm(const abq_gemm_params *params, abq_gemm_state *state
     }
     if (s != ABQ_OK)
         return s;
+    if (params->residual && route != ABQ_ROUTE_I8_MMA)
+        return ABQ_ERR_UNSUPPORTED; // the residual add lives in the decode kernels' epilogues
     state->route = route;
     state->p.allreduce = nullptr;
     if (state->ar.world > 0 && !(route == ABQ_ROUTE_I8_MMA && stream_planned(state) && state->cluster == 1))

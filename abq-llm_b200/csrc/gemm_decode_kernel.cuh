@@ -69,6 +69,7 @@ struct DecodeArgs {
     int scale_groups;     // scale groups per weight row
     int w_signed;
     int *status;
+    const __half *residual; // not null: added (fp16) to the fp16 result before it is stored
 };
 
 // Expand the activation planes of groups [g_first, g_first + n_groups) into records in shared memory.  Record of a
@@ -540,6 +541,8 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
                                         f *= a.x_scale[tok];
                                     h = __float2half_rn(f);
                                 }
+                                if (a.residual)
+                                    h = __hadd(h, a.residual[o]);
                                 reinterpret_cast<__half *>(a.D)[o] = h;
                             }
                         }

@@ -401,6 +401,7 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
                                           : reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
         a.D = reinterpret_cast<uint8_t *>(p.D) + (size_t)m0 * out_row_bytes;
         a.x_scale = p.x_scale ? p.x_scale + m0 : nullptr;
+        a.residual = p.residual ? reinterpret_cast<const __half *>(p.residual) + (size_t)m0 * p.N : nullptr;
         a.ar.row0 = m0;
         cudaError_t e;
         switch (p.w_bits) {

@@ -75,6 +75,7 @@ struct StreamArgs {
     const __half *C;
     int out_dtype, scale_mode, w_signed;
     int *status;
+    const __half *residual; // not null: added (fp16) to the fp16 result before it is stored
     StreamAllreduce ar; // world <= 1: none
 };
 
@@ -1074,6 +1075,8 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
                     f *= a.x_scale[m];
                 h = __float2half_rn(f);
             }
+            if (a.residual)
+                h = __hadd(h, a.residual[o]);
             reinterpret_cast<__half *>(a.D)[o] = h;
         }
     };
@@ -1136,7 +1139,10 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
                 // written by another GPU into this one's memory: read past the L1 (no stale line)
                 f += __half2float(__ushort_as_half(__ldcv(reinterpret_cast<const unsigned short *>(a.ar.recv[a.ar.rank] + at))));
             }
-            reinterpret_cast<__half *>(a.D)[(size_t)m * a.N + n] = __float2half_rn(f);
+            __half h = __float2half_rn(f);
+            if (a.residual)
+                h = __hadd(h, a.residual[(size_t)m * a.N + n]);
+            reinterpret_cast<__half *>(a.D)[(size_t)m * a.N + n] = h;
         }
         __syncthreads();
         if (threadIdx.x == 0) { // the last CTA of the launch advances the call counter

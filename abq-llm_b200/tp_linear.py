@@ -108,12 +108,31 @@ class TensorParallelBlockLinears:
         act = be.glue_swiglu(gu, self.layers["gate_up"].out_features // 2, self._buf("down", M))
         return h, self.layers["down"](act)                                                 # partial [M][hidden]
 
-    def forward(self, x):
-        """x: fp16 [M][hidden], replicated on every rank.  Returns fp16 [M][hidden], replicated."""
+    def input_buffer(self, M):
+        """Where this block's first layer reads its activations: a caller that chains blocks hands it to the block before
+        as ``out_to`` (None with backends that keep no such buffers)."""
+        return self._buf("qkv", M)
+
+    def forward(self, x, out_to=None):
+        """x: fp16 [M][hidden], replicated on every rank.  Returns fp16 [M][hidden], replicated (in ``out_to`` if given)."""
         be = self.backend
+        if getattr(be, "fuses_residual", False):
+            return self._forward_fused_residual(x, out_to)
         o = be.all_reduce(self.attention_part(x))
         h, d = self.ffn_part(x, o)
-        return be.glue_residual(h, be.all_reduce(d), None)
+        return be.glue_residual(h, be.all_reduce(d), out_to)
+
+    def _forward_fused_residual(self, x, out_to=None):
+        """The same block with both residual adds done where the row-parallel layer's sum is finished (the GEMM's epilogue,
+        or the all-reduce kernel behind it): h = x + O(attn) lands in the gate/up layer's input buffer, the block's
+        output is h + down(act).  Same arithmetic as forward(): the fp16 sum rounded, then an fp16 add."""
+        be, M = self.backend, x.shape[0]
+        qkv = self.layers["qkv"](x)
+        attn = be.glue_attention(qkv, self.layers["qkv"].out_features // 3, self._buf("o", M))
+        h = be.linear_sum_plus(self.layers["o"], attn, x, self._buf("gate_up", M), "h")
+        gu = self.layers["gate_up"](h)
+        act = be.glue_swiglu(gu, self.layers["gate_up"].out_features // 2, self._buf("down", M))
+        return be.linear_sum_plus(self.layers["down"], act, h, out_to, "y")
 
 
 class AbqLinear:
@@ -140,6 +159,8 @@ class AbqLinear:
         self.work = torch.empty(max(256, abq.gemm_workspace_bytes(max_tokens, N, K, x_bits, w_bits)), dtype=torch.uint8, device="cuda")
         self.status = status
         self.plans = {}
+        self.inputs = {}
+        self.needs_reduce = False  # set by the backend: a row-parallel layer on several ranks
         self.prepared = None
         self.prepared_done = False
         self.fused = None
@@ -161,21 +182,26 @@ class AbqLinear:
             self.fused = dict(buf=buf, handle=h, counter=counter,
                               desc=abq.make_fused_allreduce(world, rank, base, [b + (recv_bytes + 255) // 256 * 256 for b in base], counter, max_tokens))
 
-    def _plan(self, M):
+    def _plan(self, M, residual=None, out_to=None):
         """Plan and output buffer per token count, made on first use (outside stream capture: planning may touch the
-        workspace) and reused afterwards, so that a captured graph replays launches only."""
-        key = M
+        workspace) and reused afterwards, so that a captured graph replays launches only.  ``residual`` (fp16 [M][N]) is
+        added to the result by the GEMM itself; ``out_to`` makes the GEMM write into a caller's buffer (the next layer's
+        input) -- both only where this rank's GEMM delivers the final value (no separate all-reduce behind it)."""
+        key = (M, None if residual is None else residual.data_ptr(), None if out_to is None else out_to.data_ptr())
         if key not in self.plans:
             B = self.abq.binding
             fused = self.fused if M <= self.fused_rows else None
-            out = (self.make_out(M, self.out_features) if (self.make_out and fused is None) else
-                   self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda"))
-            x_view = self.torch.empty((M, self.in_features), dtype=self.torch.float16, device="cuda")  # the GEMM reads fp16 here
+            if out_to is not None:
+                out = out_to
+            else:
+                out = (self.make_out(M, self.out_features) if (self.make_out and fused is None) else
+                       self.torch.empty((M, self.out_features), dtype=self.torch.float16, device="cuda"))
+            x_view = self.input(M)  # the GEMM reads fp16 here (one buffer per token count, whatever the plan)
             flags = self.abq.FLAG_PDL | self.abq.FLAG_X_HALF
             kw = dict(x_bits=self.x_bits, w_bits=self.w_bits, x_signed=True, w_signed=False, out_dtype=self.abq.OUT_FP16,
                       scale_mode=self.abq.SCALE_GROUP if self.group else self.abq.SCALE_CHANNEL, group_size=self.group,
                       w_scale=self.scale, w_zero=self.zero, x_scale=self.inv, x_quant_scale=self.q_scale, workspace=self.work,
-                      status_word=self.status)
+                      status_word=self.status, residual=residual)
             probe = B.make_params(M, self.out_features, self.in_features, x_view, self.planes, out, flags=flags, **kw)
             nbytes = self.abq.gemm_prepared_weight_bytes(probe) if M <= 32 else 0
             st = None
@@ -205,13 +231,19 @@ class AbqLinear:
 
     def input(self, M):
         """The fp16 buffer [M][in_features] this layer's plan reads: producers write straight into it."""
-        return self._plan(M)[1]
+        if M not in self.inputs:
+            self.inputs[M] = self.torch.empty((M, self.in_features), dtype=self.torch.float16, device="cuda")
+        return self.inputs[M]
 
-    def __call__(self, x):
+    def sums_in_gemm(self, M):
+        """True where this layer's GEMM call delivers the finished value: one rank, or the all-reduce fused into its epilogue."""
+        return not self.needs_reduce or (self.fused is not None and M <= self.fused_rows)
+
+    def __call__(self, x, residual=None, out_to=None):
         M = x.shape[0]
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens, planned for at most {self.max_tokens}")
-        st, x_view, out = self._plan(M)
+        st, x_view, out = self._plan(M, residual, out_to)
         if x.data_ptr() != x_view.data_ptr():
             x_view.copy_(x)  # callers that cannot write into input(M) pay one copy; the GEMM call quantises x_view itself
         self.abq.gemm_exec(st)
@@ -250,6 +282,7 @@ class AbqBackend:
         fused = (self.dist, self.dist.get_world_size(), self.dist.get_rank()) if (reduce_output and self.fused_rows > 0) else None
         layer = AbqLinear(self.abq, self.torch, codes, scale, zero, w_bits, group, self.x_bits, self.x_scale, self.max_tokens, make_out,
                           fused_reduce=fused, status=self.status, fused_rows=self.fused_rows)
+        layer.needs_reduce = bool(reduce_output and self.dist is not None and self.dist.get_world_size() > 1)
         # all_reduce() leaves the outputs of fused plans alone: the GEMM already summed them
         layer.on_fused_output = lambda out: self._fused_outputs.add(out.data_ptr())
         return layer
@@ -264,6 +297,25 @@ class AbqBackend:
         self._reduced[t.data_ptr()] = (h, t, self.torch.empty((M, N), dtype=self.torch.float16, device="cuda"),
                                        self.torch.zeros(2, dtype=self.torch.int32, device="cuda"))
         return t
+
+    fuses_residual = True  # TensorParallelBlockLinears may call linear_sum_plus()
+
+    def linear_sum_plus(self, layer, x_in, residual, out_to, tag):
+        """residual + (sum over the ranks of layer(x_in)), written to ``out_to`` where given: inside the GEMM where its call
+        delivers the finished value, inside the peer all-reduce kernel behind it otherwise; with NCCL (or more than 32
+        tokens, where the tensor-core route has no residual input) as separate steps."""
+        M = x_in.shape[0]
+        if M <= 32 and layer.sums_in_gemm(M):
+            return layer(x_in, residual=residual, out_to=out_to)
+        part = layer(x_in)
+        entry = self._reduced.get(part.data_ptr()) if M <= 32 else None
+        if entry is None:
+            return self.glue_residual(residual, self.all_reduce(part), out_to)
+        h, _, own_out, counter = entry
+        out = own_out if out_to is None else out_to
+        self.abq.peer_allreduce_half(h.buffer_ptrs_dev, h.signal_pad_ptrs_dev, h.rank, h.world_size, h.signal_pad_size // 8, out, part.numel(),
+                                     counter, self.status, residual=residual)
+        return out
 
     def all_reduce(self, t):
         if self.dist is None or self.dist.get_world_size() == 1 or t.data_ptr() in self._fused_outputs:

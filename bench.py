@@ -777,8 +777,8 @@ def tp_decode_measure(args, torch, dist, abq, rank, world):
 
         def step():
             h = x
-            for b in blocks:
-                h = b.forward(h)
+            for i, b in enumerate(blocks):  # a block writes its output where the next one reads its input
+                h = b.forward(h, blocks[i + 1].input_buffer(M) if i + 1 < len(blocks) else None)
             return h
         for _ in range(2):
             step()  # plans and buffers are made here

@@ -150,6 +150,9 @@ typedef struct abq_gemm_params {
     void *w_prepared;           /* ABQ_FLAG_WEIGHTS_PREPARED on route I8_MMA: the re-ordered weights, 16-byte aligned */
     const abq_fused_allreduce *allreduce; /* optional (host pointer, copied by abq_gemm_init): sum D over the ranks inside the
                                              GEMM; plans that cannot do it answer ABQ_ERR_UNSUPPORTED */
+    const void *residual;   /* optional fp16 [M][N] (fp16 output, route I8_MMA; other plans answer ABQ_ERR_UNSUPPORTED):
+                               D = half(result) + residual, the fp16 add a separate residual kernel would do after the GEMM
+                               (after the sum over the ranks when `allreduce` is set); may alias neither X nor D */
 } abq_gemm_params;
 
 /*
@@ -261,10 +264,12 @@ ABQ_API abq_status abq_gemm_prepare_weights(const abq_gemm_state *state, abq_str
  * Every rank adds in rank order in fp32: all ranks get the same bits.  The call returns (on the stream) only after every
  * peer has read this rank's buffer, so the buffer may be rewritten by whatever comes next, and one call site can be used
  * back to back.  The waits for the peers are bounded (status_word).  abq_fused_allreduce does the same sum inside the GEMM.
+ *   residual     optional local fp16 array of n_halves values added to the sum (fp16 add of the rounded sum, as a separate
+ *                residual kernel after the all-reduce would do); NULL for the plain sum
  */
 ABQ_API abq_status abq_peer_allreduce_half(const void *const *bufs_dev, uint32_t *const *signals_dev, int rank, int world,
                                            int signal_offset, void *out, long n_halves, uint32_t *counter, int *status_word,
-                                           abq_stream_t stream);
+                                           const void *residual, abq_stream_t stream);
 
 /*
  * The fp16 elementwise steps between the GEMMs of a decoder block, as single launches that join the programmatic-dependent-

@@ -304,3 +304,47 @@ def test_fp16_activations_32_rows(abq, oracle, cuda, monkeypatch):
     _, codes = oracle.quantize_half_compat(x, 13.0, 8)
     codes = ((codes + 128) % 256) - 128
     assert np.array_equal(got, oracle.gemm_values_blas(codes, w))
+
+
+@pytest.mark.parametrize("M,N,K,q,group,prepared", [(1, 4096, 4096, 4, 0, True), (5, 264, 1152, 2, 128, True), (16, 512, 4096, 4, 0, True), (16, 1024, 11008, 3, 128, True),
+                                                     (33, 320, 1280, 4, 0, True), (4, 520, 1024, 4, 0, False), (16, 136, 4096, 5, 128, False)])
+def test_residual_added_in_the_epilogue(abq, oracle, cuda, M, N, K, q, group, prepared):
+    """params.residual: D = half(result) + residual, bit for bit what the same GEMM without it followed by an fp16 add gives,
+    on the prepared-weights kernel and on the kernel that reads the planes (also across launches of 16 rows and with K split
+    over CTAs); the tensor-core route has no such input and says so."""
+    from abq_llm_b200 import binding as B
+    rng = np.random.default_rng(M + N + K + q)
+    x, w = rand_codes(rng, M, K, 8, True), rand_codes(rng, N, K, q, False)
+    xp, wp = planes_dev(oracle, x, 8), planes_dev(oracle, w, q)
+    shape = (N, K // group) if group else (N,)
+    scale = dev(rng.uniform(0.001, 0.01, size=shape).astype(np.float16))
+    zero = dev(rng.integers(0, 1 << q, size=shape).astype(np.uint8))
+    res = torch.randn((M, N), device="cuda").half()
+    ws = torch.empty(max(256, abq.gemm_workspace_bytes(M, N, K, 8, q, abq.ROUTE_I8_MMA)), dtype=torch.uint8, device="cuda")
+    outs = []
+    prep = None
+    for residual in (None, res):
+        out = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+        p = B.make_params(M, N, K, xp, wp, out, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_dtype=abq.OUT_FP16,
+                          scale_mode=abq.SCALE_GROUP if group else abq.SCALE_CHANNEL, group_size=group, w_scale=scale, w_zero=zero,
+                          route=abq.ROUTE_I8_MMA, flags=abq.FLAG_WEIGHTS_PREPARED if prepared else 0, workspace=ws, residual=residual)
+        if prepared:
+            if prep is None:
+                prep = torch.empty(abq.gemm_prepared_weight_bytes(p), dtype=torch.uint8, device="cuda")
+            p.w_prepared = prep.data_ptr()
+        st = abq.gemm_init(p)
+        assert abq.state_kernel(st) == ("stream_kernel" if prepared else "decode_kernel")
+        if prepared:
+            abq.gemm_prepare_weights(st)
+        abq.gemm_exec(st)
+        torch.cuda.synchronize()
+        outs.append(out)
+    assert torch.equal(outs[1], outs[0] + res)  # torch's fp16 add: the exact sum rounded once, as __hadd
+    big = torch.zeros((64, N), dtype=torch.float16, device="cuda")
+    wsu = torch.empty(abq.gemm_workspace_bytes(64, N, K, 8, q, abq.ROUTE_I8_UMMA), dtype=torch.uint8, device="cuda")
+    xb = planes_dev(oracle, rand_codes(rng, 64, K, 8, True), 8)
+    with pytest.raises(abq.AbqError) as err:
+        abq.gemm_init(B.make_params(64, N, K, xb, wp, big, x_bits=8, w_bits=q, x_signed=True, w_signed=False, out_dtype=abq.OUT_FP16,
+                                    scale_mode=abq.SCALE_CHANNEL, w_scale=dev(np.ones(N, dtype=np.float16)), route=abq.ROUTE_I8_UMMA, workspace=wsu,
+                                    residual=big))
+    assert err.value.status == 2  # ABQ_ERR_UNSUPPORTED
