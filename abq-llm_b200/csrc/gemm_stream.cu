@@ -196,8 +196,8 @@ static bool make_plan_rows(const abq_gemm_params &p, int rows, StreamPlan *P, si
     const int force_full = H.full;
     const int force_slices = H.slices;
     const int force_warps = H.warps;
-    if (force_warps < 0 || force_warps > kStreamMaxWarps)
-        return false;
+    if (force_warps < 0 || force_warps > kStreamMaxWarps || (force_warps & (force_warps - 1)))
+        return false; // (a power of two: the kernel shares the chunks out by a shift)
     // Preference: no K split before a K split (its partial sums go through global memory); then eight warps in a CTA that
     // leaves room for a second one on the SM, sixteen in one that fills it, and so on down.
     // A CTA of fewer than eight warps only when no K split makes room for eight.
@@ -365,6 +365,15 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.ring = P.ring;
     a.prefill = P.prefill;
     a.nw = P.nw;
+    a.nw_shift = 0;
+    while ((1 << a.nw_shift) < P.nw)
+        ++a.nw_shift;
+    a.tiles_q = a.tiles / P.ctas_per_slice;
+    a.tiles_r = a.tiles % P.ctas_per_slice;
+    a.max_tiles = (a.tiles + P.ctas_per_slice - 1) / P.ctas_per_slice;
+    a.cpt_full = (P.units_per_slice + P.cu - 1) / P.cu;
+    a.rec_magic = 0xffffffffu / (uint32_t)(P.units_per_slice * (P.uw / 32)) + 1u;
+    a.cpt_magic = 0xffffffffu / (uint32_t)a.cpt_full + 1u;
     a.Wp = reinterpret_cast<const uint8_t *>(p.w_prepared);
     a.x_plane_words = (size_t)p.M * (p.K / 32);
     a.x_qscale = (p.flags & ABQ_FLAG_X_HALF) ? p.x_quant_scale : nullptr;
@@ -397,6 +406,7 @@ cudaError_t stream_launch(const abq_gemm_state *st, cudaStream_t stream)
     const int step = P.rows_per_launch;
     for (int m0 = 0; m0 < p.M; m0 += step) { // taller problems: 16 or 32 rows per launch, in stream order (they share the workspace)
         a.M = p.M - m0 < step ? p.M - m0 : step;
+        a.per_tile_magic = 0xffffffffu / (uint32_t)(16 * a.M) + 1u;
         a.X = (p.flags & ABQ_FLAG_X_HALF) ? reinterpret_cast<const uint32_t *>(reinterpret_cast<const __half *>(p.X) + (size_t)m0 * p.K)
                                           : reinterpret_cast<const uint32_t *>(p.X) + (size_t)m0 * (p.K / 32);
         a.D = reinterpret_cast<uint8_t *>(p.D) + (size_t)m0 * out_row_bytes;

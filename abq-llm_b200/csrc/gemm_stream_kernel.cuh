@@ -60,7 +60,15 @@ struct StreamArgs {
     int cu;              // units per chunk (multiple of GS)
     int ring;            // chunks per warp ring
     int prefill;         // chunks per warp requested before the wait on the previous kernel (the rest right after it)
-    int nw;              // warps per CTA
+    int nw;              // warps per CTA (a power of two)
+    // what the host can work out once instead of every thread at every launch (each of these is an integer division there):
+    int nw_shift;            // log2(nw)
+    int tiles_q, tiles_r;    // tiles / ctas_per_slice and the remainder: the first tiles_r CTAs of a slice take one tile more
+    int max_tiles;           // ceil(tiles / ctas_per_slice)
+    int cpt_full;            // chunks per tile of a slice with all its units_per_slice units
+    uint32_t rec_magic;      // idx / (units_per_slice * uw / 32) == umulhi(idx, rec_magic) for the record items
+    uint32_t per_tile_magic; // tid / (16 * M) == umulhi(tid, per_tile_magic)
+    uint32_t cpt_magic;      // c / cpt_full == umulhi(c, cpt_magic) for the chunk indices of a CTA
     const uint8_t *Wp;   // weights in stream layout
     const uint32_t *X;   // activation planes [x_bits][rows][K/32], first row of this launch (fp16 [rows][K] with x_qscale)
     size_t x_plane_words;
@@ -653,17 +661,18 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int nw = a.nw;
-    const int s = blockIdx.x / a.ctas_per_slice;
+    // (without a K split, which is the common case, a CTA's position is its block index)
+    const int s = a.slices > 1 ? blockIdx.x / a.ctas_per_slice : 0;
     const int cb = blockIdx.x - s * a.ctas_per_slice;
-    // (32-bit arithmetic: a launch has at most a few hundred CTAs per slice and the planner bounds tiles * CTAs below 2^31)
-    const int r_begin = (int)((unsigned)cb * (unsigned)a.tiles / (unsigned)a.ctas_per_slice);
-    const int r_end = (int)((unsigned)(cb + 1) * (unsigned)a.tiles / (unsigned)a.ctas_per_slice);
-    const int T = r_end - r_begin;
-    const int max_T = (a.tiles + a.ctas_per_slice - 1) / a.ctas_per_slice;
+    // tiles [r_begin, r_end) of this CTA: an even share, the first tiles_r CTAs of the slice taking one more
+    const int r_begin = cb * a.tiles_q + min(cb, a.tiles_r);
+    const int T = a.tiles_q + (cb < a.tiles_r ? 1 : 0);
+    const int r_end = r_begin + T;
+    const int max_T = a.max_tiles;
     const int u0 = s * a.units_per_slice;                        // first unit of this CTA's K range
     const int n_units = max(0, min(a.units - u0, a.units_per_slice)); // its unit count
     const int units_pad = a.units_per_slice;                     // records are padded to whole chunks
-    const int cpt = (n_units + a.cu - 1) / a.cu;                 // chunks per tile
+    const int cpt = n_units == a.units_per_slice ? a.cpt_full : (n_units + a.cu - 1) / a.cu; // chunks per tile
     const int total_chunks = T * cpt;
     const int chunk_bytes = a.cu * a.unit_bytes;
 
@@ -688,7 +697,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     // ---- this warp's chunks: [c_begin, c_end) of the CTA's T * cpt chunks (tile-major)
     __shared__ int chunk_bound[kStreamMaxWarps + 1];
     // (the same share for every warp, the first warps served first: the warps that hold a share of a tile are then consecutive)
-    const int chunks_per_warp = (total_chunks + nw - 1) / nw;
+    const int chunks_per_warp = (total_chunks + nw - 1) >> a.nw_shift;
     if ((int)threadIdx.x <= nw)
         chunk_bound[threadIdx.x] = min((int)threadIdx.x * chunks_per_warp, total_chunks); // read again after the barriers below
     const int c_begin = min(warp * chunks_per_warp, total_chunks);
@@ -699,7 +708,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     int q_cit = 0, q_left = 0;
     const uint8_t *q_src = a.Wp; // where the next chunk starts: chunks of a tile follow one another in memory
     if (cpt > 0) {
-        const int q_tile = c_begin / cpt;
+        const int q_tile = cpt == a.cpt_full ? (int)__umulhi((uint32_t)c_begin, a.cpt_magic) : c_begin / cpt;
         q_cit = c_begin - q_tile * cpt;
         q_left = c_end - c_begin;
         q_src = a.Wp + ((size_t)(r_begin + q_tile) * a.units + u0 + (size_t)q_cit * a.cu) * a.unit_bytes;
@@ -736,7 +745,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
         tile_warps[tl] = (unsigned short)(min(w_lo, w_hi) | (w_hi << 8));
     }
     const int per_tile = a.M * 16; // outputs of a tile; output idx of the CTA is tile idx / per_tile, token (idx % per_tile) / 16, row idx % 16
-    const int first_tl = (int)threadIdx.x / per_tile, first_i = (int)threadIdx.x - first_tl * per_tile;
+    const int first_tl = (int)__umulhi(threadIdx.x, a.per_tile_magic), first_i = (int)threadIdx.x - first_tl * per_tile;
     // The activation records.  Common case (plane input of 8 or 4 bits, at most kFast items per thread): everything about
     // a thread's items that can be known now is computed now -- where the plane words come from, where the record goes --
     // so that after the wait only loads, the bit shuffle and stores remain, in straight-line code.  Other cases run the
@@ -744,14 +753,18 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     // lines to be read (and the lines this CTA will store its results to) are requested into L2, page-table walk included.
     constexpr int kFast = 4;
     const int rec_words = units_pad * (UW / 32), rec_items = MR * rec_words;
-    const int rec_batches = (rec_items + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int rec_batches = (rec_items + (int)blockDim.x - 1) >> (a.nw_shift + 5); // (the CTA has 32 << nw_shift threads)
     const bool rec_fast = !a.x_qscale && (a.x_bits == 8 || a.x_bits == 4) && rec_batches <= kFast;
     const uint32_t *it_src[kFast]; // plane 0 word of the item, or null: padding (already zero)
     uint32_t it_dst[kFast];        // byte offset of the record from rec_base | 1: this lane also stores the unit's code sum
     if (rec_fast) {
-        const uint32_t magic = 0xffffffffu / (uint32_t)rec_words + 1u; // idx / rec_words == umulhi(idx, magic) here
+        const uint32_t magic = a.rec_magic; // idx / rec_words == umulhi(idx, magic) here
 #pragma unroll
         for (int i = 0; i < kFast; ++i) {
+            it_src[i] = nullptr;
+            it_dst[i] = 0;
+            if (i >= rec_batches) // (the same for every thread: one token needs one batch)
+                continue;
             const int idx = i * (int)blockDim.x + (int)threadIdx.x;
             const int m = (int)__umulhi((uint32_t)idx, magic), kwl = idx - m * rec_words;
             const bool live = idx < rec_items && m < a.M && kwl / (UW / 32) < n_units;
@@ -790,9 +803,11 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
             uint32_t pl[kFast][P];
 #pragma unroll
             for (int i = 0; i < kFast; ++i) {
+                if (i < rec_batches) { // (uniform: no predicated loads for batches that do not exist)
 #pragma unroll
-                for (int b = 0; b < P; ++b)
-                    pl[i][b] = (i < rec_batches && it_src[i]) ? __ldg(it_src[i] + b * a.x_plane_words) : 0u;
+                    for (int b = 0; b < P; ++b)
+                        pl[i][b] = it_src[i] ? __ldg(it_src[i] + b * a.x_plane_words) : 0u;
+                }
             }
 #pragma unroll
             for (int i = 0; i < kFast; ++i) {
@@ -833,7 +848,8 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     bool ok = true;
     int slot = 0;
     uint32_t phase = 0;
-    int tile_l = cpt > 0 ? c_begin / cpt : 0; // tile (local) and chunk within it of the chunk being consumed
+    // tile (local) and chunk within it of the chunk being consumed
+    int tile_l = cpt > 0 ? (cpt == a.cpt_full ? (int)__umulhi((uint32_t)c_begin, a.cpt_magic) : c_begin / cpt) : 0;
     int cit = cpt > 0 ? c_begin - tile_l * cpt : 0;
 
     int acc_run[F::kSets][MT][4]; // without per-group scales: integer sums over the whole K range of a tile
