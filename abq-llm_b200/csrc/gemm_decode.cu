@@ -185,6 +185,11 @@ cudaError_t decode_launch(const abq_gemm_state *st, cudaStream_t stream)
     a.ctas_per_slice = st->tile[2];
     a.split = st->tile[3];
     a.stages_per_split = (a.stages_per_slice + a.split - 1) / a.split;
+    a.tiles_q = tiles / a.ctas_per_slice;
+    a.tiles_r = tiles % a.ctas_per_slice;
+    a.tiles_per_round = (int)st->block[0] / 32 / a.split;
+    a.split_magic = 0xffffffffu / (uint32_t)a.split + 1u;
+    a.words_magic = 0xffffffffu / (uint32_t)(a.stages_per_slice * 16) + 1u;
     a.ring = st->tile[1];
     a.X = reinterpret_cast<const uint32_t *>(p.X);
     a.x_plane_words = (size_t)p.M * (p.K / 32);

@@ -70,6 +70,11 @@ struct DecodeArgs {
     int w_signed;
     int *status;
     const __half *residual; // not null: added (fp16) to the fp16 result before it is stored
+    // worked out once on the host instead of by every thread of every launch (each an integer division there):
+    int tiles_q, tiles_r;    // tiles / ctas_per_slice and the remainder: the first tiles_r CTAs of a slice take one tile more
+    int tiles_per_round;     // warps of the CTA / split
+    uint32_t split_magic;    // warp / split == umulhi(warp, split_magic)
+    uint32_t words_magic;    // idx / (4 * stages_per_slice * 4) == umulhi(idx, words_magic): record items of a full slice
 };
 
 // Expand the activation planes of groups [g_first, g_first + n_groups) into records in shared memory.  Record of a
@@ -82,8 +87,10 @@ __device__ __forceinline__ void build_records(const DecodeArgs &a, uint8_t *rec_
     const int words = n_groups * 4;
     const int items = MT * 8 * words;
     const size_t plane = a.x_plane_words;
+    // idx / words by a multiplication (a few thousand items at most); the host knows the divisor of a slice with all its stages
+    const uint32_t magic = words == a.stages_per_slice * 16 ? a.words_magic : 0xffffffffu / (uint32_t)max(words, 1) + 1u;
     for (int idx = threadIdx.x; idx < items; idx += NW * 32) {
-        const int m = idx / words, kwl = idx - m * words;
+        const int m = (int)__umulhi((uint32_t)idx, magic), kwl = idx - m * words;
         uint32_t r[8];
         int sum = 0;
         if (m < a.M) {
@@ -132,8 +139,9 @@ __device__ __forceinline__ void build_records_half(const DecodeArgs &a, uint8_t 
     const __half *xh = reinterpret_cast<const __half *>(a.X);
     const __half hscale = __float2half(__ldg(a.x_qscale));
     const uint32_t keep = 0x01010101u * ((1u << a.x_bits) - 1u);
+    const uint32_t magic = words == a.stages_per_slice * 16 ? a.words_magic : 0xffffffffu / (uint32_t)max(words, 1) + 1u;
     for (int idx = threadIdx.x; idx < items; idx += NW * 32) {
-        const int m = idx / words, kwl = idx - m * words;
+        const int m = (int)__umulhi((uint32_t)idx, magic), kwl = idx - m * words;
         uint32_t r[8];
 #pragma unroll
         for (int s = 0; s < 8; ++s)
@@ -193,10 +201,11 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int s = blockIdx.x / a.ctas_per_slice;      // K-slice of this CTA
-    const int cb = blockIdx.x - s * a.ctas_per_slice; // position among the CTAs of the slice
-    const int r_begin = (int)((long long)cb * a.tiles / a.ctas_per_slice);
-    const int r_end = (int)((long long)(cb + 1) * a.tiles / a.ctas_per_slice);
+    const int s = a.slices > 1 ? blockIdx.x / a.ctas_per_slice : 0; // K-slice of this CTA
+    const int cb = blockIdx.x - s * a.ctas_per_slice;               // position among the CTAs of the slice
+    // tiles [r_begin, r_end): an even share, the first tiles_r CTAs of the slice taking one more
+    const int r_begin = cb * a.tiles_q + min(cb, a.tiles_r);
+    const int r_end = r_begin + a.tiles_q + (cb < a.tiles_r ? 1 : 0);
     const int total_stages = (a.total_groups + 3) >> 2;
     const int slice_first = s * a.stages_per_slice;                                     // first stage of the slice
     const int slice_nst = max(0, min(total_stages - slice_first, a.stages_per_slice)); // its stage count
@@ -204,8 +213,8 @@ __global__ void __launch_bounds__(NW * 32, 1) decode_kernel(const __grid_constan
     const int n_groups = max(0, min(a.total_groups - g_slice, a.stages_per_slice * 4));
 
     // role of this warp: tile slot ts of the round, part sc of that tile's stages
-    const int tiles_per_round = NW / a.split;
-    const int ts = warp / a.split, sc = warp - ts * a.split;
+    const int tiles_per_round = a.tiles_per_round;
+    const int ts = a.split == 1 ? warp : (int)__umulhi((uint32_t)warp, a.split_magic), sc = warp - ts * a.split; // (no magic for 1)
     const bool active = ts < tiles_per_round;
     const int st_begin = min(slice_nst, sc * a.stages_per_split); // stages [st_begin, st_end) of the slice
     const int st_end = min(slice_nst, st_begin + a.stages_per_split);

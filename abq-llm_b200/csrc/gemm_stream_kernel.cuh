@@ -708,7 +708,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     int q_cit = 0, q_left = 0;
     const uint8_t *q_src = a.Wp; // where the next chunk starts: chunks of a tile follow one another in memory
     if (cpt > 0) {
-        const int q_tile = cpt == a.cpt_full ? (int)__umulhi((uint32_t)c_begin, a.cpt_magic) : c_begin / cpt;
+        const int q_tile = cpt == 1 ? c_begin : cpt == a.cpt_full ? (int)__umulhi((uint32_t)c_begin, a.cpt_magic) : c_begin / cpt; // (no magic for 1)
         q_cit = c_begin - q_tile * cpt;
         q_left = c_end - c_begin;
         q_src = a.Wp + ((size_t)(r_begin + q_tile) * a.units + u0 + (size_t)q_cit * a.cu) * a.unit_bytes;
@@ -849,7 +849,7 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     int slot = 0;
     uint32_t phase = 0;
     // tile (local) and chunk within it of the chunk being consumed
-    int tile_l = cpt > 0 ? (cpt == a.cpt_full ? (int)__umulhi((uint32_t)c_begin, a.cpt_magic) : c_begin / cpt) : 0;
+    int tile_l = cpt > 1 ? (cpt == a.cpt_full ? (int)__umulhi((uint32_t)c_begin, a.cpt_magic) : c_begin / cpt) : c_begin;
     int cit = cpt > 0 ? c_begin - tile_l * cpt : 0;
 
     int acc_run[F::kSets][MT][4]; // without per-group scales: integer sums over the whole K range of a tile
