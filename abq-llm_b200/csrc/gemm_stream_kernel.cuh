@@ -715,7 +715,17 @@ __global__ void __launch_bounds__(MT == 4 ? 256 : kStreamMaxWarps * 32, 1) strea
     }
     const uint32_t last_chunk_bytes = (uint32_t)(n_units - (cpt - 1) * a.cu) * a.unit_bytes;        // of a tile's K range
     const size_t tile_gap = (size_t)(a.units - n_units) * a.unit_bytes;                               // K range of the other slices
+    // (common case: every chunk has all its units and the tiles of this CTA follow one another in memory, so the requests
+    // are equal pieces of one contiguous byte range and need no bookkeeping)
+    const bool uniform_chunks = last_chunk_bytes == (uint32_t)chunk_bytes && tile_gap == 0;
     auto issue = [&](int slot) {
+        if (uniform_chunks) {
+            mbar_arrive_expect_tx(&full[slot], (uint32_t)chunk_bytes);
+            bulk_load(my_ring + (size_t)slot * chunk_bytes, q_src, (uint32_t)chunk_bytes, &full[slot]);
+            q_src += chunk_bytes;
+            --q_left;
+            return;
+        }
         const bool last = q_cit == cpt - 1;
         const uint32_t bytes = last ? last_chunk_bytes : (uint32_t)chunk_bytes;
         mbar_arrive_expect_tx(&full[slot], bytes);
