@@ -163,6 +163,9 @@ def make_params(M, N, K, X, W, D, *, x_bits, w_bits, x_signed, w_signed, out_dty
     p.x_quant_scale = _ptr(x_quant_scale)
     p.w_prepared = _ptr(w_prepared)
     p.residual = _ptr(residual)
+    # the block carries raw pointers: keep the tensors alive as long as it lives (a temporary passed inline would otherwise
+    # be freed, and its memory reused, before the launch)
+    p._keep_alive = (X, W, D, C, w_scale, w_zero, x_scale, workspace, status_word, x_quant_scale, w_prepared, residual)
     if allreduce is not None:
         p.allreduce = ctypes.pointer(allreduce)
         p._keep_allreduce = allreduce  # the struct must outlive the call that reads it
