@@ -263,13 +263,13 @@ class AbqBackend:
         several = dist is not None and dist.get_world_size() > 1
         # how the row-parallel partials are summed: "peer" (the library's one-shot all-reduce kernel after the GEMM), "fused"
         # (inside the GEMM's epilogue), "nccl" (torch.distributed), or "auto" (default) = whichever of the first two measured
-        # faster: fused for up to 8 tokens on 4 or more ranks (the one-shot kernel reads world x the bytes and needs a closing
-        # round), peer otherwise (the fused form ties the layer to the prepared-weights kernel, and for 9..16 rows the
-        # plane-reading kernel is the faster one; on 2 ranks the two are level at batch 1)
+        # faster on 2, 4 and 8 ranks: fused for up to 8 tokens (no launch of its own, one flag round trip instead of two),
+        # peer above (the fused form ties the layer to the prepared-weights kernel, and for the tensor-parallel shapes at
+        # 9..16 rows per launch the plane-reading kernel is the faster one)
         self.reduce_kind = os.environ.get("ABQ_TP_REDUCE", "nccl" if os.environ.get("ABQ_TP_NCCL", "0") == "1" else "auto") if several else "none"
         if self.reduce_kind not in ("none", "auto", "fused", "peer", "nccl"):
             raise ValueError(f"ABQ_TP_REDUCE={self.reduce_kind}")
-        self.fused_rows = {"fused": 1 << 30, "auto": 8 if several and dist.get_world_size() >= 4 else 0}.get(self.reduce_kind, 0)
+        self.fused_rows = {"fused": 1 << 30, "auto": 8 if several else 0}.get(self.reduce_kind, 0)
         if self.reduce_kind == "auto" and "ABQ_TP_FUSED_ROWS" in os.environ:
             self.fused_rows = int(os.environ["ABQ_TP_FUSED_ROWS"])
         self.peer_reduce = self.reduce_kind in ("auto", "fused", "peer")  # no NCCL call on the data path: the step can be one CUDA graph
