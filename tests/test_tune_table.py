@@ -64,3 +64,45 @@ def test_committed_table_parses():
             continue
         key, _, rest = line.partition(":")
         assert len(key.split()) == 7 and len(rest.split("#")[0].split()) == 9, line
+
+
+INVARIANTS = textwrap.dedent("""
+    import sys, ctypes
+    sys.path.insert(0, {tests!r}); sys.path.insert(0, {root!r})
+    from conftest import load_package
+    abq = load_package()
+    from abq_llm_b200 import binding as B
+    bad = []
+    n = 0
+    for q in (2, 3, 4, 8):
+        for M in (1, 2, 3, 4, 7, 8):                       # (9 and more token rows may need a K split: its counters are device memory)
+            for (N, K) in ((16, 128), (48, 384), (4096, 4096), (12288, 4096), (11008, 4096), (4096, 11008), (5120, 5120), (13824, 5120), (1000, 1152)):
+                for group in (0, 64, 128):
+                    if group and K % group:
+                        continue
+                    p = B.GemmParams(); p.M, p.N, p.K = M, N, K; p.X = p.W = p.D = 4096; p.x_bits, p.w_bits, p.x_signed = 8, q, 1
+                    p.route = 2; p.flags = abq.FLAG_WEIGHTS_PREPARED; p.w_prepared = 4096
+                    if group:
+                        p.out_dtype, p.scale_mode, p.group_size, p.w_scale = 1, abq.SCALE_GROUP, group, 4096
+                    st = B.GemmState(); rc = abq.lib().abq_gemm_init(ctypes.byref(p), ctypes.byref(st))
+                    n += 1
+                    if rc == 4 and st.cluster == 0:
+                        continue                            # a shape that splits K: planned, but the counter reset needs a device
+                    ok = (rc == 0 and abq.state_kernel(st) == "stream_kernel" and st.block[0] in (64, 128, 256, 512) and 1 <= st.grid[0] <= 2048
+                          and st.shared_mem_size <= 227 * 1024 and st.tile[1] >= 2 and st.tile[3] >= 1)
+                    if not ok:
+                        bad.append((q, M, N, K, group, rc, st.grid[0], st.block[0], st.shared_mem_size, list(st.tile)))
+    print(n, bad)
+""")
+
+
+def test_prepared_weights_plans_stay_inside_the_hardware_limits():
+    """Every decode problem of up to 8 tokens over a spread of shapes, widths and scale groups gets a prepared-weights plan:
+    a power-of-two CTA of at most 16 warps, at most 227 KB of shared memory, a ring of at least two chunks per warp."""
+    code = INVARIANTS.format(tests=str(ROOT / "tests"), root=str(ROOT))
+    e = {k: v for k, v in os.environ.items() if not k.startswith("ABQ_")}
+    e["ABQ_TUNE_IGNORE"] = "1"
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=e, timeout=600)
+    assert out.returncode == 0, out.stderr[-1500:]
+    count, bad = out.stdout.strip().split(" ", 1)
+    assert int(count) > 500 and bad == "[]", bad[:2000]
