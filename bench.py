@@ -242,7 +242,10 @@ def tune_in_pass(torch, abq, gemms, status, out_path):
     fields = ["mp", "cu", "ring", "warps", "full", "ctas", "slices", "prefill", "planes"]
     candidates = [dict(), dict(full=1, warps=16), dict(full=1, warps=8), dict(planes=1), dict(ctas=296), dict(cu=2), dict(cu=4), dict(cu=8),
                   dict(mp=2), dict(mp=4), dict(mp=8), dict(mp=8, cu=4), dict(mp=4, cu=4), dict(full=1, warps=16, cu=4), dict(full=1, warps=16, cu=8),
-                  dict(full=1, warps=16, mp=8), dict(full=1, warps=8, cu=8)]
+                  dict(full=1, warps=16, mp=8), dict(full=1, warps=8, cu=8),
+                  # K split over CTAs small enough for two to share an SM (the only way 9..16 tokens get a neighbour on their SM)
+                  dict(full=2, warps=8, slices=2, cu=2), dict(full=2, warps=8, slices=4, cu=2), dict(full=2, warps=8, slices=4, cu=1),
+                  dict(full=2, warps=8, slices=8, cu=1), dict(full=1, warps=16, slices=2), dict(prefill=2), dict(prefill=4)]
 
     def plan(g, hints):
         saved = {n: os.environ.get(n) for n in names}
